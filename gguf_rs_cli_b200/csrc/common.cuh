@@ -1,0 +1,69 @@
+// Shared declarations of the sm_100a kernels: storage types, error reporting and the
+// C entry points' conventions.  Every entry point is `extern "C"`, takes raw device
+// pointers and the stream to launch on, and returns 0 or a non-zero code after
+// leaving a message that gb_last_error() returns.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define GB_API extern "C" __attribute__((visibility("default")))
+
+enum GbDtype { GB_F32 = 0, GB_BF16 = 1 };
+
+// Positions per cache page; the host-side page pool uses the same constant.
+constexpr int GB_PAGE = 64;
+constexpr int GB_PAGE_SHIFT = 6;
+
+int gb_fail(const char* fmt, ...);
+
+#define GB_REQUIRE(cond, ...)                 \
+    do {                                      \
+        if (!(cond)) return gb_fail(__VA_ARGS__); \
+    } while (0)
+
+#define GB_LAUNCH_OK(name)                                                        \
+    do {                                                                          \
+        cudaError_t e__ = cudaGetLastError();                                     \
+        if (e__ != cudaSuccess) return gb_fail("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+    } while (0)
+
+static inline bool gb_is_dtype(int d) { return d == GB_F32 || d == GB_BF16; }
+static inline size_t gb_dtype_size(int d) { return d == GB_F32 ? 4 : 2; }
+
+__device__ __forceinline__ float gb_to_float(float v) { return v; }
+__device__ __forceinline__ float gb_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T gb_from_float(float v);
+template <> __device__ __forceinline__ float gb_from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 gb_from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Loads/stores through a runtime dtype tag, for kernels whose cost is not in the
+// conversion (norms, rotation, sampling).
+__device__ __forceinline__ float gb_load(const void* p, int dtype, size_t i) {
+    return dtype == GB_F32 ? reinterpret_cast<const float*>(p)[i]
+                           : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ void gb_store(void* p, int dtype, size_t i, float v) {
+    if (dtype == GB_F32) reinterpret_cast<float*>(p)[i] = v;
+    else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+// Where position `pos` of the sequence with page-table row `row` lives: element offset
+// of [kv head g][pos % PAGE][0] inside one run's K or V storage
+// [pages][kv heads][PAGE][head_dim].
+__device__ __forceinline__ size_t gb_kv_offset(const int* row, int ring_pages, int pos, int g, int nkv, int hd) {
+    int page = row[(pos >> GB_PAGE_SHIFT) % ring_pages];
+    return ((size_t(page) * nkv + g) * GB_PAGE + (pos & (GB_PAGE - 1))) * size_t(hd);
+}
+
+__device__ __forceinline__ float gb_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float gb_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}

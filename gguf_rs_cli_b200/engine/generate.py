@@ -1,0 +1,106 @@
+"""The generation loop above the step function: batches of unequal prompts, stop
+tokens, sequences that end earlier than their batch, and as many batches one after
+another as there are requests.
+
+Per sequence it decides in the reference's order (src/main.rs:279-311): sample from
+the last logits; a stop token ends the sequence and is not emitted; then the count
+limit; then the context limit (position >= context - 1); else the token is emitted
+and fed back.  The loop itself touches no device: it drives a backend (`open`,
+`close`, `run`, `admit`), so its decisions are tested on the host with a scripted one.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+from ..sampling.params import SamplingParams, stream_key
+
+
+class GenerationError(ValueError):
+    """A request that cannot be run (empty prompt, prompt longer than the context)."""
+
+
+@dataclass
+class _Live:
+    request: int
+    slot: int
+    feed: List[int]
+    pos: int = 0
+
+
+@dataclass
+class GenerationStats:
+    """What --stats prints (src/main.rs:118-122): prompt tokens and time, generated
+    tokens and time."""
+    prompt_tokens: int = 0
+    prefill_seconds: float = 0.0
+    generated_tokens: int = 0
+    decode_seconds: float = 0.0
+    decode_steps: int = 0
+    batches: int = 0
+    step_batch_sizes: List[int] = field(default_factory=list)
+
+
+def generate_ids(backend, prompts: Sequence[Sequence[int]], max_tokens: int, params: SamplingParams = SamplingParams(),
+                 stop_token_ids: Sequence[int] = (), max_batch: Optional[int] = None,
+                 on_token: Optional[Callable[[int, int], None]] = None,
+                 stats: Optional[GenerationStats] = None, clock: Optional[Callable[[], float]] = None) -> List[List[int]]:
+    """Returns the generated ids of every prompt, in the order of the prompts.
+
+    backend.context_limit      positions one sequence may hold
+    backend.admit(lens, n)     how many of the next prompts (lengths `lens`) may start together
+                               when each may grow by n tokens; at least 1 or an error
+    backend.open() -> slot     backend.close(slot)
+    backend.run(slots, feeds, keys, params) -> one sampled token per sequence
+    """
+    params.validate()
+    stops = set(int(s) for s in stop_token_ids)
+    ctx = backend.context_limit
+    for i, p in enumerate(prompts):
+        if len(p) == 0:
+            raise GenerationError(f"prompt {i} is empty: a request needs at least one token")
+        if len(p) > ctx:
+            raise GenerationError(f"prompt {i} has {len(p)} tokens, the cache holds {ctx} per sequence")
+    results: List[List[int]] = [[] for _ in prompts]
+    keys = [stream_key(params.seed, i) for i in range(len(prompts))]
+    now = clock or (lambda: 0.0)
+    nxt = 0
+    while nxt < len(prompts):
+        window = prompts[nxt:nxt + max_batch] if max_batch else prompts[nxt:]
+        n = backend.admit([len(p) for p in window], max_tokens)
+        if n < 1:
+            raise GenerationError(f"prompt {nxt} does not fit the cache even alone")
+        live = [_Live(i, backend.open(), list(prompts[i])) for i in range(nxt, nxt + n)]
+        nxt += n
+        first = True
+        if stats:
+            stats.batches += 1
+        while live:
+            t0 = now()
+            sampled = backend.run([s.slot for s in live], [s.feed for s in live], [keys[s.request] for s in live], params)
+            dt = now() - t0
+            if stats:
+                stats.step_batch_sizes.append(len(live))
+                if first:
+                    stats.prompt_tokens += sum(len(s.feed) for s in live)
+                    stats.prefill_seconds += dt
+                else:
+                    stats.decode_steps += 1
+                    stats.decode_seconds += dt
+            first = False
+            still = []
+            for s, tok in zip(live, sampled):
+                s.pos += len(s.feed)
+                tok = int(tok)
+                if tok in stops or len(results[s.request]) >= max_tokens or s.pos >= ctx - 1:
+                    backend.close(s.slot)          # given back at once: the next batch may use it
+                    continue
+                results[s.request].append(tok)
+                if stats:
+                    stats.generated_tokens += 1
+                if on_token:
+                    on_token(s.request, tok)
+                s.feed = [tok]
+                still.append(s)
+            live = still
+    return results

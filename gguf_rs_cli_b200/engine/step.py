@@ -1,0 +1,161 @@
+"""The step function: a batch of sequences, each bringing its next tokens (a whole
+prompt, a further piece of one, or one token), run as one packed batch from the
+cache; returns the logits at the wanted places.
+
+The reference's step is one token of one sequence (`forward_cpu(token, pos, cache)`,
+src/model/llama.rs:343) and its prompt loop calls it once per token
+(src/main.rs:241-256); this one takes all tokens of all sequences at once.  A token's
+position is its index in its sequence, for the cache and for the rotation alike
+(src/model/llama.rs:370-373).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import native
+from ..cache.cache import Cache
+from ..models.decoder import Decoder
+from ..parts.base import StepContext, Workspace
+
+SAMPLER_STATES = {"sampler.recent": ((64,), "int32"), "sampler.count": ((), "int32")}
+
+
+class StepError(ValueError):
+    """A step that cannot run: bad slot, bad token id, empty entry; nothing was launched."""
+
+
+@dataclass
+class Entry:
+    """One sequence's share of a step: its slot, its next tokens, and the places among
+    these tokens whose logits are wanted."""
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class Engine:
+    def __init__(self, model: Decoder, n_tokens: int, n_slots: int, max_len: Optional[int] = None,
+                 max_step_tokens: Optional[int] = None):
+        """n_tokens: the most positions that live sequences hold together, each rounded up
+        to whole pages of 64.  n_slots: the most live sequences.  max_len: the longest
+        sequence (default: the model's max position, at most n_tokens)."""
+        native.require_device()
+        self.model, self.device, self.dtype = model, model.device, model.dtype
+        layout = model.cache_layout()
+        layout.states.update(SAMPLER_STATES)
+        if max_len is None:
+            max_len = model.spec.max_position
+        self.cache = Cache(layout, n_slots, n_tokens, max_len=min(int(max_len), ((n_tokens + 63) // 64) * 64),
+                           max_step_tokens=max_step_tokens, dtype=self.dtype, device=self.device)
+        self.ws = Workspace(self.device)
+        self.runs = model.run_views(self.cache)
+        self.vocab_size = model.spec.vocab_size
+        self._meta_host: Optional[torch.Tensor] = None
+        self._meta_dev: Optional[torch.Tensor] = None
+        self.launches = 0
+
+    # ------------------------------------------------------------ sequences
+    def open(self) -> int:
+        return self.cache.open()
+
+    def close(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    # ----------------------------------------------------------------- plan
+    def _meta(self, n: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self._meta_host is None or self._meta_host.numel() < n:
+            size = max(n, 4096)
+            self._meta_host = torch.empty(size, dtype=torch.int32, pin_memory=True)
+            self._meta_dev = torch.empty(size, dtype=torch.int32, device=self.device)
+        return self._meta_host, self._meta_dev
+
+    def plan(self, entries: Sequence[Entry], pad_to: Optional[int] = None,
+             full_tables: bool = False) -> Tuple[StepContext, torch.Tensor, int]:
+        """Checks the entries, reserves cache room and ships the step's index arrays to the
+        device in one copy.  pad_to pads a batch of single tokens with entries that change
+        nothing.  Returns (context, wanted rows, number of wanted rows)."""
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        V = self.vocab_size
+        slots, qlens = [], []
+        for e in entries:
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"slot {e.slot}: an entry must bring at least one token")
+            for t in e.tokens:
+                if not 0 <= int(t) < V:
+                    raise StepError(f"slot {e.slot}: token id {t} is outside the vocabulary (0..{V - 1})")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"slot {e.slot}: wanted place {w} is not among its {n} tokens")
+            slots.append(int(e.slot))
+            qlens.append(n)
+        starts = [self.cache.length(s) for s in slots]
+        self.cache.reserve(slots, qlens)
+
+        B, T = len(entries), sum(qlens)
+        Bp, Tp = B, T
+        if pad_to is not None and pad_to > B:
+            if max(qlens) != 1:
+                raise StepError("only steps of single tokens can be padded")
+            Bp = Tp = pad_to
+        tokens, seq_of, pos, cu, want = [], [], [], [0], []
+        for b, e in enumerate(entries):
+            tokens += [int(t) for t in e.tokens]
+            seq_of += [b] * qlens[b]
+            pos += list(range(starts[b], starts[b] + qlens[b]))
+            want += [cu[-1] + int(w) for w in e.want]
+            cu.append(cu[-1] + qlens[b])
+        padT, padB = Tp - T, Bp - B
+        tokens += [0] * padT
+        seq_of += [-1] * padT
+        pos += [0] * padT
+        cu += [cu[-1]] * padB
+        slots_p = slots + [-1] * padB
+        starts_p = starts + [0] * padB
+        qlens_p = qlens + [0] * padB
+        flat = tokens + seq_of + pos + slots_p + starts_p + qlens_p + cu + want
+        offs, o = {}, 0
+        for name, n in (("tokens", Tp), ("seq_of", Tp), ("pos", Tp), ("slots", Bp), ("starts", Bp), ("qlens", Bp),
+                        ("cu", Bp + 1), ("want", len(want))):
+            offs[name] = (o, n)
+            o += n
+        table_offs = []
+        max_kv = max(s + q for s, q in zip(starts, qlens))
+        for g in self.cache.groups:
+            # only as many table entries as this step's longest sequence uses, unless the
+            # caller needs the same layout every step (a captured graph)
+            width = g.table_width if full_tables else max(1, g.pages_needed(max_kv))
+            rows = self.cache.table_rows(g.index, slots_p, width)
+            table_offs.append((len(flat), Bp, width))
+            for r in rows:
+                flat += r
+        host, dev = self._meta(len(flat))
+        host[:len(flat)] = torch.tensor(flat, dtype=torch.int32)
+        dev[:len(flat)].copy_(host[:len(flat)], non_blocking=True)
+
+        def view(name):
+            a, n = offs[name]
+            return dev[a:a + n]
+
+        ctx = StepContext(
+            T=Tp, B=Bp, dtype=self.dtype, tokens=view("tokens"), seq_of=view("seq_of"), pos=view("pos"),
+            slots=view("slots"), starts=view("starts"), qlens=view("qlens"), cu=view("cu"),
+            tables=[dev[a:a + b * w].view(b, w) for a, b, w in table_offs], cache=self.cache, ws=self.ws,
+            decode=max(qlens) == 1, max_qlen=max(qlens), max_kv=max_kv,
+            host={"slots": slots, "starts": starts, "qlens": qlens, "h2d_bytes": 4 * len(flat)})
+        return ctx, view("want"), len(want)
+
+    # ----------------------------------------------------------------- step
+    def step(self, entries: Sequence[Entry]) -> Optional[torch.Tensor]:
+        """Runs the entries' tokens as one batch from the cache and advances the sequences.
+        Returns float32 logits [wanted, V] in the order of the entries and of each `want`
+        (None when nothing is wanted; the tokens still enter the cache)."""
+        entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
+        ctx, want_rows, n_want = self.plan(entries)
+        logits = self.model.forward(ctx, self.runs, want_rows)
+        self.cache.advance(ctx.host["slots"], ctx.host["qlens"])
+        return logits if n_want else None

@@ -1,0 +1,122 @@
+"""Typed Python faces of the CUDA entry points: tensors in, launch on the current
+stream.  Nothing here computes; a missing or failing library raises NativeError.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import native
+from .native import call, dtype_code, ptr, stream_ptr
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise native.NativeError("kernels take CUDA tensors only; there is no CPU path")
+
+
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t,:] = table[tokens[t],:] in float32."""
+    _cuda(table, tokens, out)
+    V, E = table.shape
+    T = tokens.numel()
+    assert out.dtype == torch.float32 and out.shape == (T, E) and out.is_contiguous() and tokens.dtype == torch.int32
+    call("gb_embed", ptr(table), dtype_code(table), ptr(tokens), T, E, V, ptr(out), stream_ptr())
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None, write_x: bool = True) -> torch.Tensor:
+    """x: float32 [T,E] residual stream.  delta: None, [T,E] or [S,T,E] terms still to be
+    added to x.  rows: int32 row numbers to gather (then out has len(rows) rows)."""
+    _cuda(x, delta, weight, out, rows)
+    T, E = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and weight.numel() == E
+    n_delta, stride = 0, 0
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape[-2:] == (T, E)
+        n_delta = 1 if delta.dim() == 2 else delta.shape[0]
+        stride = T * E
+    n_rows = T if rows is None else rows.numel()
+    assert out.shape == (n_rows, E)
+    call("gb_add_rmsnorm", ptr(x), ptr(delta), 0 if delta is None else dtype_code(delta), n_delta, stride, ptr(rows),
+         n_rows, E, ptr(weight), dtype_code(weight), float(eps), ptr(out), dtype_code(out), int(write_x), stream_ptr())
+    return out
+
+
+def rope_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], n_heads: int, n_kv_heads: int,
+                  head_dim: int, inv_freq: Optional[torch.Tensor], rotary_dim: int, pairing: int,
+                  seq_of: torch.Tensor, pos: torch.Tensor, table: Optional[torch.Tensor], ring_pages: int,
+                  kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor]) -> None:
+    """q, k, v: column slices [T, heads*head_dim] of one row-major buffer (equal row
+    stride).  Rotates q in place; writes rotated k and v into the cache pages."""
+    _cuda(q, k, v, inv_freq, seq_of, pos, table, kcache, vcache)
+    T = q.shape[0]
+    ld = q.stride(0)
+    assert q.stride(1) == 1 and (k is None or (k.stride(0) == ld and v.stride(0) == ld and k.dtype == q.dtype))
+    call("gb_rope_kv_write", ptr(q), ptr(k), ptr(v), dtype_code(q), ld, T, n_heads, n_kv_heads, head_dim,
+         rotary_dim, pairing, ptr(inv_freq), ptr(seq_of), ptr(pos), ptr(table),
+         0 if table is None else table.shape[1], ring_pages, ptr(kcache), ptr(vcache),
+         0 if kcache is None else dtype_code(kcache), stream_ptr())
+
+
+def attention_generic(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                      seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, ring_pages: int,
+                      kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float) -> torch.Tensor:
+    _cuda(q, out, seq_of, pos, table, kcache, vcache)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, n_heads * head_dim)
+    call("gb_attention_generic", ptr(q), dtype_code(q), q.stride(0), ptr(out), dtype_code(out), out.stride(0), T,
+         n_heads, n_kv_heads, head_dim, ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(kcache),
+         ptr(vcache), dtype_code(kcache), int(window or 0), float(scale), stream_ptr())
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """gate_up: [T, 2F], gate in the first F columns; out[t,i] = silu(gate)*up."""
+    _cuda(gate_up, out)
+    T, F = out.shape
+    assert gate_up.shape == (T, 2 * F) and gate_up.stride(1) == 1 and out.is_contiguous() and out.dtype == gate_up.dtype
+    call("gb_swiglu", ptr(gate_up), gate_up.stride(0), ptr(out), T, F, dtype_code(out), stream_ptr())
+    return out
+
+
+def gemm_generic(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+    """out[t,n] = sum_k x[t,k] w[n,k] + bias[n], 32-bit FMAs on the CUDA cores."""
+    _cuda(x, w, bias, out)
+    T, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (T, N) and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    call("gb_gemm_generic", ptr(x), dtype_code(x), x.stride(0), ptr(w), dtype_code(w), w.stride(0), ptr(bias),
+         0 if bias is None else dtype_code(bias), ptr(out), dtype_code(out), out.stride(0), T, N, K, stream_ptr())
+    return out
+
+
+def sample(logits: torch.Tensor, slots: torch.Tensor, seeds: torch.Tensor, temperature: float, top_k: int,
+           top_p: float, rep_penalty: float, recent: torch.Tensor, count: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """One token per row of float32 logits [n, V]; the repetition penalty changes the logits
+    in place.  recent [slots, 64] and count [slots] are the sequences' own state."""
+    _cuda(logits, slots, seeds, recent, count, out)
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and seeds.dtype == torch.int64
+    assert slots.dtype == torch.int32 and recent.dtype == torch.int32 and count.dtype == torch.int32
+    assert recent.shape[1] == 64 and recent.is_contiguous() and out.dtype == torch.int32 and out.numel() >= n
+    call("gb_sample", ptr(logits), logits.stride(0), n, V, ptr(slots), ptr(seeds), float(temperature), int(top_k),
+         float(top_p), float(rep_penalty), ptr(recent), ptr(count), ptr(out), stream_ptr())
+    return out
+
+
+# ------------------------------------------------------------------ dispatch
+def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+    """The product path of every projection: the tensor-core kernel when dtype and sizes
+    fit it, else the CUDA-core kernel."""
+    return gemm_generic(x, w, bias, out)
+
+
+def attention(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, ctx, table: torch.Tensor,
+              ring_pages: int, kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float) -> torch.Tensor:
+    """Attention of one step over the cache; picks the kernel for the step's shape."""
+    return attention_generic(q, out, n_heads, n_kv_heads, head_dim, ctx.seq_of, ctx.pos, table, ring_pages, kcache,
+                             vcache, window, scale)

@@ -1,0 +1,126 @@
+"""The generic decoder: builds parts from a ModelSpec and runs them in the spec's
+order.  It is the only model class; architectures differ in the spec they build.
+
+forward: embedding -> for each run of the schedule, that layer's block on the
+residual stream -> final norm on the wanted rows only -> head.  The reference runs
+the head for every token and throws all but the last logits away
+(src/main.rs:248-254); here only the rows that are asked for reach the final norm
+and the head.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..cache.cache import Cache, CacheLayout
+from ..config.specs import LayerSpec, ModelSpec, PartSpec
+from ..parts.base import RunView, StepContext, Stream
+from ..parts.registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS
+from ..weights.loader import TensorRequest, WeightStore
+
+
+class Layer:
+    def __init__(self, spec: LayerSpec, dtype, device, positions: Dict[str, object]):
+        position = None
+        if spec.position is not None:
+            key = spec.position.key()
+            if key not in positions:          # layers with equal constants share one table
+                positions[key] = POSITIONS.get(spec.position.kind)(spec.position, dtype, device)
+            position = positions[key]
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, dtype, device, position=position)
+        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, dtype, device)
+        self.norms = {name: NORMS.get(s.kind)(s, dtype, device) for name, s in spec.norms.items()}
+        self.block = BLOCKS.get(spec.block)(self.mixer, self.feed_forward, self.norms)
+
+    def parts(self):
+        return [self.mixer, self.feed_forward] + list(self.norms.values())
+
+
+def _requests_of(spec: ModelSpec, parts) -> List[TensorRequest]:
+    seen, out = set(), []
+    for p in parts:
+        for r in p.tensor_requests():
+            if (r.name, r.fallback) not in seen:
+                seen.add((r.name, r.fallback))
+                out.append(r)
+    return out
+
+
+class Decoder:
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device):
+        spec.validate()
+        self.spec, self.dtype, self.device = spec, dtype, device
+        self.positions: Dict[str, object] = {}
+        self.embedding = EMBEDDINGS.get(spec.embedding.kind)(spec.embedding, dtype, device)
+        self.layers = [Layer(ls, dtype, device, self.positions) for ls in spec.layers]
+        self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, dtype, device)
+        self.head = HEADS.get(spec.head.kind)(spec.head, dtype, device)
+        for r, run in enumerate(spec.schedule):
+            mixer = self.layers[run.layer].mixer
+            owns = mixer.kv_spec() is not None
+            if run.cache_of is not None and owns:
+                raise ValueError(f"schedule[{r}] reads the cache of run {run.cache_of}, but its mixer keeps keys and "
+                                 f"values of its own (build it with shares_kv)")
+            if run.cache_of is not None:
+                src = self.layers[spec.schedule[run.cache_of].layer].mixer.kv_spec()
+                if src is None or src != mixer.reads_kv_spec():
+                    raise ValueError(f"schedule[{r}] cannot read the cache of run {run.cache_of}: {src} does not match "
+                                     f"{mixer.reads_kv_spec()}")
+
+    # ---------------------------------------------------------------- weights
+    def parts(self):
+        out = [self.embedding]
+        for l in self.layers:
+            out += l.parts()
+        return out + [self.final_norm, self.head]
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        return _requests_of(self.spec, self.parts())
+
+    def load(self, store: WeightStore) -> "Decoder":
+        store.check(self.tensor_requests())
+        for p in self.parts():
+            p.load(store)
+        store.release()
+        return self
+
+    # ------------------------------------------------------------------ cache
+    def cache_layout(self) -> CacheLayout:
+        """Keys and values for every run whose mixer keeps them, and the fixed-size state
+        every run's mixer declares (named run<r>.<name>)."""
+        layout = CacheLayout()
+        for r, run in enumerate(self.spec.schedule):
+            mixer = self.layers[run.layer].mixer
+            kv = mixer.kv_spec()
+            if kv is not None and run.cache_of is None:
+                layout.kv[r] = kv
+            for name, sd in mixer.state_spec().items():
+                layout.states[f"run{r}.{name}"] = sd
+        return layout
+
+    def run_views(self, cache: Cache) -> List[RunView]:
+        views = []
+        for r, run in enumerate(self.spec.schedule):
+            src = r if run.cache_of is None else run.cache_of
+            if src in cache.group_of_run:
+                gi, i = cache.group_of_run[src]
+                g = cache.groups[gi]
+                views.append(RunView(r, run.layer, run.cache_of is None, gi, g.k[i], g.v[i], g.ring_pages, g.spec))
+            else:
+                views.append(RunView(r, run.layer, False))
+        return views
+
+    # ---------------------------------------------------------------- forward
+    def forward(self, ctx: StepContext, runs: List[RunView], want_rows: torch.Tensor) -> torch.Tensor:
+        """Logits float32 [len(want_rows), V] at the packed token rows asked for."""
+        stream = Stream(self.embedding.forward(ctx.tokens, ctx))
+        for view in runs:
+            self.layers[view.layer].block.forward(stream, ctx, view)
+        h = self.final_norm.apply(stream, ctx, rows=want_rows, buffer="final_normed")
+        return self.head.forward(h, ctx)
+
+
+def tensor_requests(spec: ModelSpec) -> List[TensorRequest]:
+    """The tensors a model of this spec asks for, without building anything on a device."""
+    return Decoder(spec, torch.float32, "meta").tensor_requests()

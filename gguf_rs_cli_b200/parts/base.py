@@ -1,0 +1,113 @@
+"""Interfaces of the parts and the objects a step hands them.
+
+Every part is built from its `PartSpec` alone (sizes and constants in `spec.params`,
+tensor names in `spec.tensors`), says which tensors it needs (`tensor_requests`),
+takes them from the store (`load`), and computes on the tokens of one step.  No part
+knows which model it is in.
+
+Roles:
+  norm          apply(stream, ctx, rows=None) -> normalised rows in ctx.dtype; folds the
+                stream's pending term into x (32-bit sum) on the way
+  position      gives the mixer what it needs to encode positions (for "rope": inv_freq,
+                rotary_dim, pairing)
+  mixer         kv_spec() -> KVSpec or None; state_spec() -> {name: (shape, dtype name)};
+                forward(h, ctx, run) -> term [T, E] (or [S, T, E] partial sums) to add to x
+  feed-forward  forward(h, ctx) -> term to add to x
+  block         forward(stream, ctx, run): wires norms, mixer and feed-forward around x
+  embedding     forward(tokens, ctx) -> float32 x [T, E]
+  head          forward(h, ctx) -> float32 logits [rows, V]
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..cache.cache import Cache, KVSpec
+from ..config.specs import PartSpec
+from ..weights.loader import TensorRequest, WeightStore
+
+
+class Part:
+    def __init__(self, spec: PartSpec, dtype: torch.dtype, device):
+        self.spec, self.dtype, self.device = spec, dtype, device
+        self.p = spec.params
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        return []
+
+    def load(self, store: WeightStore) -> None:
+        pass
+
+
+class Workspace:
+    """Buffers that live as long as the engine and are handed out by name, so that a
+    step allocates nothing once its shapes have been seen (and a captured graph keeps
+    valid addresses)."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[Tuple, torch.Tensor] = {}
+
+    def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        key = (name, tuple(int(s) for s in shape), dtype)
+        t = self._bufs.get(key)
+        if t is None:
+            t = torch.empty(key[1], dtype=dtype, device=self.device)
+            self._bufs[key] = t
+        return t
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._bufs.values())
+
+
+@dataclass
+class RunView:
+    """What one entry of the run order sees of the cache: its group's geometry and its
+    own K and V storage [pages, kv heads, PAGE, head_dim] (None when the mixer keeps no
+    keys), plus the page tables of this step's sequences for that group."""
+    index: int
+    layer: int
+    owns_cache: bool
+    group: Optional[int] = None
+    k: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None
+    ring_pages: int = 1
+    kv_spec: Optional[KVSpec] = None
+
+
+@dataclass
+class StepContext:
+    """One step's batch on the device.  T tokens of B sequences, packed sequence after
+    sequence; padding tokens have seq_of = -1 and padding sequences slot = -1."""
+    T: int
+    B: int
+    dtype: torch.dtype
+    tokens: torch.Tensor          # int32 [T]
+    seq_of: torch.Tensor          # int32 [T]  row of the token's sequence in this step's tables
+    pos: torch.Tensor             # int32 [T]  position of the token in its sequence
+    slots: torch.Tensor           # int32 [B]  cache slot of each sequence (-1: padding)
+    starts: torch.Tensor          # int32 [B]  cached length before this step
+    qlens: torch.Tensor           # int32 [B]
+    cu: torch.Tensor              # int32 [B+1] first token of each sequence in the packing
+    tables: List[torch.Tensor]    # per cache group: int32 [B, table width]
+    cache: Cache
+    ws: Workspace
+    decode: bool                  # every sequence brings exactly one token
+    max_qlen: int
+    max_kv: int                   # longest cached length after this step
+    host: Dict = field(default_factory=dict)    # host copies for parts that plan on the host
+
+    def state(self, name: str) -> torch.Tensor:
+        """Fixed-size per-sequence state [slots, ...]; index it with ctx.slots."""
+        return self.cache.states[name]
+
+
+class Stream:
+    """The residual stream: x in float32 plus a term that has not been added yet.  The
+    next norm adds it in 32-bit in the same kernel that normalises."""
+
+    def __init__(self, x: torch.Tensor):
+        self.x = x
+        self.pending: Optional[torch.Tensor] = None

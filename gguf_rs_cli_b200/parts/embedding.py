@@ -1,0 +1,47 @@
+"""Token embedding (a row gather, src/model/llama.rs:349) and the output head
+(logits = W h, src/model/llama.rs:406-407), which falls back to the embedding table
+when the folder has no matrix of its own (src/model/llama.rs:124)."""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .. import kernels
+from ..weights.loader import TensorRequest, WeightStore
+from .base import Part, StepContext
+from .linear import Linear
+from .registry import register_embedding, register_head
+
+
+@register_embedding("embedding")
+class Embedding(Part):
+    """params: vocab_size, hidden_size.  tensors: weight [V, E]."""
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        return [TensorRequest(self.spec.tensors["weight"], (self.p["vocab_size"], self.p["hidden_size"]))]
+
+    def load(self, store: WeightStore) -> None:
+        self.weight = store.get(self.tensor_requests()[0])
+
+    def forward(self, tokens: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        x = ctx.ws.get("x", (tokens.numel(), self.p["hidden_size"]), torch.float32)
+        return kernels.embed(self.weight, tokens, x)
+
+
+@register_head("lm_head")
+class LMHead(Part):
+    """params: vocab_size, hidden_size, tied_to (a tensor name or None).
+    tensors: weight [V, E], absent from a folder whose head is tied."""
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        shape = (self.p["vocab_size"], self.p["hidden_size"])
+        if self.p.get("tied_to"):
+            return [TensorRequest(self.spec.tensors["weight"], shape, optional=True, fallback=self.p["tied_to"])]
+        return [TensorRequest(self.spec.tensors["weight"], shape)]
+
+    def load(self, store: WeightStore) -> None:
+        self.proj = Linear(store.get(self.tensor_requests()[0]), name="logits")
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        return self.proj(h, ctx, out_dtype=torch.float32)

@@ -1,0 +1,42 @@
+"""Dense gated feed-forward: down(act(gate(h)) * up(h)) with act = SiLU
+(src/model/llama.rs:399-402, src/math/ops.rs:11).  gate and up are one matrix
+[2F, E] after loading, so one product reads h once."""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .. import kernels
+from ..weights.loader import TensorRequest, WeightStore
+from .base import Part, StepContext
+from .linear import Linear
+from .registry import register_feed_forward
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(Part):
+    """params: hidden_size, intermediate_size, activation ("silu").
+    tensors: gate [F, E], up [F, E], down [E, F]."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        if self.p.get("activation", "silu") != "silu":
+            raise ValueError(f"gated_mlp: activation {self.p['activation']!r} is not supported (silu)")
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        E, F, t = self.p["hidden_size"], self.p["intermediate_size"], self.spec.tensors
+        return [TensorRequest(t["gate"], (F, E)), TensorRequest(t["up"], (F, E)), TensorRequest(t["down"], (E, F))]
+
+    def load(self, store: WeightStore) -> None:
+        g, u, d = (store.get(r) for r in self.tensor_requests())
+        if g.dtype != u.dtype:
+            u = u.to(g.dtype)
+        self.gate_up = Linear(torch.cat([g, u], dim=0), name="ff.gate_up")
+        self.down = Linear(d, name="ff.down")
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        gu = self.gate_up(h, ctx)
+        act = ctx.ws.get("ff.act", (h.shape[0], self.p["intermediate_size"]), ctx.dtype)
+        kernels.swiglu(gu, act)
+        return self.down(act, ctx)

@@ -1,0 +1,35 @@
+"""RMS norm: x / sqrt(mean(x^2) + eps) * w, sums in 32-bit (src/math/ops.rs:1-4,
+src/gpu/rmsnorm.glsl:13-26), fused with the residual add that precedes it as the
+reference's unused add_rmsnorm shader does (src/gpu/add_rmsnorm.glsl:1-32)."""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from .. import kernels
+from ..weights.loader import TensorRequest, WeightStore
+from .base import Part, StepContext, Stream
+from .registry import register_norm
+
+
+@register_norm("rmsnorm")
+class RMSNorm(Part):
+    """params: size, eps.  tensors: weight [size]."""
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        return [TensorRequest(self.spec.tensors["weight"], (self.p["size"],))]
+
+    def load(self, store: WeightStore) -> None:
+        self.weight = store.get(self.tensor_requests()[0])
+
+    def apply(self, stream: Stream, ctx: StepContext, rows: Optional[torch.Tensor] = None,
+              buffer: str = "normed") -> torch.Tensor:
+        """Adds the stream's pending term into x and returns the normalised rows.  With
+        `rows`, only those rows are produced and x is left as it is."""
+        n = stream.x.shape[0] if rows is None else rows.numel()
+        out = ctx.ws.get(buffer, (n, self.p["size"]), ctx.dtype)
+        kernels.add_rmsnorm(stream.x, stream.pending, self.weight, self.p["eps"], out, rows=rows, write_x=rows is None)
+        if rows is None:
+            stream.pending = None
+        return out

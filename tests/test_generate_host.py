@@ -1,0 +1,115 @@
+"""The generation loop's decisions, with a scripted backend in place of the device."""
+import pytest
+
+from gguf_rs_cli_b200.engine import GenerationError, GenerationStats, generate_ids
+from gguf_rs_cli_b200.sampling import SamplingParams, stream_key
+
+
+class Scripted:
+    """Sequences "generate" prompt[0]+1, +2, ...; keeps a log of every call and a slot pool."""
+
+    def __init__(self, n_slots=2, context_limit=100, admit_limit=None):
+        self.free = list(range(n_slots))
+        self.context_limit = context_limit
+        self.admit_limit = admit_limit
+        self.state = {}
+        self.log = []
+        self.held_max = 0
+
+    def admit(self, lens, max_new):
+        n = min(len(lens), len(self.free))
+        return n if self.admit_limit is None else min(n, self.admit_limit)
+
+    def open(self):
+        s = self.free.pop(0)
+        self.state[s] = None
+        self.held_max = max(self.held_max, len(self.state))
+        self.log.append(("open", s))
+        return s
+
+    def close(self, slot):
+        assert slot in self.state, "closed twice"
+        del self.state[slot]
+        self.free.append(slot)
+        self.free.sort()
+        self.log.append(("close", slot))
+
+    def run(self, slots, feeds, keys, params):
+        self.log.append(("run", list(slots), [list(f) for f in feeds]))
+        out = []
+        for s, f in zip(slots, feeds):
+            if self.state[s] is None:
+                self.state[s] = [f[0], 0, len(f)]
+            else:
+                assert len(f) == 1, "after the prompt a sequence brings one token"
+                self.state[s][2] += 1
+            self.state[s][1] += 1
+            out.append(self.state[s][0] + self.state[s][1])
+        return out
+
+
+def test_max_tokens_and_order_of_results():
+    b = Scripted(n_slots=3)
+    out = generate_ids(b, [[10, 1], [20], [30, 1, 1]], max_tokens=3)
+    assert out == [[11, 12, 13], [21, 22, 23], [31, 32, 33]]
+    runs = [e for e in b.log if e[0] == "run"]
+    assert runs[0][2] == [[10, 1], [20], [30, 1, 1]]              # prompts in one step
+    assert all(all(len(f) == 1 for f in r[2]) for r in runs[1:])   # then one token each
+    assert len(runs) == 4 and not b.state
+
+
+def test_stop_token_ends_early_and_is_not_emitted():
+    b = Scripted(n_slots=2)
+    out = generate_ids(b, [[10], [20]], max_tokens=5, stop_token_ids=[12])
+    assert out == [[11], [21, 22, 23, 24, 25]]
+    runs = [e for e in b.log if e[0] == "run"]
+    assert runs[1][1] == [0, 1] and runs[2][1] == [1]             # the finished one left the batch
+    i_close0 = b.log.index(("close", 0))
+    assert i_close0 < b.log.index(runs[2])                         # and gave its slot back at once
+
+
+def test_batches_follow_one_another_and_reuse_slots():
+    b = Scripted(n_slots=2)
+    prompts = [[10 * i] for i in range(1, 6)]
+    stats = GenerationStats()
+    out = generate_ids(b, prompts, max_tokens=2, stats=stats)
+    assert out == [[10 * i + 1, 10 * i + 2] for i in range(1, 6)]
+    assert stats.batches == 3 and b.held_max == 2 and not b.state
+    opens = [e[1] for e in b.log if e[0] == "open"]
+    assert opens == [0, 1, 0, 1, 0]
+    assert stats.generated_tokens == 10 and stats.prompt_tokens == 5
+
+
+def test_max_batch_limits_a_batch():
+    b = Scripted(n_slots=4)
+    stats = GenerationStats()
+    generate_ids(b, [[1], [2], [3]], max_tokens=1, max_batch=2, stats=stats)
+    assert stats.batches == 2 and b.held_max == 2
+
+
+def test_context_limit_stops_as_the_reference_does():
+    # position >= context - 1 ends the sequence after sampling (src/main.rs:284-286)
+    b = Scripted(n_slots=1, context_limit=8)
+    out = generate_ids(b, [[10, 0, 0, 0, 0]], max_tokens=50)
+    assert out == [[11, 12]]          # cache reaches 7 positions, never context - 1
+    with pytest.raises(GenerationError, match="holds 8"):
+        generate_ids(Scripted(n_slots=1, context_limit=8), [[1] * 9], max_tokens=1)
+
+
+def test_zero_max_tokens_and_errors():
+    assert generate_ids(Scripted(), [[5]], max_tokens=0) == [[]]
+    with pytest.raises(GenerationError, match="empty"):
+        generate_ids(Scripted(), [[1], []], max_tokens=1)
+    with pytest.raises(GenerationError, match="does not fit"):
+        generate_ids(Scripted(admit_limit=0), [[1]], max_tokens=1)
+    with pytest.raises(ValueError, match="top_p"):
+        generate_ids(Scripted(), [[1]], 1, SamplingParams(top_p=0.0))
+
+
+def test_streaming_callback_and_keys():
+    seen = []
+    b = Scripted(n_slots=2)
+    generate_ids(b, [[10], [20]], max_tokens=2, on_token=lambda i, t: seen.append((i, t)))
+    assert seen == [(0, 11), (1, 21), (0, 12), (1, 22)]
+    assert stream_key(1, 0) != stream_key(1, 1) != stream_key(2, 1)
+    assert -(1 << 63) <= stream_key(123, 4) < (1 << 63)

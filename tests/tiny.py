@@ -1,0 +1,39 @@
+"""The tiny configurations the tests run: two Llama shapes that differ in every size
+and option, as plain config.json dicts, plus helpers to make a model folder."""
+import copy
+
+TINY_A = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+    "intermediate_size": 176, "vocab_size": 256, "rope_theta": 10000.0, "rope_scaling": None,
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 128, "tie_word_embeddings": False,
+    "hidden_act": "silu", "attention_bias": False, "eos_token_id": 2, "bos_token_id": 1,
+}
+
+TINY_B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 4, "num_key_value_heads": 1, "head_dim": 24,
+    "intermediate_size": 224, "vocab_size": 384, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64},
+    "rms_norm_eps": 1e-6, "max_position_embeddings": 256, "tie_word_embeddings": True,
+    "hidden_act": "silu", "attention_bias": True, "eos_token_id": [3, 5], "bos_token_id": 0,
+}
+
+# A wider shape whose sizes reach the tensor-core and tiled kernels: head_dim 64, sizes
+# that are multiples of 8 but of no power of two beyond that.
+TINY_C = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 320, "num_attention_heads": 6, "num_key_value_heads": 3, "head_dim": 64,
+    "intermediate_size": 520, "vocab_size": 1000, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 128},
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 1024, "tie_word_embeddings": False,
+    "hidden_act": "silu", "attention_bias": False, "eos_token_id": 2,
+}
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+
+
+def config(name):
+    return copy.deepcopy(CONFIGS[name])
