@@ -1,0 +1,265 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the Llama-3.1-8B shape with random bf16 weights on
+one B200.  Prints one JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--layers L] [--batch B] [--no-points]
+
+`value` is decoded tokens a second at batch 8 after 512-token prompts, timed on the
+device with CUDA events around K decode steps (each step: index arrays host to
+device, the model, sampling, sampled ids device to host).  `e2e` is the same through
+the Python entry point `generate()`, host token ids in and out.  `prefill` is one
+step of 2,048 tokens; `points` are decode at batch 1 and 64; `roofline` is the bytes a
+decode step has to read (every weight once, the cache of the live requests) over its
+time, against the measured copy bandwidth.  The weights (15 GB) are far larger than
+L2, so consecutive steps cannot reuse cached inputs.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPE_8B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 32, "hidden_size": 4096,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336,
+    "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 8192, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+CONTEXT = 8192
+PROMPT = 512
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            raw = json.load(f)
+        out = {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
+        if raw.get("bf16_tflops_sustained"):
+            out["bf16_tflops_sustained"] = float(raw["bf16_tflops_sustained"])
+        return out
+    except Exception:
+        return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def mark(self):
+        return time.time()
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        rows = [r for t, r in self.rows if t0 <= t <= t1 and len(r) >= 6] or [r for _, r in self.rows if len(r) >= 6]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(int(r[0]) for r in rows if r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None,
+                "sm_max_mhz": int(rows[0][1]) if rows[0][1].isdigit() else None, "reasons": reasons, "samples": len(rows)}
+
+
+def weight_bytes(cfg, layers):
+    E, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (nh * hd * E + 2 * nkv * hd * E + E * nh * hd + 3 * F * E + 2 * E) * 2
+    return layers * per_layer + (V * E + E) * 2          # + head and final norm; embedding rows are negligible
+
+
+def kv_bytes_per_token(cfg, layers):
+    return layers * 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+
+def prefill_flops(cfg, layers, T):
+    E, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    linear = 2 * T * layers * (nh * hd * E + 2 * nkv * hd * E + E * nh * hd + 3 * F * E)
+    attn = layers * 4 * nh * hd * T * (T + 1) // 2
+    return linear + attn + 2 * V * E
+
+
+def measure_decode(llm, batch, steps, warmup, cfg):
+    """K decode steps at `batch` after 512-token prompts.  Returns (tokens/s, ms/step,
+    launches per step, context at the middle of the timed steps)."""
+    import torch
+    from gguf_rs_cli_b200 import native
+    from gguf_rs_cli_b200.sampling import SamplingParams, stream_key
+    g = torch.Generator().manual_seed(batch)
+    prompts = [torch.randint(0, cfg["vocab_size"], (PROMPT,), generator=g).tolist() for _ in range(batch)]
+    backend = llm.backend(n_tokens=64 * CONTEXT, n_slots=64, max_len=CONTEXT)
+    params = SamplingParams(temperature=0.0)
+    keys = [stream_key(0, i) for i in range(batch)]
+    slots = [backend.open() for _ in range(batch)]
+    toks = backend.run(slots, prompts, keys, params)
+    for _ in range(warmup):
+        toks = backend.run(slots, [[t] for t in toks], keys, params)
+    torch.cuda.synchronize()
+    n0 = native.launch_count()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        toks = backend.run(slots, [[t] for t in toks], keys, params)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    launches = (native.launch_count() - n0) // steps
+    for s in slots:
+        backend.close(s)
+    ctx_mid = PROMPT + warmup + steps // 2
+    return batch * 1000.0 / ms, ms, launches, ctx_mid
+
+
+def measure_prefill(llm, cfg, layers, reps=3):
+    import torch
+    from gguf_rs_cli_b200.engine.step import Entry
+    eng = llm.engine(n_tokens=64 * CONTEXT, n_slots=64, max_len=CONTEXT)
+    g = torch.Generator().manual_seed(7)
+    toks = torch.randint(0, cfg["vocab_size"], (PREFILL_TOKENS,), generator=g).tolist()
+    best = None
+    for i in range(reps + 1):
+        s = eng.open()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        eng.step([Entry(s, toks, [PREFILL_TOKENS - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        eng.close(s)
+        if i:                                       # the first run warms up
+            ms = a.elapsed_time(b)
+            best = ms if best is None else min(best, ms)
+    return best
+
+
+def measure_e2e(llm, cfg, batch, steps):
+    """Through generate(): host ids in, host ids out.  Decode tokens a second from the
+    loop's own clock (synchronised on both sides of every step)."""
+    import torch
+    from gguf_rs_cli_b200.api import generate
+    from gguf_rs_cli_b200.engine.generate import GenerationStats
+    g = torch.Generator().manual_seed(100 + batch)
+    prompts = [torch.randint(0, cfg["vocab_size"], (PROMPT,), generator=g).tolist() for _ in range(batch)]
+    backend = llm.backend(n_tokens=64 * CONTEXT, n_slots=64, max_len=CONTEXT)
+    h0, d0 = backend.h2d_bytes, backend.d2h_bytes
+    stats = GenerationStats()
+    out = generate(llm, prompts, max_tokens=steps, temperature=0.0, stop_token_ids=[], max_batch=64, ctx_len=CONTEXT,
+                   stats=stats)
+    assert all(len(o) == steps for o in out)
+    n_steps = stats.decode_steps + 1
+    tok_s = batch * stats.decode_steps / max(stats.decode_seconds, 1e-9)
+    return tok_s, (backend.h2d_bytes - h0) // n_steps, (backend.d2h_bytes - d0) // n_steps
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=SHAPE_8B["num_hidden_layers"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1/64, prefill and e2e")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust/Vulkan program: pip finds neither "
+                          "setup.py nor pyproject.toml, and the image has no cargo, rustc or Vulkan loader"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+    from gguf_rs_cli_b200 import native
+    from gguf_rs_cli_b200.api import from_random
+    cfg = dict(SHAPE_8B)
+    full_layers = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = args.layers
+    pk = peaks()
+    llm = from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = sampler.mark()
+    tok_s, ms, launches, ctx_mid = measure_decode(llm, args.batch, args.steps, warmup, cfg)
+    t1 = sampler.mark()
+    clocks = sampler.summary(t0, t1)
+
+    wbytes, kvb = weight_bytes(cfg, args.layers), kv_bytes_per_token(cfg, args.layers)
+    step_bytes = wbytes + args.batch * ctx_mid * kvb
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "Llama-3.1-8B decode tok/s @ batch 8 (512-token prompts)", "value": round(tok_s, 2), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights N(0,0.02)",
+        "impl": "ours",
+        "config": {"model": "llama-3.1-8b-shape", "layers": args.layers, "layers_full": full_layers,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
+                   "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single-gpu",
+                   "l2": "inputs (15 GB of weights per step) exceed L2", "peaks": pk["source"]},
+        "clocks": clocks, "gpu_launches": launches * args.steps,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": step_bytes},
+    }
+    if not args.no_points:
+        pms = measure_prefill(llm, cfg, args.layers)
+        flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
+        line["prefill"] = {"value": round(PREFILL_TOKENS * 1000.0 / pms, 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+                           "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        points = {}
+        for b in (1, 64):
+            p_tok_s, p_ms, _, _ = measure_decode(llm, b, max(8, args.steps // 2), warmup, cfg)
+            points[f"decode_b{b}"] = round(p_tok_s, 2)
+            points[f"decode_b{b}_ms"] = round(p_ms, 4)
+        line["points"] = points
+        e_tok_s, h2d, d2h = measure_e2e(llm, cfg, args.batch, args.steps)
+        line["e2e"] = {"value": round(e_tok_s, 2), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+                       "d2h_bytes_per_step": int(d2h)}
+    sampler.stop()
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

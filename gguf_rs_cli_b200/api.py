@@ -44,7 +44,13 @@ class LLM:
         self._backend: Optional[EngineBackend] = None
 
     def engine(self, n_tokens: int, n_slots: int, max_len: Optional[int] = None) -> Engine:
+        """An engine whose cache has at least this room; the one at hand is kept when it
+        is large enough and idle, else a new one replaces it."""
         key = (n_tokens, n_slots, max_len)
+        e = self._engine
+        if (e is not None and e.cache.slots.held_count == 0 and e.cache.n_slots >= n_slots
+                and e.cache.n_pages * 64 >= n_tokens and e.cache.max_len >= (max_len or self.spec.max_position)):
+            return e
         if self._engine is None or self._engine_key != key:
             self._backend = None
             self._engine = None          # free the old cache before the new one is made
@@ -107,4 +113,4 @@ def generate(llm: LLM, prompt_ids: Sequence[Sequence[int]], max_tokens: int = 51
         return time.perf_counter()
 
     return generate_ids(backend, prompts, max_tokens, params, stops, max_batch=batch, on_token=on_token, stats=stats,
-                        clock=clock if stats is not None else None)
+                        clock=clock if stats is not None else None, context_limit=limit)

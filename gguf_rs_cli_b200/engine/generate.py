@@ -44,10 +44,11 @@ class GenerationStats:
 def generate_ids(backend, prompts: Sequence[Sequence[int]], max_tokens: int, params: SamplingParams = SamplingParams(),
                  stop_token_ids: Sequence[int] = (), max_batch: Optional[int] = None,
                  on_token: Optional[Callable[[int, int], None]] = None,
-                 stats: Optional[GenerationStats] = None, clock: Optional[Callable[[], float]] = None) -> List[List[int]]:
+                 stats: Optional[GenerationStats] = None, clock: Optional[Callable[[], float]] = None,
+                 context_limit: Optional[int] = None) -> List[List[int]]:
     """Returns the generated ids of every prompt, in the order of the prompts.
 
-    backend.context_limit      positions one sequence may hold
+    backend.context_limit      positions one sequence may hold (`context_limit` may lower it)
     backend.admit(lens, n)     how many of the next prompts (lengths `lens`) may start together
                                when each may grow by n tokens; at least 1 or an error
     backend.open() -> slot     backend.close(slot)
@@ -55,7 +56,7 @@ def generate_ids(backend, prompts: Sequence[Sequence[int]], max_tokens: int, par
     """
     params.validate()
     stops = set(int(s) for s in stop_token_ids)
-    ctx = backend.context_limit
+    ctx = backend.context_limit if context_limit is None else min(backend.context_limit, int(context_limit))
     for i, p in enumerate(prompts):
         if len(p) == 0:
             raise GenerationError(f"prompt {i} is empty: a request needs at least one token")

@@ -164,11 +164,23 @@ def library():
     return _lib
 
 
+_launches = 0
+# kernels launched by one call of an entry point, where that is not one
+KERNELS_PER_CALL = {}
+
+
+def launch_count() -> int:
+    """Kernels this process has launched through the library so far."""
+    return _launches
+
+
 def call(name: str, *args) -> None:
     """Calls an entry point; a non-zero return becomes a NativeError with its message."""
+    global _launches
     lib = library()
     if getattr(lib, name)(*args):
         raise NativeError(lib.gb_last_error().decode("utf-8", "replace"))
+    _launches += KERNELS_PER_CALL.get(name, 1)
 
 
 _checked_device = False
