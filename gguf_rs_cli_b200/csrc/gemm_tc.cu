@@ -1,0 +1,359 @@
+// bf16 matrix product on the 5th-generation tensor cores:
+//   out[t,n] = sum_k X[t,k] * W[n,k] (+ bias[n]),  f32 accumulation in TMEM.
+//
+// The weights are the M operand of tcgen05.mma (128 output features per tile), the
+// tokens the N operand (16..256 per tile), so a decode step of a few tokens streams
+// the weights through full 128-row instructions and a prompt of thousands of tokens
+// uses 128x256 tiles; both operands are K-major, as the model folder stores W [out,in]
+// (src/tensor/dequant.rs:258-259) and activations are [tokens, in].
+//
+// One CTA per (feature tile, token tile, K split), 6 warps: warp 0 issues TMA loads of
+// 128-byte-swizzled [rows x 64] bf16 tiles into a ring of shared-memory stages, warp 1
+// owns the TMEM allocation and issues the MMAs (one thread), warps 2..5 read the
+// accumulator back (each its quarter of the 128 lanes) and store.  Out-of-range rows
+// and the K tail are zero-filled by TMA, so any T, any N, and any K that is a multiple
+// of 8 (16-byte row pitch) work; other sizes are refused and the caller falls back to
+// the CUDA-core kernel.
+//
+// With K split over several CTAs (few tiles, as in decode, would leave SMs idle), each
+// split writes its partial tile to scratch memory and bumps the tile's counter; the
+// CTA that arrives last adds all partials in split order and writes the result.
+// Nobody waits for anybody, and the order of the sum does not depend on timing.
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128;       // output features per tile (MMA M)
+constexpr int BK = 64;        // K per stage: one 128-byte swizzled row of bf16
+constexpr int UMMA_K = 16;
+constexpr int TC_THREADS = 192;
+constexpr int A_BYTES = BM * BK * 2;
+
+template <int BN> struct TileCfg {
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;     // + slack to align the ring to 1024 bytes
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+};
+
+struct TcParams {
+    void* out;
+    const void* bias;
+    float* scratch;       // [tiles][splits][BN][128] partial sums, used when splits > 1
+    int* counters;        // [tiles], zero between launches
+    int* status;          // set non-zero when a bounded wait gave up
+    long long ldo;
+    int out_dtype, bias_dtype;
+    int T, N, K, splits;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                const __grid_constant__ CUtensorMap map_x, TcParams p) {
+    using Cfg = TileCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t full_bar[Cfg::STAGES], empty_bar[Cfg::STAGES], acc_bar;
+    __shared__ uint32_t tmem_base;
+    __shared__ int last_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BM, t0 = blockIdx.y * BN, split = blockIdx.z;
+    const int kb_total = (p.K + BK - 1) / BK;
+    const int kb_begin = int((long long)split * kb_total / p.splits);
+    const int kb_end = int((long long)(split + 1) * kb_total / p.splits);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&acc_bar, 1);
+        fence_barrier_init();
+        prefetch_tensormap(&map_w);
+        prefetch_tensormap(&map_x);
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer: TMA loads into the ring
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
+                if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { atomicExch(p.status, 1); break; }
+                uint8_t* a = ring + stage * Cfg::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+                tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[stage]);
+                tma_load_2d(a + A_BYTES, &map_x, kb * BK, t0, &full_bar[stage]);
+                if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issue
+            constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
+                if (!mbar_wait(&full_bar[stage], phase)) { atomicExch(p.status, 2); ok = false; break; }
+                tc_fence_after();
+                uint32_t a = smem_u32(ring + stage * Cfg::STAGE_BYTES);
+                uint32_t b = a + A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    mma_f16(tmem_d, smem_desc_sw128(a + k * UMMA_K * 2), smem_desc_sw128(b + k * UMMA_K * 2), idesc,
+                            (kb > kb_begin || k > 0) ? 1u : 0u);
+                mma_commit(&empty_bar[stage]);      // the stage is free once these MMAs have read it
+                if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
+            }
+            (void)ok;
+            mma_commit(&acc_bar);                   // the accumulator is complete
+        }
+    } else {
+        // ---- epilogue: 4 warps, warp w reads TMEM lanes 32*(w%4) .. +31
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;        // feature within the tile = TMEM lane
+        const int n = n0 + row;
+        const bool waited = mbar_wait(&acc_bar, 0);
+        if (!waited && lane == 0) atomicExch(p.status, 3);
+        tc_fence_after();
+        const uint32_t taddr = tmem_d + (uint32_t(quarter * 32) << 16);
+        const int cols = min(BN, p.T - t0);         // valid tokens of this tile
+        float bias = 0.f;
+        if (p.bias && n < p.N) bias = gb_load(p.bias, p.bias_dtype, n);
+        if (p.splits == 1) {
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (c0 >= cols) break;               // uniform over the warp
+                float v[16];
+                tmem_ld16(taddr + c0, v);
+                if (n < p.N && waited) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j < cols) gb_store(p.out, p.out_dtype, size_t(t0 + c0 + j) * p.ldo + n, v[j] + bias);
+                }
+            }
+        } else {
+            const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+            float* mine = p.scratch + (size_t(tile) * p.splits + split) * (BN * BM);
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (c0 >= cols) break;
+                float v[16];
+                tmem_ld16(taddr + c0, v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (c0 + j < cols) mine[(c0 + j) * BM + row] = v[j];
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) {
+                int old = atomicAdd(&p.counters[tile], 1);
+                last_flag = (old == p.splits - 1);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (last_flag) {
+                __threadfence();
+                const float* base = p.scratch + size_t(tile) * p.splits * (BN * BM);
+                if (n < p.N && waited) {
+                    // 4 columns at a time so that 4 * splits loads are in flight; the sum itself
+                    // runs over the splits in ascending order
+                    for (int c0 = 0; c0 < cols; c0 += 4) {
+                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                        for (int s0 = 0; s0 < p.splits; s0 += 4) {
+                            float v[4][4];
+#pragma unroll
+                            for (int si = 0; si < 4; ++si)
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    v[si][j] = (s0 + si < p.splits && c0 + j < cols)
+                                                   ? __ldcg(base + size_t(s0 + si) * (BN * BM) + (c0 + j) * BM + row)
+                                                   : 0.f;
+#pragma unroll
+                            for (int si = 0; si < 4; ++si)
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) acc[j] += v[si][j];
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (c0 + j < cols) gb_store(p.out, p.out_dtype, size_t(t0 + c0 + j) * p.ldo + n, acc[j] + bias);
+                    }
+                }
+                if (threadIdx.x == 64) p.counters[tile] = 0;       // ready for the next launch
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_d, Cfg::TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(f);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    long long rows, cols, ld;
+    int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.ptr);
+        for (long long v : {k.rows, k.cols, k.ld, (long long)k.box_rows}) h = h * 1000003u ^ std::hash<long long>()(v);
+        return h;
+    }
+};
+
+// Tensor map of a row-major bf16 matrix [rows, cols] with pitch ld, box [box_rows x 64], 128-byte swizzle.
+int tensor_map_2d(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return gb_fail("gb_gemm_tc: the driver gives no cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+    cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
+    cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return gb_fail("gb_gemm_tc: cuTensorMapEncodeTiled failed with code %d", int(r));
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+int* g_status_host = nullptr;
+int* g_status_dev = nullptr;
+
+int ensure_status() {
+    if (g_status_host) return 0;
+    if (cudaHostAlloc(&g_status_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess)
+        return gb_fail("gb_gemm_tc: cannot allocate the status word");
+    *g_status_host = 0;
+    if (cudaHostGetDevicePointer(&g_status_dev, g_status_host, 0) != cudaSuccess)
+        return gb_fail("gb_gemm_tc: cannot map the status word");
+    return 0;
+}
+
+template <int BN>
+int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, cudaStream_t stream) {
+    using Cfg = TileCfg<BN>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
+            return gb_fail("gb_gemm_tc: cannot get %d bytes of shared memory", Cfg::SMEM);
+        configured = true;
+    }
+    dim3 grid((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, p.splits);
+    gemm_tc_kernel<BN><<<grid, TC_THREADS, Cfg::SMEM, stream>>>(mw, mx, p);
+    GB_LAUNCH_OK("gb_gemm_tc");
+    return 0;
+}
+
+}  // namespace
+
+// Tokens per tile for T tokens.
+GB_API int gb_gemm_tc_tile(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
+
+// How many ways the kernel would split K for these sizes on a device with `sms` SMs (1 = no scratch needed).
+GB_API int gb_gemm_tc_splits(int T, int N, int K, int sms) {
+    int bn = gb_gemm_tc_tile(T);
+    long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
+    int kb = (K + BK - 1) / BK;
+    if (tiles >= sms || kb < 8) return 1;
+    int s = int(sms / tiles);
+    if (s > kb / 4) s = kb / 4;       // at least 4 K blocks per split
+    if (s > 16) s = 16;
+    return s < 1 ? 1 : s;
+}
+
+// Floats of scratch a launch with these sizes needs (0 when K is not split).
+GB_API long long gb_gemm_tc_scratch_floats(int T, int N, int K, int sms) {
+    int s = gb_gemm_tc_splits(T, N, K, sms);
+    if (s == 1) return 0;
+    int bn = gb_gemm_tc_tile(T);
+    long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
+    return tiles * s * bn * BM;
+}
+
+// Whether the tensor-core kernel takes these operands (bf16, 16-byte aligned, pitches multiples of 8).
+GB_API int gb_gemm_tc_supported(const void* X, long long ldx, const void* W, long long ldw, int K) {
+    return K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0 &&
+           (reinterpret_cast<uintptr_t>(W) & 15) == 0;
+}
+
+// X: bf16 [T, K] pitch ldx; W: bf16 [N, K] pitch ldw; out: bf16 or f32 [T, N] pitch ldo; bias optional.
+// scratch: gb_gemm_tc_scratch_floats(...) floats; counters: at least as many zeroed ints as tiles
+// (the kernel leaves them zero).  Both may be null when K is not split.
+GB_API int gb_gemm_tc(const void* X, long long ldx, const void* W, long long ldw, const void* bias, int bias_dtype,
+                      void* out, int out_dtype, long long ldo, int T, int N, int K, float* scratch, int* counters,
+                      int n_counters, int sms, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(out_dtype) && (!bias || gb_is_dtype(bias_dtype)), "gb_gemm_tc: bad dtype");
+    GB_REQUIRE(T >= 0 && N > 0 && K > 0 && ldo >= N, "gb_gemm_tc: bad sizes T=%d N=%d K=%d ldo=%lld", T, N, K, ldo);
+    GB_REQUIRE(gb_gemm_tc_supported(X, ldx, W, ldw, K),
+               "gb_gemm_tc: K=%d and the row pitches (%lld, %lld) must be multiples of 8 and the operands 16-byte aligned",
+               K, ldx, ldw);
+    if (T == 0) return 0;
+    if (ensure_status()) return 1;
+    int bn = gb_gemm_tc_tile(T);
+    TcParams p;
+    p.out = out; p.bias = bias; p.scratch = scratch; p.counters = counters; p.status = g_status_dev;
+    p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype; p.T = T; p.N = N; p.K = K;
+    p.splits = (scratch && counters) ? gb_gemm_tc_splits(T, N, K, sms) : 1;
+    long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
+    GB_REQUIRE(p.splits == 1 || tiles <= n_counters, "gb_gemm_tc: %lld tiles need as many counters, %d given", tiles, n_counters);
+    GB_REQUIRE((T + bn - 1) / bn <= 65535, "gb_gemm_tc: T=%d is too many rows for one launch", T);
+    CUtensorMap mw, mx;
+    if (tensor_map_2d(W, N, K, ldw, BM, &mw)) return 1;
+    if (tensor_map_2d(X, T, K, ldx, bn, &mx)) return 1;
+    switch (bn) {
+        case 16: return launch_tc<16>(mw, mx, p, stream);
+        case 32: return launch_tc<32>(mw, mx, p, stream);
+        case 64: return launch_tc<64>(mw, mx, p, stream);
+        case 128: return launch_tc<128>(mw, mx, p, stream);
+        default: return launch_tc<256>(mw, mx, p, stream);
+    }
+}
+
+// Non-zero when a bounded wait inside a tensor-core kernel gave up since the last clear
+// (1: a load stage never came free, 2: a load never arrived, 3: the accumulator never completed).
+// Read after synchronising the stream.
+GB_API int gb_tc_status() { return g_status_host ? *g_status_host : 0; }
+GB_API int gb_tc_status_clear() {
+    if (g_status_host) *g_status_host = 0;
+    return 0;
+}

@@ -56,6 +56,7 @@ class EngineBackend:
         self.sampler.sample(logits, ctx.slots[:n], self._keys_dev[:n], params, self._out_dev)
         self._out_host[:n].copy_(self._out_dev[:n], non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        eng.check()
         self.h2d_bytes += ctx.host["h2d_bytes"] + 8 * n
         self.d2h_bytes += 4 * n
         return self._out_host[:n].tolist()

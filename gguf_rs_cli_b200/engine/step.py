@@ -64,6 +64,12 @@ class Engine:
     def close(self, slot: int) -> None:
         self.cache.close(slot)
 
+    def check(self) -> None:
+        """After a synchronise: raises if a kernel's bounded wait gave up during the steps
+        since the last check."""
+        from .. import kernels
+        kernels.check_tc_status()
+
     # ----------------------------------------------------------------- plan
     def _meta(self, n: int) -> Tuple[torch.Tensor, torch.Tensor]:
         if self._meta_host is None or self._meta_host.numel() < n:

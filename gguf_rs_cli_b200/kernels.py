@@ -108,10 +108,81 @@ def sample(logits: torch.Tensor, slots: torch.Tensor, seeds: torch.Tensor, tempe
     return out
 
 
+class _TcScratch:
+    """Scratch of the tensor-core product's K split, per device: partial tiles and the
+    tiles' arrival counters (zero between launches).  Launches on one stream follow one
+    another, so they can share it."""
+    COUNTERS = 4096
+
+    def __init__(self, device):
+        self.device = device
+        self.sms = native.library().gb_sm_count()
+        self.floats = torch.empty(1 << 20, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(self.COUNTERS, dtype=torch.int32, device=device)
+
+    def ensure(self, n_floats: int) -> None:
+        if n_floats > self.floats.numel():
+            self.floats = torch.empty(int(n_floats * 1.25), dtype=torch.float32, device=self.device)
+
+
+_tc_scratch = {}
+
+
+def tc_scratch(device) -> _TcScratch:
+    key = torch.device(device).index or 0
+    if key not in _tc_scratch:
+        _tc_scratch[key] = _TcScratch(device)
+    return _tc_scratch[key]
+
+
+def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or w.stride(1) != 1:
+        return False
+    return bool(native.library().gb_gemm_tc_supported(ptr(x), x.stride(0), ptr(w), w.stride(0), x.shape[1]))
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+            split_k: bool = True) -> torch.Tensor:
+    """bf16 x bf16 -> f32 accumulate on tcgen05; out bf16 or f32.  Refuses what
+    gemm_tc_supported refuses."""
+    _cuda(x, w, bias, out)
+    T, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (T, N) and out.stride(1) == 1
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    sc = tc_scratch(x.device)
+    scratch = counters = None
+    if split_k:
+        need = native.library().gb_gemm_tc_scratch_floats(T, N, K, sc.sms)
+        if need:
+            sc.ensure(need)
+            scratch, counters = sc.floats, sc.counters
+    call("gb_gemm_tc", ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(bias), 0 if bias is None else dtype_code(bias),
+         ptr(out), dtype_code(out), out.stride(0), T, N, K, ptr(scratch), ptr(counters),
+         0 if counters is None else counters.numel(), sc.sms, stream_ptr())
+    return out
+
+
+def tc_status() -> int:
+    """Non-zero when a bounded wait inside a tensor-core kernel gave up (read after a
+    synchronise)."""
+    return native.library().gb_tc_status()
+
+
+def check_tc_status() -> None:
+    code = tc_status()
+    if code:
+        native.library().gb_tc_status_clear()
+        raise native.NativeError(f"a tensor-core kernel gave up waiting (code {code}: 1 a stage never came free, "
+                                 f"2 a load never arrived, 3 the accumulator never completed); its output is invalid")
+
+
 # ------------------------------------------------------------------ dispatch
 def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
     """The product path of every projection: the tensor-core kernel when dtype and sizes
     fit it, else the CUDA-core kernel."""
+    if gemm_tc_supported(x, w):
+        return gemm_tc(x, w, bias, out)
     return gemm_generic(x, w, bias, out)
 
 

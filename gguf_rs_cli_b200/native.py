@@ -130,7 +130,15 @@ _SIGNATURES = {
     "gb_gemm_generic": [_P, _I, _L, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P],
     "gb_attention_generic": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _F, _P],
     "gb_sample": [_P, _L, _I, _I, _P, _P, _F, _I, _F, _F, _P, _P, _P, _P],
+    "gb_gemm_tc": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _P],
+    "gb_gemm_tc_tile": [_I],
+    "gb_gemm_tc_splits": [_I, _I, _I, _I],
+    "gb_gemm_tc_scratch_floats": [_I, _I, _I, _I],
+    "gb_gemm_tc_supported": [_P, _L, _P, _L, _I],
+    "gb_tc_status": [],
+    "gb_tc_status_clear": [],
 }
+_RESTYPES = {"gb_gemm_tc_scratch_floats": ctypes.c_longlong}
 
 
 def register_signature(name: str, argtypes) -> None:
@@ -159,7 +167,7 @@ def library():
                         fn = getattr(lib, name)
                     except AttributeError:
                         raise NativeError(f"{path} lacks the entry point {name}; rebuild it") from None
-                    fn.argtypes, fn.restype = argtypes, ctypes.c_int
+                    fn.argtypes, fn.restype = argtypes, _RESTYPES.get(name, ctypes.c_int)
                 _lib = lib
     return _lib
 

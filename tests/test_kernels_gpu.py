@@ -1,0 +1,365 @@
+"""Each kernel alone against its plain reference, at sizes other than the tiny models'."""
+import math
+
+import pytest
+import torch
+
+from tests import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+BF, F32 = torch.bfloat16, torch.float32
+
+
+def K():
+    from gguf_rs_cli_b200 import kernels
+    return kernels
+
+
+def rel_err(got, want):
+    got, want = got.float().cpu(), want.float().cpu()
+    assert torch.isfinite(got).all()
+    return float((got - want).abs().max()) / max(float(want.abs().max()), 1e-9)
+
+
+# ------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("dtype", [F32, BF])
+def test_embed(dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(1000, 200, generator=g).to(dtype)
+    toks = torch.randint(0, 1000, (77,), generator=g)
+    out = torch.empty(77, 200, dtype=F32, device=DEV)
+    K().embed(table.to(DEV), toks.to(torch.int32).to(DEV), out)
+    assert torch.equal(out.cpu(), P.embedding(table.float(), toks.tolist()))
+
+
+# ----------------------------------------------------------------- norm + add
+@pytest.mark.parametrize("E", [40, 320, 4096, 5000])
+@pytest.mark.parametrize("dtype", [F32, BF])
+def test_add_rmsnorm(E, dtype):
+    g = torch.Generator().manual_seed(E)
+    T, eps = 9, 3e-4
+    x = torch.randn(T, E, generator=g) * 3
+    w = (1 + 0.3 * torch.randn(E, generator=g)).to(dtype)
+    d1 = torch.randn(T, E, generator=g).to(dtype)
+    d3 = torch.randn(3, T, E, generator=g)
+    tol = 1e-5 if dtype == F32 else 1e-2
+    k = K()
+    # no pending term
+    xd, out = x.to(DEV).clone(), torch.empty(T, E, dtype=dtype, device=DEV)
+    k.add_rmsnorm(xd, None, w.to(DEV), eps, out)
+    assert rel_err(out, P.rmsnorm(x, w.float(), eps)) < tol and torch.equal(xd.cpu(), x)
+    # one pending term of the working dtype: x is updated with the 32-bit sum
+    k.add_rmsnorm(xd, d1.to(DEV), w.to(DEV), eps, out)
+    assert rel_err(out, P.rmsnorm(x + d1.float(), w.float(), eps)) < tol
+    assert torch.allclose(xd.cpu(), x + d1.float(), atol=1e-6)
+    # several 32-bit partial sums, gathered rows, x untouched
+    xd = x.to(DEV).clone()
+    rows = torch.tensor([7, 0, 3], dtype=torch.int32, device=DEV)
+    out3 = torch.empty(3, E, dtype=dtype, device=DEV)
+    k.add_rmsnorm(xd, d3.to(DEV), w.to(DEV), eps, out3, rows=rows, write_x=False)
+    want = P.rmsnorm((x + d3.sum(0))[[7, 0, 3]], w.float(), eps)
+    assert rel_err(out3, want) < tol and torch.equal(xd.cpu(), x)
+
+
+# --------------------------------------------------------------------- swiglu
+@pytest.mark.parametrize("dtype", [F32, BF])
+def test_swiglu(dtype):
+    g = torch.Generator().manual_seed(1)
+    gu = (torch.randn(13, 2 * 520, generator=g) * 4).to(dtype)
+    out = torch.empty(13, 520, dtype=dtype, device=DEV)
+    K().swiglu(gu.to(DEV), out)
+    want = P.silu(gu.float()[:, :520]) * gu.float()[:, 520:]
+    assert rel_err(out, want) < (1e-6 if dtype == F32 else 5e-3)
+
+
+# ---------------------------------------------------------------------- gemms
+SHAPES = [(1, 100, 72), (5, 257, 136), (70, 130, 1000), (129, 64, 24), (33, 300, 200)]
+
+
+@pytest.mark.parametrize("T,N,Kd", SHAPES)
+@pytest.mark.parametrize("xdt,wdt", [(F32, F32), (BF, BF), (BF, F32)])
+def test_gemm_generic(T, N, Kd, xdt, wdt):
+    g = torch.Generator().manual_seed(T * N)
+    x, w = torch.randn(T, Kd, generator=g).to(xdt), (torch.randn(N, Kd, generator=g) * 0.1).to(wdt)
+    b = torch.randn(N, generator=g)
+    out = torch.empty(T, N, dtype=F32, device=DEV)
+    K().gemm_generic(x.to(DEV), w.to(DEV), b.to(DEV), out)
+    assert rel_err(out, P.linear(x.double(), w.double(), b.double())) < 2e-6
+    outb = torch.empty(T, N + 3, dtype=xdt, device=DEV)[:, :N]               # a strided output
+    K().gemm_generic(x.to(DEV), w.to(DEV), None, outb)
+    assert rel_err(outb, P.linear(x.double(), w.double())) < (2e-6 if xdt == F32 else 5e-3)
+
+
+def test_gemm_generic_rows_do_not_depend_on_the_batch():
+    g = torch.Generator().manual_seed(3)
+    x, w = torch.randn(70, 200, generator=g).to(DEV), torch.randn(90, 200, generator=g).to(DEV)
+    whole = torch.empty(70, 90, device=DEV)
+    one = torch.empty(1, 90, device=DEV)
+    K().gemm_generic(x, w, None, whole)
+    K().gemm_generic(x[41:42], w, None, one)
+    assert torch.equal(whole[41], one[0])
+
+
+TC_SHAPES = [(1, 256, 512), (8, 128, 64), (16, 1000, 4096), (33, 300, 200), (64, 520, 320), (100, 136, 72),
+             (129, 6144, 1024), (300, 520, 4096), (700, 257, 328)]
+
+
+@pytest.mark.parametrize("T,N,Kd", TC_SHAPES)
+@pytest.mark.parametrize("out_dtype", [F32, BF])
+def test_gemm_tensor_core(T, N, Kd, out_dtype):
+    k = K()
+    g = torch.Generator().manual_seed(T + N + Kd)
+    x = torch.randn(T, Kd, generator=g).to(BF).to(DEV)
+    w = (torch.randn(N, Kd, generator=g) * 0.1).to(BF).to(DEV)
+    b = torch.randn(N, generator=g).to(DEV)
+    assert k.gemm_tc_supported(x, w)
+    want = P.linear(x.double().cpu(), w.double().cpu(), b.double().cpu())
+    out = torch.full((T, N), float("nan"), dtype=out_dtype, device=DEV)
+    k.gemm_tc(x, w, b, out)
+    torch.cuda.synchronize()
+    k.check_tc_status()
+    assert rel_err(out, want) < (1e-5 if out_dtype == F32 else 5e-3)
+    # the generic kernel is its twin
+    twin = torch.empty(T, N, dtype=F32, device=DEV)
+    k.gemm_generic(x, w, b, twin)
+    assert rel_err(twin, want) < 1e-5
+    # without the K split the result is the same up to the order of the 32-bit sums
+    nosplit = torch.empty(T, N, dtype=F32, device=DEV)
+    k.gemm_tc(x, w, b, nosplit, split_k=False)
+    assert rel_err(nosplit, want) < 1e-5
+    # and twice in a row gives the same bits (the split's counters are left at zero)
+    again = torch.full((T, N), float("nan"), dtype=out_dtype, device=DEV)
+    k.gemm_tc(x, w, b, again)
+    assert torch.equal(again, out)
+
+
+def test_gemm_tensor_core_refuses_what_it_cannot_take():
+    k = K()
+    x = torch.zeros(4, 100, dtype=BF, device=DEV)
+    w = torch.zeros(8, 100, dtype=BF, device=DEV)
+    assert not k.gemm_tc_supported(x, w)                        # K = 100 is no multiple of 8
+    assert not k.gemm_tc_supported(x.float(), w.float())
+    from gguf_rs_cli_b200.native import NativeError
+    with pytest.raises(NativeError, match="multiples of 8"):
+        k.gemm_tc(x, w, None, torch.empty(4, 8, dtype=BF, device=DEV))
+    out = torch.empty(4, 8, dtype=BF, device=DEV)
+    k.gemm(x, w, None, out)                                     # the dispatcher takes the other kernel
+    assert torch.equal(out.cpu(), torch.zeros(4, 8, dtype=BF))
+
+
+# ------------------------------------------------- rotation, cache, attention
+def make_cache(n_pages, nkv, hd, dtype):
+    return (torch.full((n_pages, nkv, 64, hd), float("nan"), dtype=dtype, device=DEV),
+            torch.full((n_pages, nkv, 64, hd), float("nan"), dtype=dtype, device=DEV))
+
+
+def page_layout(lens, n_pages, seed=0):
+    """A scattered page table for sequences of these lengths."""
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max((n + 63) // 64 for n in lens)
+    rows, nxt = [], 0
+    for n in lens:
+        k = (n + 63) // 64
+        rows.append(perm[nxt:nxt + k] + [0] * (width - k))
+        nxt += k
+    return torch.tensor(rows, dtype=torch.int32, device=DEV)
+
+
+def read_cache(cache, table_row, n):
+    out = []
+    for p in range(n):
+        out.append(cache[int(table_row[p // 64]), :, p % 64, :])
+    return torch.stack(out).float().cpu()          # [n, nkv, hd]
+
+
+@pytest.mark.parametrize("dtype", [F32, BF])
+@pytest.mark.parametrize("nh,nkv,hd,rot,pairing", [(6, 3, 32, 32, 0), (4, 1, 48, 48, 0), (8, 8, 16, 8, 0), (2, 2, 64, 64, 1)])
+def test_rope_and_cache_write(dtype, nh, nkv, hd, rot, pairing):
+    k = K()
+    g = torch.Generator().manual_seed(nh * hd)
+    lens, starts = [70, 5, 130], [3, 0, 64]                # new tokens and where each sequence stands
+    T = sum(lens)
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, width, generator=g).to(dtype)
+    cfg = {"hidden_size": nh * rot, "num_attention_heads": nh, "head_dim": rot, "rope_theta": 50000.0}
+    inv = P.inv_freq_table(cfg)
+    seq_of = torch.tensor(sum(([b] * n for b, n in enumerate(lens)), []), dtype=torch.int32)
+    pos = torch.tensor(sum((list(range(s, s + n)) for s, n in zip(starts, lens)), []), dtype=torch.int32)
+    table = page_layout([s + n for s, n in zip(starts, lens)], 16)
+    kc, vc = make_cache(16, nkv, hd, dtype)
+    d = qkv.to(DEV).clone()
+    q, kk, vv = d[:, :nh * hd], d[:, nh * hd:(nh + nkv) * hd], d[:, (nh + nkv) * hd:]
+    k.rope_kv_write(q, kk, vv, nh, nkv, hd, inv.to(DEV), rot, pairing, seq_of.to(DEV), pos.to(DEV), table, 1 << 20, kc, vc)
+
+    def plain_rot(x, heads):
+        x = x.float().reshape(T, heads, hd)
+        r = x[..., :rot]
+        if pairing:
+            r = torch.cat([r[..., 0::2], r[..., 1::2]], -1)
+        r = P.rope(r, pos, inv)
+        if pairing:
+            out = torch.empty_like(r)
+            out[..., 0::2], out[..., 1::2] = r[..., :rot // 2], r[..., rot // 2:]
+            r = out
+        return torch.cat([r, x[..., rot:]], -1)
+
+    tol = 1e-5 if dtype == F32 else 1e-2
+    assert rel_err(q.reshape(T, nh, hd), plain_rot(qkv[:, :nh * hd], nh)) < tol
+    want_k, want_v = plain_rot(qkv[:, nh * hd:(nh + nkv) * hd], nkv), qkv[:, (nh + nkv) * hd:].float().reshape(T, nkv, hd)
+    t0 = 0
+    for b, (s, n) in enumerate(zip(starts, lens)):
+        got_k, got_v = read_cache(kc, table[b].cpu(), s + n)[s:], read_cache(vc, table[b].cpu(), s + n)[s:]
+        assert rel_err(got_k, want_k[t0:t0 + n]) < tol, f"keys of sequence {b}"
+        assert torch.equal(got_v, want_v[t0:t0 + n].to(dtype).float()), f"values of sequence {b}"
+        t0 += n
+    # nothing else was written: pages not in the tables are still untouched
+    used = set(table.cpu().flatten().tolist())
+    for pg in range(16):
+        if pg not in used:
+            assert torch.isnan(kc[pg].float()).all()
+
+
+def fill_cache(kseqs, vseqs, nkv, hd, dtype, n_pages=64, seed=0):
+    lens = [k.shape[0] for k in kseqs]
+    table = page_layout(lens, n_pages, seed)
+    kc, vc = make_cache(n_pages, nkv, hd, dtype)
+    for b, (ks, vs) in enumerate(zip(kseqs, vseqs)):
+        for p in range(ks.shape[0]):
+            pg = int(table[b, p // 64])
+            kc[pg, :, p % 64, :] = ks[p].to(dtype).to(DEV)
+            vc[pg, :, p % 64, :] = vs[p].to(dtype).to(DEV)
+    return table, kc, vc
+
+
+def attention_case(nh, nkv, hd, lens, qlens, dtype, seed, window=None, boost=None):
+    """Random q/k/v for sequences of `lens`, the last qlens[b] positions being this step's
+    queries.  boost=(b, key position, head): that query/key pair gets a large score."""
+    g = torch.Generator().manual_seed(seed)
+    qs = [torch.randn(n, nh, hd, generator=g) for n in lens]
+    ks = [torch.randn(n, nkv, hd, generator=g) for n in lens]
+    vs = [torch.randn(n, nkv, hd, generator=g) for n in lens]
+    if boost:
+        b, kp, h = boost
+        ks[b][kp, h // (nh // nkv)] = qs[b][-1, h] * 3.0        # the last query finds this far key
+    qs = [x.to(dtype).float() for x in qs]
+    ks = [x.to(dtype).float() for x in ks]
+    vs = [x.to(dtype).float() for x in vs]
+    want = torch.cat([P.attention(q, k, v, window=window)[n - ql:] for q, k, v, n, ql in zip(qs, ks, vs, lens, qlens)])
+    q = torch.cat([q[n - ql:] for q, n, ql in zip(qs, lens, qlens)]).reshape(-1, nh * hd).to(dtype).to(DEV)
+    seq_of = torch.tensor(sum(([b] * ql for b, ql in enumerate(qlens)), []), dtype=torch.int32, device=DEV)
+    pos = torch.tensor(sum((list(range(n - ql, n)) for n, ql in zip(lens, qlens)), []), dtype=torch.int32, device=DEV)
+    table, kc, vc = fill_cache(ks, vs, nkv, hd, dtype, seed=seed)
+    return q, seq_of, pos, table, kc, vc, want
+
+
+ATT_SHAPES = [(6, 3, 32), (4, 1, 48), (8, 8, 16), (8, 2, 128), (5, 5, 80)]
+
+
+@pytest.mark.parametrize("dtype", [F32, BF])
+@pytest.mark.parametrize("nh,nkv,hd", ATT_SHAPES)
+def test_attention_generic(dtype, nh, nkv, hd):
+    k = K()
+    lens, qlens = [200, 1, 65, 130], [200, 1, 1, 40]           # whole prompt, first token, decode, continuation
+    q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, qlens, dtype, seed=hd)
+    out = torch.empty(q.shape[0], nh * hd, dtype=dtype, device=DEV)
+    k.attention_generic(q, out, nh, nkv, hd, seq_of, pos, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd))
+    assert rel_err(out, want) < (2e-5 if dtype == F32 else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF])
+def test_attention_generic_finds_a_far_key_and_respects_a_window(dtype):
+    k = K()
+    nh, nkv, hd = 4, 2, 32
+    lens, qlens = [700, 300], [1, 1]
+    q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, qlens, dtype, 5, boost=(0, 3, 2))
+    out = torch.empty(2, nh * hd, dtype=dtype, device=DEV)
+    k.attention_generic(q, out, nh, nkv, hd, seq_of, pos, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd))
+    assert rel_err(out, want) < (2e-5 if dtype == F32 else 1e-2)
+    # the boosted head's output is (nearly) the far key's value: a kernel that skipped position 3 fails
+    q2, seq_of, pos, table, kc, vc, want_w = attention_case(nh, nkv, hd, lens, qlens, dtype, 5, window=100, boost=(0, 3, 2))
+    k.attention_generic(q2, out, nh, nkv, hd, seq_of, pos, table, 1 << 20, kc, vc, 100, 1 / math.sqrt(hd))
+    assert rel_err(out, want_w) < (2e-5 if dtype == F32 else 1e-2)
+    assert rel_err(want_w, want) > 0.05                        # the window hides the far key
+    # window edge: exactly W keys are seen
+    for W in (1, 64, 65):
+        _, _, _, _, _, _, ww = attention_case(nh, nkv, hd, lens, qlens, dtype, 5, window=W)
+        k.attention_generic(q2, out, nh, nkv, hd, seq_of, pos, table, 1 << 20, kc, vc, W, 1 / math.sqrt(hd))
+        assert rel_err(out, ww) < (2e-5 if dtype == F32 else 1e-2), f"window {W}"
+
+
+def test_attention_padding_tokens_give_zeros():
+    k = K()
+    nh, nkv, hd = 4, 2, 32
+    q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, [70, 3], [1, 1], F32, 9)
+    q = torch.cat([q, torch.randn(2, nh * hd, device=DEV)])
+    seq_of = torch.cat([seq_of, torch.tensor([-1, -1], dtype=torch.int32, device=DEV)])
+    pos = torch.cat([pos, torch.zeros(2, dtype=torch.int32, device=DEV)])
+    out = torch.full((4, nh * hd), float("nan"), device=DEV)
+    k.attention_generic(q, out, nh, nkv, hd, seq_of, pos, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd))
+    assert rel_err(out[:2], want) < 2e-5 and torch.equal(out[2:].cpu(), torch.zeros(2, nh * hd))
+
+
+# ------------------------------------------------------------------- sampling
+def run_sample(logits, slots, keys, temperature, top_k, top_p, rep, recent, count):
+    n = logits.shape[0]
+    out = torch.zeros(n, dtype=torch.int32, device=DEV)
+    K().sample(logits, slots, keys, temperature, top_k, top_p, rep, recent, count, out)
+    return out.cpu().tolist()
+
+
+@pytest.mark.parametrize("V", [384, 5003, 128256])
+def test_sampling_matches_the_plain_sampler(V):
+    from gguf_rs_cli_b200.sampling import stream_key
+    g = torch.Generator().manual_seed(V)
+    n_slots = 8
+    slots = [6, 0, 3, 7, 2]
+    settings = [(0.0, 0, 1.0, 1.0), (0.8, 0, 1.0, 1.0), (1.3, 40, 1.0, 1.0), (0.7, 0, 0.9, 1.0), (0.7, 40, 0.9, 1.1),
+                (1.0, 3, 0.5, 1.3), (2.0, V + 5, 0.99, 1.0)]
+    steps = 4
+    if V > 100000:                                  # the plain sampler sorts in Python: keep the big case short
+        slots, settings, steps = slots[:2], [settings[1], settings[4]], 2
+    n = len(slots)
+    for temperature, top_k, top_p, rep in settings:
+        recent = torch.zeros(n_slots, 64, dtype=torch.int32, device=DEV)
+        count = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+        hist = {s: [] for s in slots}
+        keys = [stream_key(11, i) for i in range(n)]
+        for step in range(steps):
+            logits = (torch.randn(n, V, generator=g) * 3).to(DEV)
+            logits[0, 5] = logits[0, 17] = logits[0].max() + 1           # equal maxima: the lower index wins
+            ref = logits.cpu().clone()
+            got = run_sample(logits, torch.tensor(slots, dtype=torch.int32, device=DEV),
+                             torch.tensor(keys, dtype=torch.int64, device=DEV), temperature, top_k, top_p, rep, recent, count)
+            for i, s in enumerate(slots):
+                u = P.uniform(keys[i] & P.MASK64, len(hist[s]))
+                want = P.sample(ref[i], temperature, top_k, top_p, rep, hist[s][-64:], u)
+                assert got[i] == want, f"V={V} T={temperature} k={top_k} p={top_p} rep={rep} step {step} row {i}"
+                hist[s].append(got[i])
+        assert count.cpu().tolist() == [steps if s in slots else 0 for s in range(n_slots)]
+
+
+def test_sampling_ring_and_padding():
+    V, n_slots = 50, 2
+    recent = torch.zeros(n_slots, 64, dtype=torch.int32, device=DEV)
+    count = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([1, -1], dtype=torch.int32, device=DEV)
+    keys = torch.zeros(2, dtype=torch.int64, device=DEV)
+    seen = []
+    for step in range(70):
+        logits = torch.zeros(2, V, device=DEV)
+        logits[0, step % V] = 5.0
+        seen.append(run_sample(logits, slots, keys, 0.0, 0, 1.0, 1.0, recent, count)[0])
+    assert seen == [s % V for s in range(70)]
+    assert count.cpu().tolist() == [0, 70]
+    ring = recent[1].cpu().tolist()
+    assert sorted(ring) == sorted(seen[-64:]) and recent[0].abs().sum() == 0
+    # the penalty is applied once per occurrence and turns the choice
+    logits = torch.zeros(1, V, device=DEV)
+    logits[0, 19], logits[0, 40] = 5.0, 2.0                          # 19 is in the ring twice (5/2/2 < 2/2 fails: 1.25 > 1)
+    logits[0, 45] = 1.2                                              # 45 is in the ring once: 0.6
+    ref = logits.cpu()[0].clone()
+    got = run_sample(logits, torch.tensor([1], dtype=torch.int32, device=DEV), keys[:1], 0.0, 0, 1.0, 2.0, recent, count)[0]
+    want = P.sample(ref, 0.0, 0, 1.0, 2.0, seen[-64:], 0.0)
+    assert got == want == 19 and seen[-64:].count(19) == 2 and seen[-64:].count(40) == 1
