@@ -109,9 +109,10 @@ def sample(logits: torch.Tensor, slots: torch.Tensor, seeds: torch.Tensor, tempe
 
 
 class _TcScratch:
-    """Scratch of the tensor-core product's K split, per device: partial tiles and the
-    tiles' arrival counters (zero between launches).  Launches on one stream follow one
-    another, so they can share it."""
+    """Scratch of the kernels that split their work and merge it without waiting (the
+    tensor-core product's K split, decode attention's page split), per device: partial
+    results and arrival counters (zero between launches).  Launches on one stream follow
+    one another, so they can share it."""
     COUNTERS = 4096
 
     def __init__(self, device):
@@ -163,6 +164,37 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
     return out
 
 
+def attention_decode_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> bool:
+    return bool(native.library().gb_attention_decode_supported(head_dim, dtype_code(kcache), dtype_code(q)))
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                     seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, ring_pages: int,
+                     kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float,
+                     splits: Optional[int] = None) -> torch.Tensor:
+    """One token per sequence over the bf16 cache; all heads of a group share one pass over
+    the keys and values."""
+    _cuda(q, out, seq_of, pos, table, kcache, vcache)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, n_heads * head_dim)
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
+    lib = native.library()
+    sc = tc_scratch(q.device)
+    if splits is None:
+        splits = lib.gb_attention_decode_splits(T, n_heads, n_kv_heads, sc.sms, table.shape[1])
+    need = lib.gb_attention_decode_scratch_floats(T, n_heads, head_dim, splits)
+    scratch = counters = None
+    if need:
+        sc.ensure(need)
+        scratch, counters = sc.floats, sc.counters
+        if T * n_heads > sc.COUNTERS:
+            splits, scratch, counters = 1, None, None
+    call("gb_attention_decode", ptr(q), q.stride(0), ptr(out), out.stride(0), T, n_heads, n_kv_heads, head_dim,
+         ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(kcache), ptr(vcache), int(window or 0),
+         float(scale), splits, ptr(scratch), ptr(counters), 0 if counters is None else counters.numel(), stream_ptr())
+    return out
+
+
 def tc_status() -> int:
     """Non-zero when a bounded wait inside a tensor-core kernel gave up (read after a
     synchronise)."""
@@ -189,5 +221,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: to
 def attention(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, ctx, table: torch.Tensor,
               ring_pages: int, kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float) -> torch.Tensor:
     """Attention of one step over the cache; picks the kernel for the step's shape."""
+    if ctx.decode and attention_decode_supported(q, kcache, head_dim):
+        return attention_decode(q, out, n_heads, n_kv_heads, head_dim, ctx.seq_of, ctx.pos, table, ring_pages, kcache,
+                                vcache, window, scale)
     return attention_generic(q, out, n_heads, n_kv_heads, head_dim, ctx.seq_of, ctx.pos, table, ring_pages, kcache,
                              vcache, window, scale)

@@ -135,10 +135,14 @@ _SIGNATURES = {
     "gb_gemm_tc_splits": [_I, _I, _I, _I],
     "gb_gemm_tc_scratch_floats": [_I, _I, _I, _I],
     "gb_gemm_tc_supported": [_P, _L, _P, _L, _I],
+    "gb_attention_decode": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P],
+    "gb_attention_decode_splits": [_I, _I, _I, _I, _I],
+    "gb_attention_decode_scratch_floats": [_I, _I, _I, _I],
+    "gb_attention_decode_supported": [_I, _I, _I],
     "gb_tc_status": [],
     "gb_tc_status_clear": [],
 }
-_RESTYPES = {"gb_gemm_tc_scratch_floats": ctypes.c_longlong}
+_RESTYPES = {"gb_gemm_tc_scratch_floats": ctypes.c_longlong, "gb_attention_decode_scratch_floats": ctypes.c_longlong}
 
 
 def register_signature(name: str, argtypes) -> None:
