@@ -78,11 +78,18 @@ class Engine:
             self._meta_dev = torch.empty(size, dtype=torch.int32, device=self.device)
         return self._meta_host, self._meta_dev
 
-    def plan(self, entries: Sequence[Entry], pad_to: Optional[int] = None,
-             full_tables: bool = False) -> Tuple[StepContext, torch.Tensor, int]:
+    def meta_size(self, batch: int) -> int:
+        """int32 words of index arrays for a padded batch of single tokens with full tables."""
+        return 8 * batch + 1 + batch * sum(g.table_width for g in self.cache.groups)
+
+    def plan(self, entries: Sequence[Entry], pad_to: Optional[int] = None, full_tables: bool = False,
+             want_all: bool = False, meta: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+             ) -> Tuple[StepContext, torch.Tensor, int]:
         """Checks the entries, reserves cache room and ships the step's index arrays to the
         device in one copy.  pad_to pads a batch of single tokens with entries that change
-        nothing.  Returns (context, wanted rows, number of wanted rows)."""
+        nothing; full_tables, want_all (every row, padding too) and meta (pinned host and
+        device buffers to use) give the arrays the same layout and addresses every step, as
+        a captured graph needs.  Returns (context, wanted rows, number of wanted rows)."""
         if not entries:
             raise StepError("a step needs at least one entry")
         V = self.vocab_size
@@ -123,6 +130,8 @@ class Engine:
         slots_p = slots + [-1] * padB
         starts_p = starts + [0] * padB
         qlens_p = qlens + [0] * padB
+        if want_all:
+            want = list(range(Tp))
         flat = tokens + seq_of + pos + slots_p + starts_p + qlens_p + cu + want
         offs, o = {}, 0
         for name, n in (("tokens", Tp), ("seq_of", Tp), ("pos", Tp), ("slots", Bp), ("starts", Bp), ("qlens", Bp),
@@ -139,7 +148,9 @@ class Engine:
             table_offs.append((len(flat), Bp, width))
             for r in rows:
                 flat += r
-        host, dev = self._meta(len(flat))
+        host, dev = meta if meta is not None else self._meta(len(flat))
+        if len(flat) > host.numel():
+            raise StepError(f"the step's index arrays ({len(flat)} words) exceed the buffer given ({host.numel()})")
         host[:len(flat)] = torch.tensor(flat, dtype=torch.int32)
         dev[:len(flat)].copy_(host[:len(flat)], non_blocking=True)
 
