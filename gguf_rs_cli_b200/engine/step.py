@@ -15,7 +15,7 @@ from typing import List, Optional, Sequence, Tuple
 
 import torch
 
-from .. import native
+from .. import kernels, native
 from ..cache.cache import Cache
 from ..models.decoder import Decoder
 from ..parts.base import StepContext, Workspace
@@ -67,7 +67,6 @@ class Engine:
     def check(self) -> None:
         """After a synchronise: raises if a kernel's bounded wait gave up during the steps
         since the last check."""
-        from .. import kernels
         kernels.check_tc_status()
 
     # ----------------------------------------------------------------- plan
@@ -132,10 +131,11 @@ class Engine:
         qlens_p = qlens + [0] * padB
         if want_all:
             want = list(range(Tp))
-        flat = tokens + seq_of + pos + slots_p + starts_p + qlens_p + cu + want
+        tiles = [] if max(qlens) == 1 else kernels.attention_prefill_tiles(qlens)
+        flat = tokens + seq_of + pos + slots_p + starts_p + qlens_p + cu + want + tiles
         offs, o = {}, 0
         for name, n in (("tokens", Tp), ("seq_of", Tp), ("pos", Tp), ("slots", Bp), ("starts", Bp), ("qlens", Bp),
-                        ("cu", Bp + 1), ("want", len(want))):
+                        ("cu", Bp + 1), ("want", len(want)), ("tiles", len(tiles))):
             offs[name] = (o, n)
             o += n
         table_offs = []
@@ -163,7 +163,8 @@ class Engine:
             slots=view("slots"), starts=view("starts"), qlens=view("qlens"), cu=view("cu"),
             tables=[dev[a:a + b * w].view(b, w) for a, b, w in table_offs], cache=self.cache, ws=self.ws,
             decode=max(qlens) == 1, max_qlen=max(qlens), max_kv=max_kv,
-            host={"slots": slots, "starts": starts, "qlens": qlens, "h2d_bytes": 4 * len(flat)})
+            host={"slots": slots, "starts": starts, "qlens": qlens, "h2d_bytes": 4 * len(flat)},
+            tiles=view("tiles").view(-1, 2) if tiles else None)
         return ctx, view("want"), len(want)
 
     # ----------------------------------------------------------------- step

@@ -195,6 +195,35 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_head
     return out
 
 
+def attention_prefill_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> bool:
+    return bool(native.library().gb_attention_prefill_supported(head_dim, dtype_code(kcache), dtype_code(q)))
+
+
+def attention_prefill_tiles(qlens) -> list:
+    """(sequence row, first query) of every tile of queries, flat, for the step's sequences."""
+    bm = native.library().gb_attention_prefill_tile()
+    flat = []
+    for b, n in enumerate(qlens):
+        for q0 in range(0, n, bm):
+            flat += [b, q0]
+    return flat
+
+
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                      tiles: torch.Tensor, cu: torch.Tensor, starts: torch.Tensor, qlens: torch.Tensor,
+                      table: torch.Tensor, ring_pages: int, kcache: torch.Tensor, vcache: torch.Tensor, window: int,
+                      scale: float) -> torch.Tensor:
+    """Many tokens per sequence over the bf16 cache (which already holds their keys and
+    values), flash style on mma.sync."""
+    _cuda(q, out, tiles, cu, starts, qlens, table, kcache, vcache)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (q.shape[0], n_heads * head_dim)
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
+    call("gb_attention_prefill", ptr(q), q.stride(0), ptr(out), out.stride(0), n_heads, n_kv_heads, head_dim, ptr(tiles),
+         tiles.numel() // 2, ptr(cu), ptr(starts), ptr(qlens), ptr(table), table.shape[1], ring_pages, ptr(kcache),
+         ptr(vcache), int(window or 0), float(scale), stream_ptr())
+    return out
+
+
 def tc_status() -> int:
     """Non-zero when a bounded wait inside a tensor-core kernel gave up (read after a
     synchronise)."""
@@ -224,5 +253,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int,
     if ctx.decode and attention_decode_supported(q, kcache, head_dim):
         return attention_decode(q, out, n_heads, n_kv_heads, head_dim, ctx.seq_of, ctx.pos, table, ring_pages, kcache,
                                 vcache, window, scale)
+    if not ctx.decode and ctx.tiles is not None and attention_prefill_supported(q, kcache, head_dim):
+        return attention_prefill(q, out, n_heads, n_kv_heads, head_dim, ctx.tiles, ctx.cu, ctx.starts, ctx.qlens, table,
+                                 ring_pages, kcache, vcache, window, scale)
     return attention_generic(q, out, n_heads, n_kv_heads, head_dim, ctx.seq_of, ctx.pos, table, ring_pages, kcache,
                              vcache, window, scale)

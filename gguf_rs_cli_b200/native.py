@@ -139,6 +139,9 @@ _SIGNATURES = {
     "gb_attention_decode_splits": [_I, _I, _I, _I, _I],
     "gb_attention_decode_scratch_floats": [_I, _I, _I, _I],
     "gb_attention_decode_supported": [_I, _I, _I],
+    "gb_attention_prefill": [_P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _P],
+    "gb_attention_prefill_supported": [_I, _I, _I],
+    "gb_attention_prefill_tile": [],
     "gb_tc_status": [],
     "gb_tc_status_clear": [],
 }

@@ -98,6 +98,7 @@ class StepContext:
     max_qlen: int
     max_kv: int                   # longest cached length after this step
     host: Dict = field(default_factory=dict)    # host copies for parts that plan on the host
+    tiles: Optional[torch.Tensor] = None        # int32 [n, 2] (sequence row, first query) per tile of queries; prompts only
 
     def state(self, name: str) -> torch.Tensor:
         """Fixed-size per-sequence state [slots, ...]; index it with ctx.slots."""
