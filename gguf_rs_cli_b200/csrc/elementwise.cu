@@ -34,10 +34,87 @@ GB_API int gb_embed(const void* table, int table_dtype, const int* tokens, int T
 // For each output row r (source row s = rows ? rows[r] : r):
 //   v = x[s,:] + sum_d delta[d][s,:]            (32-bit sum; written back to x when write_x)
 //   out[r,:] = v / sqrt(mean(v^2) + eps) * w
+// Each thread keeps its share of the row in registers (4 consecutive elements at a time, up
+// to NORM_MAX_VEC such groups), so the row is read once; rows too long for that, or not a
+// multiple of 4, take the two-pass loop below.
+constexpr int NORM_THREADS = 512;
+constexpr int NORM_MAX_VEC = 8;          // 512 threads * 8 groups * 4 = rows up to 16384 elements
+
+__device__ __forceinline__ float4 load4(const void* p, int dtype, size_t i) {
+    if (dtype == GB_F32) return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+    uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+    float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&raw.x));
+    float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(void* p, int dtype, size_t i, float4 v) {
+    if (dtype == GB_F32) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + i) = v;
+    } else {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<unsigned*>(&a);
+        raw.y = *reinterpret_cast<unsigned*>(&b);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p) + i) = raw;
+    }
+}
+
+__device__ __forceinline__ float block_total(float v, float* red) {
+    v = gb_warp_sum(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) t += red[w];
+    return t;
+}
+
+template <int NV>
+__global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_vec_kernel(
+    float* __restrict__ x, const void* __restrict__ delta, int delta_dtype, int n_delta, size_t delta_stride,
+    const int* __restrict__ rows, int E, const void* __restrict__ w, int w_dtype, float eps, void* __restrict__ out,
+    int out_dtype, int write_x) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    const size_t base = size_t(s) * E;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        int i = (j * NORM_THREADS + threadIdx.x) * 4;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < E) v[j] = *reinterpret_cast<const float4*>(x + base + i);
+    }
+    for (int d = 0; d < n_delta; ++d) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            int i = (j * NORM_THREADS + threadIdx.x) * 4;
+            if (i < E) {
+                float4 t = load4(delta, delta_dtype, d * delta_stride + base + i);
+                v[j].x += t.x; v[j].y += t.y; v[j].z += t.z; v[j].w += t.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+    const float rms = sqrtf(block_total(ss, red) / float(E) + eps);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        int i = (j * NORM_THREADS + threadIdx.x) * 4;
+        if (i < E) {
+            if (write_x && n_delta) *reinterpret_cast<float4*>(x + base + i) = v[j];
+            float4 wv = load4(w, w_dtype, i);
+            store4(out, out_dtype, size_t(r) * E + i,
+                   make_float4(v[j].x / rms * wv.x, v[j].y / rms * wv.y, v[j].z / rms * wv.z, v[j].w / rms * wv.w));
+        }
+    }
+}
+
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ delta, int delta_dtype, int n_delta,
                                    size_t delta_stride, const int* __restrict__ rows, int E,
                                    const void* __restrict__ w, int w_dtype, float eps, void* __restrict__ out,
                                    int out_dtype, int write_x) {
+    __shared__ float red[32];
     int r = blockIdx.x;
     int s = rows ? rows[r] : r;
     float* xr = x + size_t(s) * E;
@@ -48,18 +125,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
         if (write_x) xr[i] = v;
         ss += v * v;
     }
-    __shared__ float red[32];
-    __shared__ float total;
-    ss = gb_warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
-        v = gb_warp_sum(v);
-        if (threadIdx.x == 0) total = v;
-    }
-    __syncthreads();
-    float rms = sqrtf(total / float(E) + eps);
+    float rms = sqrtf(block_total(ss, red) / float(E) + eps);
     for (int i = threadIdx.x; i < E; i += blockDim.x) {
         float v = xr[i];
         if (!write_x)
@@ -75,18 +141,34 @@ GB_API int gb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_de
     GB_REQUIRE(n_delta == 0 || (delta && gb_is_dtype(delta_dtype)), "gb_add_rmsnorm: bad delta");
     GB_REQUIRE(E > 0 && n_rows >= 0 && eps > 0.f, "gb_add_rmsnorm: bad sizes E=%d rows=%d eps=%g", E, n_rows, eps);
     if (n_rows == 0) return 0;
-    int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
-    add_rmsnorm_kernel<<<n_rows, threads, 0, stream>>>(x, delta, delta_dtype, n_delta, size_t(delta_stride), rows, E, w,
-                                                       w_dtype, eps, out, out_dtype, write_x);
+    auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    bool vec = E % 4 == 0 && E <= NORM_THREADS * NORM_MAX_VEC * 4 && aligned(x) && aligned(out) && aligned(w) &&
+               (n_delta == 0 || (aligned(delta) && delta_stride % 4 == 0));
+#define NORM_LAUNCH(NV)                                                                                               \
+    add_rmsnorm_vec_kernel<NV><<<n_rows, NORM_THREADS, 0, stream>>>(x, delta, delta_dtype, n_delta, size_t(delta_stride), \
+                                                                     rows, E, w, w_dtype, eps, out, out_dtype, write_x)
+    if (vec) {
+        int groups = (E / 4 + NORM_THREADS - 1) / NORM_THREADS;
+        if (groups <= 1) NORM_LAUNCH(1);
+        else if (groups <= 2) NORM_LAUNCH(2);
+        else if (groups <= 4) NORM_LAUNCH(4);
+        else NORM_LAUNCH(8);
+    } else {
+        int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
+        add_rmsnorm_kernel<<<n_rows, threads, 0, stream>>>(x, delta, delta_dtype, n_delta, size_t(delta_stride), rows, E, w,
+                                                           w_dtype, eps, out, out_dtype, write_x);
+    }
+#undef NORM_LAUNCH
     GB_LAUNCH_OK("gb_add_rmsnorm");
     return 0;
 }
 
 // ------------------------------------------------ rotation + cache write
-// One block per token.  q is rotated in place; k is rotated and written to the cache; v
-// is copied to the cache.  Angles are position * inv_freq[i] in 32-bit with the
-// accurate sincosf.  pairing 0: (i, i + rot/2); pairing 1: (2i, 2i+1).  Dimensions
-// beyond rotary_dim pass through.  Tokens of padding (seq_of < 0) are skipped.
+// One block per (token, head): the first nh blocks of a token rotate its q heads in place,
+// the next nkv rotate a k head into the cache, the last nkv copy a v head into the cache.
+// Each thread handles one pair (or two plain elements).  Angles are position * inv_freq[i]
+// in 32-bit with the accurate sincosf.  pairing 0: (i, i + rot/2); pairing 1: (2i, 2i+1).
+// Dimensions beyond rotary_dim pass through.  Tokens of padding (seq_of < 0) are skipped.
 constexpr int ROPE_MAX_HALF = 256;
 
 __global__ void rope_kv_write_kernel(void* __restrict__ q, const void* __restrict__ k, const void* __restrict__ v,
@@ -95,50 +177,51 @@ __global__ void rope_kv_write_kernel(void* __restrict__ q, const void* __restric
                                      const int* __restrict__ pos, const int* __restrict__ table, int table_width,
                                      int ring_pages, void* __restrict__ kcache, void* __restrict__ vcache,
                                      int cache_dtype) {
-    int t = blockIdx.x;
-    int b = seq_of[t];
+    const int t = blockIdx.x, head = blockIdx.y;
+    const int b = seq_of[t];
     if (b < 0) return;
-    int p = pos[t];
-    int half = inv_freq ? rotary_dim / 2 : 0;
-    __shared__ float sn[ROPE_MAX_HALF], cs[ROPE_MAX_HALF];
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        float ang = float(p) * inv_freq[i];
-        sincosf(ang, &sn[i], &cs[i]);
-    }
-    __syncthreads();
-    size_t row = size_t(t) * size_t(ld);
-    if (q) {
-        for (int idx = threadIdx.x; idx < nh * half; idx += blockDim.x) {
-            int h = idx / half, i = idx - h * half;
-            int d0 = pairing ? 2 * i : i, d1 = pairing ? 2 * i + 1 : i + half;
-            size_t o = row + size_t(h) * hd;
-            float x0 = gb_load(q, dtype, o + d0), x1 = gb_load(q, dtype, o + d1);
-            gb_store(q, dtype, o + d0, x0 * cs[i] - x1 * sn[i]);
-            gb_store(q, dtype, o + d1, x0 * sn[i] + x1 * cs[i]);
-        }
+    const int p = pos[t];
+    const int half = inv_freq ? rotary_dim / 2 : 0;
+    const size_t row = size_t(t) * size_t(ld);
+    const int i = threadIdx.x;                         // pair index, or element pair index beyond the rotation
+    const int pairs = hd / 2;
+    if (i >= pairs) return;
+    if (head < nh) {
+        if (!q || i >= half) return;                   // q's unrotated dimensions stay as they are
+        float sn, cs;
+        sincosf(float(p) * inv_freq[i], &sn, &cs);
+        const int d0 = pairing ? 2 * i : i, d1 = pairing ? 2 * i + 1 : i + half;
+        const size_t o = row + size_t(head) * hd;
+        const float x0 = gb_load(q, dtype, o + d0), x1 = gb_load(q, dtype, o + d1);
+        gb_store(q, dtype, o + d0, x0 * cs - x1 * sn);
+        gb_store(q, dtype, o + d1, x0 * sn + x1 * cs);
+        return;
     }
     if (!k) return;
     const int* trow = table + size_t(b) * table_width;
-    for (int idx = threadIdx.x; idx < nkv * half; idx += blockDim.x) {
-        int g = idx / half, i = idx - g * half;
-        int d0 = pairing ? 2 * i : i, d1 = pairing ? 2 * i + 1 : i + half;
-        size_t o = row + size_t(g) * hd;
-        float x0 = gb_load(k, dtype, o + d0), x1 = gb_load(k, dtype, o + d1);
-        size_t c = gb_kv_offset(trow, ring_pages, p, g, nkv, hd);
-        gb_store(kcache, cache_dtype, c + d0, x0 * cs[i] - x1 * sn[i]);
-        gb_store(kcache, cache_dtype, c + d1, x0 * sn[i] + x1 * cs[i]);
+    if (head < nh + nkv) {
+        const int g = head - nh;
+        const size_t o = row + size_t(g) * hd;
+        const size_t c = gb_kv_offset(trow, ring_pages, p, g, nkv, hd);
+        if (i < half) {
+            float sn, cs;
+            sincosf(float(p) * inv_freq[i], &sn, &cs);
+            const int d0 = pairing ? 2 * i : i, d1 = pairing ? 2 * i + 1 : i + half;
+            const float x0 = gb_load(k, dtype, o + d0), x1 = gb_load(k, dtype, o + d1);
+            gb_store(kcache, cache_dtype, c + d0, x0 * cs - x1 * sn);
+            gb_store(kcache, cache_dtype, c + d1, x0 * sn + x1 * cs);
+        } else {                                       // the tail beyond the rotation: dims 2*half + 2*(i-half), +1
+            const int d = 2 * i;
+            gb_store(kcache, cache_dtype, c + d, gb_load(k, dtype, o + d));
+            gb_store(kcache, cache_dtype, c + d + 1, gb_load(k, dtype, o + d + 1));
+        }
+        return;
     }
-    int rot = 2 * half;
-    for (int idx = threadIdx.x; idx < nkv * (hd - rot); idx += blockDim.x) {
-        int g = idx / (hd - rot), d = rot + idx - g * (hd - rot);
-        size_t c = gb_kv_offset(trow, ring_pages, p, g, nkv, hd);
-        gb_store(kcache, cache_dtype, c + d, gb_load(k, dtype, row + size_t(g) * hd + d));
-    }
-    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
-        int g = idx / hd, d = idx - g * hd;
-        size_t c = gb_kv_offset(trow, ring_pages, p, g, nkv, hd);
-        gb_store(vcache, cache_dtype, c + d, gb_load(v, dtype, row + size_t(g) * hd + d));
-    }
+    const int g = head - nh - nkv;
+    const size_t o = row + size_t(g) * hd;
+    const size_t c = gb_kv_offset(trow, ring_pages, p, g, nkv, hd);
+    gb_store(vcache, cache_dtype, c + 2 * i, gb_load(v, dtype, o + 2 * i));
+    gb_store(vcache, cache_dtype, c + 2 * i + 1, gb_load(v, dtype, o + 2 * i + 1));
 }
 
 // q, k, v: first elements of the q, k and v parts of token 0's row; rows are `ld` elements
@@ -149,14 +232,17 @@ GB_API int gb_rope_kv_write(void* q, const void* k, const void* v, int dtype, lo
                             const int* pos, const int* table, int table_width, int ring_pages, void* kcache,
                             void* vcache, int cache_dtype, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(dtype) && gb_is_dtype(cache_dtype), "gb_rope_kv_write: bad dtype");
-    GB_REQUIRE(hd > 0 && rotary_dim >= 0 && rotary_dim <= hd && rotary_dim % 2 == 0,
-               "gb_rope_kv_write: rotary_dim %d must be even and at most head_dim %d", rotary_dim, hd);
-    GB_REQUIRE(rotary_dim / 2 <= ROPE_MAX_HALF, "gb_rope_kv_write: rotary_dim %d exceeds %d", rotary_dim, 2 * ROPE_MAX_HALF);
+    GB_REQUIRE(hd > 0 && hd % 2 == 0 && rotary_dim >= 0 && rotary_dim <= hd && rotary_dim % 2 == 0,
+               "gb_rope_kv_write: head_dim %d and rotary_dim %d must be even, rotary_dim at most head_dim", hd, rotary_dim);
+    GB_REQUIRE(hd / 2 <= 1024, "gb_rope_kv_write: head_dim %d exceeds 2048", hd);
     GB_REQUIRE((k == nullptr) == (v == nullptr), "gb_rope_kv_write: k and v must both be given or both be null");
     GB_REQUIRE(!k || (table && kcache && vcache && ring_pages > 0 && table_width >= 1), "gb_rope_kv_write: cache missing");
+    GB_REQUIRE(nh + 2 * nkv <= 65535, "gb_rope_kv_write: too many heads");
     if (T == 0) return 0;
-    rope_kv_write_kernel<<<T, 128, 0, stream>>>(q, k, v, dtype, ld, nh, nkv, hd, rotary_dim, pairing, inv_freq, seq_of, pos,
-                                                table, table_width, ring_pages, kcache, vcache, cache_dtype);
+    int threads = ((hd / 2 + 31) / 32) * 32;
+    dim3 grid(T, k ? nh + 2 * nkv : nh);
+    rope_kv_write_kernel<<<grid, threads, 0, stream>>>(q, k, v, dtype, ld, nh, nkv, hd, rotary_dim, pairing, inv_freq, seq_of,
+                                                       pos, table, table_width, ring_pages, kcache, vcache, cache_dtype);
     GB_LAUNCH_OK("gb_rope_kv_write");
     return 0;
 }
