@@ -52,6 +52,7 @@ struct TcParams {
     long long ldo;
     int out_dtype, bias_dtype;
     int T, N, K, splits;
+    int swiglu, N_out;    // swiglu: W's rows alternate gate, up; out has N_out features
 };
 
 template <int BN>
@@ -134,22 +135,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         const int cols = min(BN, p.T - t0);         // valid tokens of this tile
         float bias = 0.f;
         if (p.bias && n < p.N) bias = gb_load(p.bias, p.bias_dtype, n);
-        if (p.splits == 1) {
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (c0 >= cols) break;               // uniform over the warp
-                float v[16];
-                tmem_ld16(taddr + c0, v);
-                if (n < p.N && waited) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (c0 + j < cols) gb_store(p.out, p.out_dtype, size_t(t0 + c0 + j) * p.ldo + n, v[j] + bias);
-                }
-            }
-        } else {
-            const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        const float* partials = p.scratch + size_t(tile) * p.splits * (BN * BM);
+        bool finish = true;                          // does this CTA write the tile's result?
+        if (p.splits > 1) {
             float* mine = p.scratch + (size_t(tile) * p.splits + split) * (BN * BM);
             for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (c0 >= cols) break;
+                if (c0 >= cols) break;               // uniform over the warp
                 float v[16];
                 tmem_ld16(taddr + c0, v);
 #pragma unroll
@@ -163,35 +155,64 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                 last_flag = (old == p.splits - 1);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (last_flag) {
-                __threadfence();
-                const float* base = p.scratch + size_t(tile) * p.splits * (BN * BM);
-                if (n < p.N && waited) {
-                    // 4 columns at a time so that 4 * splits loads are in flight; the sum itself
-                    // runs over the splits in ascending order
-                    for (int c0 = 0; c0 < cols; c0 += 4) {
-                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            finish = last_flag != 0;
+            if (finish) __threadfence();
+        }
+        if (finish) {
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (c0 >= cols) break;
+                float v[16];
+                if (p.splits == 1) {
+                    tmem_ld16(taddr + c0, v);
+                } else {
+                    // the splits' partial sums in ascending order; 4 columns x 4 splits of loads in flight
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
+#pragma unroll
+                    for (int j0 = 0; j0 < 16; j0 += 4) {
+                        if (c0 + j0 >= cols) break;
                         for (int s0 = 0; s0 < p.splits; s0 += 4) {
-                            float v[4][4];
+                            float ld[4][4];
 #pragma unroll
                             for (int si = 0; si < 4; ++si)
 #pragma unroll
                                 for (int j = 0; j < 4; ++j)
-                                    v[si][j] = (s0 + si < p.splits && c0 + j < cols)
-                                                   ? __ldcg(base + size_t(s0 + si) * (BN * BM) + (c0 + j) * BM + row)
-                                                   : 0.f;
+                                    ld[si][j] = (s0 + si < p.splits && c0 + j0 + j < cols)
+                                                    ? __ldcg(partials + size_t(s0 + si) * (BN * BM) + (c0 + j0 + j) * BM + row)
+                                                    : 0.f;
 #pragma unroll
                             for (int si = 0; si < 4; ++si)
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) acc[j] += v[si][j];
+                                for (int j = 0; j < 4; ++j) v[j0 + j] += ld[si][j];
                         }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (c0 + j < cols) gb_store(p.out, p.out_dtype, size_t(t0 + c0 + j) * p.ldo + n, acc[j] + bias);
                     }
                 }
-                if (threadIdx.x == 64) p.counters[tile] = 0;       // ready for the next launch
+                if (!p.swiglu) {
+                    if (n < p.N && waited) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c0 + j < cols) gb_store(p.out, p.out_dtype, size_t(t0 + c0 + j) * p.ldo + n, v[j] + bias);
+                    }
+                } else {
+                    // even rows of the tile are gate features, odd rows the matching up features: the two
+                    // lanes of a pair swap halves of their 16 columns, the even lane finishes columns
+                    // 0..7 and the odd lane columns 8..15 of silu(gate) * up
+                    const bool odd = lane & 1;
+                    float other[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) other[j] = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[8 + j], 1);
+                    const int f = blockIdx.x * 64 + (row >> 1);      // output feature
+                    if (f < p.N_out && waited) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float gte = odd ? other[j] : v[j], u = odd ? v[8 + j] : other[j];
+                            const int c = c0 + (odd ? 8 : 0) + j;
+                            if (c < cols) gb_store(p.out, p.out_dtype, size_t(t0 + c) * p.ldo + f, gte / (1.f + expf(-gte)) * u);
+                        }
+                    }
+                }
             }
+            if (p.splits > 1 && threadIdx.x == 64) p.counters[tile] = 0;       // ready for the next launch
         }
     }
     tc_fence_before();
@@ -319,11 +340,18 @@ GB_API int gb_gemm_tc_supported(const void* X, long long ldx, const void* W, lon
 // X: bf16 [T, K] pitch ldx; W: bf16 [N, K] pitch ldw; out: bf16 or f32 [T, N] pitch ldo; bias optional.
 // scratch: gb_gemm_tc_scratch_floats(...) floats; counters: at least as many zeroed ints as tiles
 // (the kernel leaves them zero).  Both may be null when K is not split.
+// swiglu_features > 0: W is [2*64*ceil(F/64), K], row 2f being gate row f and row 2f+1 up row f (zero
+// rows pad the last tile), F = swiglu_features, and
+// out[t,f] = silu(gate_f) * up_f has F columns (src/model/llama.rs:399-401 in the product's epilogue).
 GB_API int gb_gemm_tc(const void* X, long long ldx, const void* W, long long ldw, const void* bias, int bias_dtype,
                       void* out, int out_dtype, long long ldo, int T, int N, int K, float* scratch, int* counters,
-                      int n_counters, int sms, cudaStream_t stream) {
+                      int n_counters, int sms, int swiglu_features, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(out_dtype) && (!bias || gb_is_dtype(bias_dtype)), "gb_gemm_tc: bad dtype");
-    GB_REQUIRE(T >= 0 && N > 0 && K > 0 && ldo >= N, "gb_gemm_tc: bad sizes T=%d N=%d K=%d ldo=%lld", T, N, K, ldo);
+    GB_REQUIRE(T >= 0 && N > 0 && K > 0, "gb_gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
+    GB_REQUIRE(swiglu_features >= 0 && ldo >= (swiglu_features ? swiglu_features : N), "gb_gemm_tc: output pitch %lld too small", ldo);
+    GB_REQUIRE(!swiglu_features || (N == 128 * ((swiglu_features + 63) / 64) && !bias),
+               "gb_gemm_tc: a gated product of %d features needs %d interleaved rows and no bias, got %d", swiglu_features,
+               128 * ((swiglu_features + 63) / 64), N);
     GB_REQUIRE(gb_gemm_tc_supported(X, ldx, W, ldw, K),
                "gb_gemm_tc: K=%d and the row pitches (%lld, %lld) must be multiples of 8 and the operands 16-byte aligned",
                K, ldx, ldw);
@@ -334,6 +362,7 @@ GB_API int gb_gemm_tc(const void* X, long long ldx, const void* W, long long ldw
     p.out = out; p.bias = bias; p.scratch = scratch; p.counters = counters; p.status = g_status_dev;
     p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype; p.T = T; p.N = N; p.K = K;
     p.splits = (scratch && counters) ? gb_gemm_tc_splits(T, N, K, sms) : 1;
+    p.swiglu = swiglu_features > 0; p.N_out = swiglu_features;
     long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
     GB_REQUIRE(p.splits == 1 || tiles <= n_counters, "gb_gemm_tc: %lld tiles need as many counters, %d given", tiles, n_counters);
     GB_REQUIRE((T + bn - 1) / bn <= 65535, "gb_gemm_tc: T=%d is too many rows for one launch", T);

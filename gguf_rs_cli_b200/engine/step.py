@@ -53,8 +53,8 @@ class Engine:
         self.ws = Workspace(self.device)
         self.runs = model.run_views(self.cache)
         self.vocab_size = model.spec.vocab_size
-        self._meta_host: Optional[torch.Tensor] = None
-        self._meta_dev: Optional[torch.Tensor] = None
+        self._meta_ring = None
+        self._meta_slot = None
         self.launches = 0
 
     # ------------------------------------------------------------ sequences
@@ -71,11 +71,21 @@ class Engine:
 
     # ----------------------------------------------------------------- plan
     def _meta(self, n: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        if self._meta_host is None or self._meta_host.numel() < n:
+        """Pinned host and device buffers for a step's index arrays.  Steps do not wait for
+        one another on the host, so the staging buffers form a ring, and one is written
+        again only after the copy that last read it has run."""
+        if self._meta_ring is None or self._meta_ring[0][0].numel() < n:
             size = max(n, 4096)
-            self._meta_host = torch.empty(size, dtype=torch.int32, pin_memory=True)
-            self._meta_dev = torch.empty(size, dtype=torch.int32, device=self.device)
-        return self._meta_host, self._meta_dev
+            self._meta_ring = [(torch.empty(size, dtype=torch.int32, pin_memory=True),
+                                torch.empty(size, dtype=torch.int32, device=self.device)) for _ in range(4)]
+            self._meta_events = [None] * 4
+            self._meta_next = 0
+        i = self._meta_next
+        self._meta_next = (i + 1) % len(self._meta_ring)
+        if self._meta_events[i] is not None:
+            self._meta_events[i].synchronize()
+        self._meta_slot = i
+        return self._meta_ring[i]
 
     def meta_size(self, batch: int) -> int:
         """int32 words of index arrays for a padded batch of single tokens with full tables."""
@@ -148,11 +158,16 @@ class Engine:
             table_offs.append((len(flat), Bp, width))
             for r in rows:
                 flat += r
-        host, dev = meta if meta is not None else self._meta(len(flat))
+        own = meta is None
+        host, dev = self._meta(len(flat)) if own else meta
         if len(flat) > host.numel():
             raise StepError(f"the step's index arrays ({len(flat)} words) exceed the buffer given ({host.numel()})")
         host[:len(flat)] = torch.tensor(flat, dtype=torch.int32)
         dev[:len(flat)].copy_(host[:len(flat)], non_blocking=True)
+        if own:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._meta_events[self._meta_slot] = ev
 
         def view(name):
             a, n = offs[name]

@@ -142,14 +142,26 @@ def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     return bool(native.library().gb_gemm_tc_supported(ptr(x), x.stride(0), ptr(w), w.stride(0), x.shape[1]))
 
 
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[2*64*ceil(F/64), K]: row 2f is gate row f, row 2f+1 is up row f, zero rows padding F to
+    a multiple of 64: the layout gemm_tc's gated epilogue reads."""
+    F, K = gate.shape
+    pad = (F + 63) // 64 * 64 - F
+    if pad:
+        zeros = torch.zeros(pad, K, dtype=gate.dtype, device=gate.device)
+        gate, up = torch.cat([gate, zeros]), torch.cat([up, zeros])
+    return torch.stack([gate, up], dim=1).reshape(2 * (F + pad), K).contiguous()
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-            split_k: bool = True) -> torch.Tensor:
+            split_k: bool = True, swiglu_features: int = 0) -> torch.Tensor:
     """bf16 x bf16 -> f32 accumulate on tcgen05; out bf16 or f32.  Refuses what
-    gemm_tc_supported refuses."""
+    gemm_tc_supported refuses.  With swiglu_features = F, w is interleave_gate_up(gate, up)
+    and out [T, F] = silu(x gate^T) * (x up^T)."""
     _cuda(x, w, bias, out)
     T, K = x.shape
     N = w.shape[0]
-    assert w.shape[1] == K and out.shape == (T, N) and out.stride(1) == 1
+    assert w.shape[1] == K and out.shape == (T, swiglu_features or N) and out.stride(1) == 1
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     sc = tc_scratch(x.device)
     scratch = counters = None
@@ -160,7 +172,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
             scratch, counters = sc.floats, sc.counters
     call("gb_gemm_tc", ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(bias), 0 if bias is None else dtype_code(bias),
          ptr(out), dtype_code(out), out.stride(0), T, N, K, ptr(scratch), ptr(counters),
-         0 if counters is None else counters.numel(), sc.sms, stream_ptr())
+         0 if counters is None else counters.numel(), sc.sms, int(swiglu_features), stream_ptr())
     return out
 
 

@@ -130,7 +130,7 @@ _SIGNATURES = {
     "gb_gemm_generic": [_P, _I, _L, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P],
     "gb_attention_generic": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _F, _P],
     "gb_sample": [_P, _L, _I, _I, _P, _P, _F, _I, _F, _F, _P, _P, _P, _P],
-    "gb_gemm_tc": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _P],
+    "gb_gemm_tc": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _I, _P],
     "gb_gemm_tc_tile": [_I],
     "gb_gemm_tc_splits": [_I, _I, _I, _I],
     "gb_gemm_tc_scratch_floats": [_I, _I, _I, _I],

@@ -32,11 +32,22 @@ class GatedMLP(Part):
         g, u, d = (store.get(r) for r in self.tensor_requests())
         if g.dtype != u.dtype:
             u = u.to(g.dtype)
-        self.gate_up = Linear(torch.cat([g, u], dim=0), name="ff.gate_up")
+        # where the tensor-core product can take them, gate and up are interleaved tile by tile so
+        # that its epilogue applies the activation; else they are stacked and a kernel follows
+        self.fused = g.dtype == torch.bfloat16 and self.p["hidden_size"] % 8 == 0 and g.is_cuda
+        if self.fused:
+            self.gate_up_tiles = kernels.interleave_gate_up(g, u)
+        else:
+            self.gate_up = Linear(torch.cat([g, u], dim=0), name="ff.gate_up")
         self.down = Linear(d, name="ff.down")
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gu = self.gate_up(h, ctx)
-        act = ctx.ws.get("ff.act", (h.shape[0], self.p["intermediate_size"]), ctx.dtype)
-        kernels.swiglu(gu, act)
+        F = self.p["intermediate_size"]
+        act = ctx.ws.get("ff.act", (h.shape[0], F), ctx.dtype)
+        if self.fused and kernels.gemm_tc_supported(h, self.gate_up_tiles):
+            kernels.gemm_tc(h, self.gate_up_tiles, None, act, swiglu_features=F)
+        elif self.fused:
+            raise RuntimeError("gated_mlp: the activations given do not fit the fused product it was loaded for")
+        else:
+            kernels.swiglu(self.gate_up(h, ctx), act)
         return self.down(act, ctx)

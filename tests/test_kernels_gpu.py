@@ -465,3 +465,26 @@ def test_attention_prefill_ignores_unwritten_cache_rows():
     out = torch.empty(70, nh * hd, dtype=BF, device=DEV)
     k.attention_prefill(q, out, nh, nkv, hd, tiles, cu, starts, ql, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd))
     assert rel_err(out, want) < 1e-2
+
+
+# ------------------------------------------------- gated product (fused SwiGLU)
+@pytest.mark.parametrize("T,F,Kd", [(1, 176, 64), (8, 520, 320), (16, 1024, 4096), (64, 200, 2048), (130, 520, 328),
+                                    (300, 14336 // 8, 512)])
+def test_gemm_tensor_core_gated(T, F, Kd):
+    k = K()
+    g = torch.Generator().manual_seed(T + F)
+    x = torch.randn(T, Kd, generator=g).to(BF).to(DEV)
+    wg = (torch.randn(F, Kd, generator=g) * 0.1).to(BF).to(DEV)
+    wu = (torch.randn(F, Kd, generator=g) * 0.1).to(BF).to(DEV)
+    w = k.interleave_gate_up(wg, wu)
+    assert w.shape == (128 * ((F + 63) // 64), Kd)
+    want = P.silu(P.linear(x.double().cpu(), wg.double().cpu())) * P.linear(x.double().cpu(), wu.double().cpu())
+    for split in (True, False):
+        out = torch.full((T, F), float("nan"), dtype=BF, device=DEV)
+        k.gemm_tc(x, w, None, out, split_k=split, swiglu_features=F)
+        torch.cuda.synchronize()
+        k.check_tc_status()
+        assert rel_err(out, want) < 5e-3, f"split_k={split}"
+    out32 = torch.empty(T, F, dtype=F32, device=DEV)
+    k.gemm_tc(x, w, None, out32, swiglu_features=F)
+    assert rel_err(out32, want) < 1e-5
