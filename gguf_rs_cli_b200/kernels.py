@@ -180,20 +180,28 @@ def attention_decode_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim: 
     return bool(native.library().gb_attention_decode_supported(head_dim, dtype_code(kcache), dtype_code(q)))
 
 
+def attention_decode_mma_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> bool:
+    return bool(native.library().gb_attention_decode_mma_supported(head_dim, dtype_code(kcache), dtype_code(q)))
+
+
 def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                      seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, ring_pages: int,
                      kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float,
-                     splits: Optional[int] = None) -> torch.Tensor:
+                     splits: Optional[int] = None, mma: Optional[bool] = None) -> torch.Tensor:
     """One token per sequence over the bf16 cache; all heads of a group share one pass over
-    the keys and values."""
+    the keys and values.  mma: the tensor-core kernel (head sizes 64 and 128; the default
+    where it fits) or the CUDA-core one (any head size that is a multiple of 16)."""
     _cuda(q, out, seq_of, pos, table, kcache, vcache)
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, n_heads * head_dim)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
     lib = native.library()
     sc = tc_scratch(q.device)
+    if mma is None:
+        mma = attention_decode_mma_supported(q, kcache, head_dim)
+    entry = "gb_attention_decode_mma" if mma else "gb_attention_decode"
     if splits is None:
-        splits = lib.gb_attention_decode_splits(T, n_heads, n_kv_heads, sc.sms, table.shape[1])
+        splits = getattr(lib, entry + "_splits")(T, n_heads, n_kv_heads, sc.sms, table.shape[1])
     need = lib.gb_attention_decode_scratch_floats(T, n_heads, head_dim, splits)
     scratch = counters = None
     if need:
@@ -201,7 +209,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_head
         scratch, counters = sc.floats, sc.counters
         if T * n_heads > sc.COUNTERS:
             splits, scratch, counters = 1, None, None
-    call("gb_attention_decode", ptr(q), q.stride(0), ptr(out), out.stride(0), T, n_heads, n_kv_heads, head_dim,
+    call(entry, ptr(q), q.stride(0), ptr(out), out.stride(0), T, n_heads, n_kv_heads, head_dim,
          ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(kcache), ptr(vcache), int(window or 0),
          float(scale), splits, ptr(scratch), ptr(counters), 0 if counters is None else counters.numel(), stream_ptr())
     return out

@@ -367,10 +367,13 @@ def test_sampling_ring_and_padding():
 
 # ----------------------------------------------------------- decode attention
 @pytest.mark.parametrize("nh,nkv,hd", [(6, 3, 32), (4, 1, 48), (8, 8, 16), (8, 2, 128), (5, 5, 80), (16, 1, 64),
-                                       (12, 2, 256), (3, 1, 112)])
+                                       (12, 2, 256), (3, 1, 112), (40, 2, 64), (32, 8, 128), (7, 7, 128)])
 @pytest.mark.parametrize("splits", [None, 1, 3, 7])
-def test_attention_decode(nh, nkv, hd, splits):
+@pytest.mark.parametrize("mma", [False, True])
+def test_attention_decode(nh, nkv, hd, splits, mma):
     k = K()
+    if mma and hd not in (64, 128):
+        pytest.skip("the tensor-core decode kernel takes head sizes 64 and 128")
     lens = [200, 1, 65, 130, 64, 513]
     q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, [1] * len(lens), BF, seed=hd + nh)
     # two padding tokens in the middle of the batch
@@ -383,30 +386,31 @@ def test_attention_decode(nh, nkv, hd, splits):
     qp[rows], sp[rows], pp[rows] = q, seq_of, pos
     out = torch.full((T, nh * hd), float("nan"), dtype=BF, device=DEV)
     assert k.attention_decode_supported(qp, kc, hd)
-    k.attention_decode(qp, out, nh, nkv, hd, sp, pp, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd), splits=splits)
+    k.attention_decode(qp, out, nh, nkv, hd, sp, pp, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd), splits=splits, mma=mma)
     assert rel_err(out[rows], want) < 1e-2
     assert torch.equal(out[[2, 5]].float().cpu(), torch.zeros(2, nh * hd))
     twin = torch.empty(T, nh * hd, dtype=BF, device=DEV)
     k.attention_generic(qp, twin, nh, nkv, hd, sp, pp, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd))
     assert rel_err(out[rows], twin[rows]) < 1e-2
     again = torch.full((T, nh * hd), float("nan"), dtype=BF, device=DEV)
-    k.attention_decode(qp, again, nh, nkv, hd, sp, pp, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd), splits=splits)
+    k.attention_decode(qp, again, nh, nkv, hd, sp, pp, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd), splits=splits, mma=mma)
     assert torch.equal(again, out)                 # counters were left at zero; the merge order is fixed
 
 
 @pytest.mark.parametrize("window", [1, 64, 65, 100, 300])
-def test_attention_decode_far_key_and_window(window):
+@pytest.mark.parametrize("mma", [False, True])
+def test_attention_decode_far_key_and_window(window, mma):
     k = K()
     nh, nkv, hd = 8, 2, 64
     lens = [700, 300, 50]
     scale = 1 / math.sqrt(hd)
     q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, [1, 1, 1], BF, 5, boost=(0, 3, 2))
     out = torch.empty(3, nh * hd, dtype=BF, device=DEV)
-    k.attention_decode(q, out, nh, nkv, hd, seq_of, pos, table, 1 << 20, kc, vc, 0, scale)
+    k.attention_decode(q, out, nh, nkv, hd, seq_of, pos, table, 1 << 20, kc, vc, 0, scale, mma=mma)
     assert rel_err(out, want) < 1e-2               # the far key at position 3 dominates head 2 of sequence 0
     _, _, _, _, _, _, want_w = attention_case(nh, nkv, hd, lens, [1, 1, 1], BF, 5, window=window, boost=(0, 3, 2))
     for splits in (None, 1, 5):
-        k.attention_decode(q, out, nh, nkv, hd, seq_of, pos, table, 1 << 20, kc, vc, window, scale, splits=splits)
+        k.attention_decode(q, out, nh, nkv, hd, seq_of, pos, table, 1 << 20, kc, vc, window, scale, splits=splits, mma=mma)
         assert rel_err(out, want_w) < 1e-2, f"window {window} splits {splits}"
     assert rel_err(want_w, want) > 0.05
 
