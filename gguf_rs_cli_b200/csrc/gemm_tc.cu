@@ -38,7 +38,9 @@ constexpr int A_BYTES = BM * BK * 2;
 template <int BN> struct TileCfg {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+    // small token tiles keep the ring near 100 KB so that two CTAs share an SM (more tiles in flight,
+    // no idle half wave when there are between one and two tiles per SM)
+    static constexpr int STAGES = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : BN >= 32 ? 5 : 6;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;     // + slack to align the ring to 1024 bytes
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
 };
@@ -315,8 +317,9 @@ GB_API int gb_gemm_tc_splits(int T, int N, int K, int sms) {
     int bn = gb_gemm_tc_tile(T);
     long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
     int kb = (K + BK - 1) / BK;
+    int slots = bn <= 32 ? 2 * sms : sms;          // CTAs that can be resident at once
     if (tiles >= sms || kb < 8) return 1;
-    int s = int(sms / tiles);
+    int s = int(slots / tiles);
     if (s > kb / 4) s = kb / 4;       // at least 4 K blocks per split
     if (s > 16) s = 16;
     return s < 1 ? 1 : s;

@@ -62,6 +62,9 @@ class Decoder:
             if run.cache_of is not None and owns:
                 raise ValueError(f"schedule[{r}] reads the cache of run {run.cache_of}, but its mixer keeps keys and "
                                  f"values of its own (build it with shares_kv)")
+            if run.cache_of is None and not owns and getattr(mixer, "shares_kv", False):
+                raise ValueError(f"schedule[{r}]: the mixer of layer {run.layer} has no keys and values of its own; "
+                                 f"the entry must name the run whose cache it reads (cache_of)")
             if run.cache_of is not None:
                 src = self.layers[spec.schedule[run.cache_of].layer].mixer.kv_spec()
                 if src is None or src != mixer.reads_kv_spec():
