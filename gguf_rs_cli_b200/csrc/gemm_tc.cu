@@ -389,3 +389,112 @@ GB_API int gb_tc_status_clear() {
     if (g_status_host) *g_status_host = 0;
     return 0;
 }
+
+// ------------------------------------------------------------ no-allocation entry point
+// See gemm_tc_noalloc.h.  The scratch of the K split lives in the library image.  In host code
+// the names below are host-side stand-ins, not device addresses; the device addresses are
+// looked up once per device with cudaGetSymbolAddress and handed to the kernel.
+#include "gemm_tc_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[GB_NOALLOC_SCRATCH_FLOATS];
+static __device__ __align__(256) int g_noalloc_counters[GB_NOALLOC_COUNTERS];
+static __device__ __align__(256) int g_noalloc_status;
+
+namespace {
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+struct NoallocDevice {
+    bool ready;
+    float* scratch;
+    int* counters;
+    int* status;
+    int sms;
+};
+NoallocDevice g_noalloc_dev[NOALLOC_MAX_DEVICES];      // zero-initialised; one slot per device ordinal
+std::mutex g_noalloc_mu;
+
+// Address look-up for the current device, once.
+int noalloc_setup(int dev, NoallocDevice** out) {
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return gb_fail("gb_gemm_tc_noalloc: device ordinal %d is out of range", dev);
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    NoallocDevice& d = g_noalloc_dev[dev];
+    if (!d.ready) {
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.scratch), g_noalloc_scratch);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.counters), g_noalloc_counters);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_noalloc_status);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess)
+            return gb_fail("gb_gemm_tc_noalloc: cannot find the built-in scratch on device %d: %s", dev, cudaGetErrorString(e));
+        d.ready = true;
+    }
+    *out = &d;
+    return 0;
+}
+
+// A tensor map built on the caller's stack, without the cache that gb_gemm_tc keeps on the heap.
+int encode_map_2d(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return gb_fail("gb_gemm_tc_noalloc: the driver gives no cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+    cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
+    cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return gb_fail("gb_gemm_tc_noalloc: cuTensorMapEncodeTiled failed with code %d", int(r));
+    return 0;
+}
+
+}  // namespace
+
+GB_API int gb_gemm_tc_noalloc(const void* X, long long ldx, const void* W, long long ldw, const void* bias,
+                              int bias_dtype, void* out, int out_dtype, long long ldo, int T, int N, int K,
+                              cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(out_dtype) && (!bias || gb_is_dtype(bias_dtype)), "gb_gemm_tc_noalloc: bad dtype");
+    GB_REQUIRE(T >= 0 && N > 0 && K > 0 && ldo >= N, "gb_gemm_tc_noalloc: bad sizes T=%d N=%d K=%d ldo=%lld", T, N, K, ldo);
+    GB_REQUIRE(gb_gemm_tc_supported(X, ldx, W, ldw, K),
+               "gb_gemm_tc_noalloc: K=%d and the row pitches (%lld, %lld) must be multiples of 8 and the operands 16-byte "
+               "aligned", K, ldx, ldw);
+    if (T == 0) return 0;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return gb_fail("gb_gemm_tc_noalloc: no current device");
+    NoallocDevice* d = nullptr;
+    if (noalloc_setup(dev, &d)) return 1;
+    const int bn = gb_gemm_tc_tile(T);
+    GB_REQUIRE((T + bn - 1) / bn <= 65535, "gb_gemm_tc_noalloc: T=%d is too many rows for one launch", T);
+    const long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
+    const int splits = gb_gemm_tc_splits(T, N, K, d->sms);
+    if (splits > 1) {
+        const long long need = tiles * splits * bn * BM;
+        GB_REQUIRE(need <= GB_NOALLOC_SCRATCH_FLOATS && tiles <= GB_NOALLOC_COUNTERS,
+                   "gb_gemm_tc_noalloc: T=%d N=%d K=%d splits K %d ways over %lld tiles and needs %lld floats of scratch; the "
+                   "built-in scratch holds %d floats and %d tiles (use gb_gemm_tc with memory of your own)",
+                   T, N, K, splits, tiles, need, GB_NOALLOC_SCRATCH_FLOATS, GB_NOALLOC_COUNTERS);
+        // the arrival counters must start at zero whatever an earlier call left behind
+        if (cudaMemsetAsync(d->counters, 0, sizeof(int) * size_t(tiles), stream) != cudaSuccess)
+            return gb_fail("gb_gemm_tc_noalloc: cannot clear the counters");
+    }
+    TcParams p;
+    p.out = out; p.bias = bias; p.scratch = d->scratch; p.counters = d->counters; p.status = d->status;
+    p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype; p.T = T; p.N = N; p.K = K;
+    p.splits = splits; p.swiglu = 0; p.N_out = 0;
+    CUtensorMap mw, mx;
+    if (encode_map_2d(W, N, K, ldw, BM, &mw)) return 1;
+    if (encode_map_2d(X, T, K, ldx, bn, &mx)) return 1;
+    switch (bn) {
+        case 16: return launch_tc<16>(mw, mx, p, stream);
+        case 32: return launch_tc<32>(mw, mx, p, stream);
+        case 64: return launch_tc<64>(mw, mx, p, stream);
+        case 128: return launch_tc<128>(mw, mx, p, stream);
+        default: return launch_tc<256>(mw, mx, p, stream);
+    }
+}
+
+GB_API int gb_gemm_tc_noalloc_status(void) {
+    int dev = -1, value = 0, zero = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES || !g_noalloc_dev[dev].ready) return 0;
+    if (cudaMemcpy(&value, g_noalloc_dev[dev].status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (value) cudaMemcpy(g_noalloc_dev[dev].status, &zero, sizeof(int), cudaMemcpyHostToDevice);
+    return value;
+}
