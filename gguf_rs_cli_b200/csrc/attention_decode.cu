@@ -48,6 +48,8 @@ __device__ __forceinline__ void unpack8(uint4 v, float* f) {
 
 template <int GT, int HC>
 __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p) {
+    gb_grid_launch_dependents();
+    gb_grid_wait();
     const int t = blockIdx.x;
     const int G = p.nh / p.nkv;
     const int gtiles = (G + GT - 1) / GT;
@@ -233,7 +235,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p
 }
 
 template <int GT, int HC> int launch_ad(const AdParams& p, dim3 grid, cudaStream_t stream) {
-    attention_decode_kernel<GT, HC><<<grid, AD_THREADS, 0, stream>>>(p);
+    gb_launch(attention_decode_kernel<GT, HC>, grid, dim3(AD_THREADS), 0, stream, p);
     GB_LAUNCH_OK("gb_attention_decode");
     return 0;
 }

@@ -75,6 +75,8 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
     __shared__ float m_s[DM_WARPS][DM_ROWS], l_s[DM_WARPS][DM_ROWS];
     __shared__ int last_flag;
 
+    gb_grid_launch_dependents();
+    gb_grid_wait();
     const int t = blockIdx.x;
     const int G = p.nh / p.nkv;
     const int gtiles = (G + DM_ROWS - 1) / DM_ROWS;
@@ -288,7 +290,7 @@ template <int HD> int launch_dm(const DmParams& p, dim3 grid, cudaStream_t strea
             return gb_fail("gb_attention_decode_mma: cannot get %d bytes of shared memory", SMEM);
         configured = true;
     }
-    attention_decode_mma_kernel<HD><<<grid, DM_THREADS, SMEM, stream>>>(p);
+    gb_launch(attention_decode_mma_kernel<HD>, grid, dim3(DM_THREADS), SMEM, stream, p);
     GB_LAUNCH_OK("gb_attention_decode_mma");
     return 0;
 }

@@ -78,6 +78,8 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(ApParams 
     __nv_bfloat16* ks = qs + AP_BM * HD;                                       // [2][64][HD]
     __nv_bfloat16* vs = ks + 2 * AP_BN * HD;                                   // [2][64][HD]
 
+    gb_grid_launch_dependents();
+    gb_grid_wait();
     const int b = p.tiles[2 * blockIdx.x], q0 = p.tiles[2 * blockIdx.x + 1];
     const int h = blockIdx.y, g = h / (p.nh / p.nkv);
     const int start = p.starts[b], qlen = p.qlens[b], tok0 = p.cu[b] + q0;
@@ -235,7 +237,7 @@ template <int HD> int launch_ap(const ApParams& p, int n_tiles, cudaStream_t str
             return gb_fail("gb_attention_prefill: cannot get %d bytes of shared memory", SMEM);
         configured = true;
     }
-    attention_prefill_kernel<HD><<<dim3(n_tiles, p.nh), AP_THREADS, SMEM, stream>>>(p);
+    gb_launch(attention_prefill_kernel<HD>, dim3(n_tiles, p.nh), dim3(AP_THREADS), SMEM, stream, p);
     GB_LAUNCH_OK("gb_attention_prefill");
     return 0;
 }

@@ -28,6 +28,32 @@ int gb_fail(const char* fmt, ...);
         if (e__ != cudaSuccess) return gb_fail("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
     } while (0)
 
+// Programmatic dependent launch: a kernel launched through gb_launch may start while the
+// kernel before it on the stream is still running; it may touch nothing that kernel writes (or
+// reads and this one writes) before gb_grid_wait() returns.  gb_grid_launch_dependents() lets the
+// next kernel start its own prologue.  Both are no-ops for a kernel launched the ordinary way.
+bool gb_pdl_enabled();
+__device__ __forceinline__ void gb_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void gb_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t gb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    if (gb_pdl_enabled()) {
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 static inline bool gb_is_dtype(int d) { return d == GB_F32 || d == GB_BF16; }
 static inline size_t gb_dtype_size(int d) { return d == GB_F32 ? 4 : 2; }
 

@@ -8,6 +8,8 @@
 // ------------------------------------------------------------------ embedding
 __global__ void embed_kernel(const void* __restrict__ table, int table_dtype, const int* __restrict__ tokens,
                              int E, int V, float* __restrict__ out) {
+    gb_grid_launch_dependents();
+    gb_grid_wait();
     int t = blockIdx.x;
     int tok = tokens[t];
     float* o = out + size_t(t) * E;
@@ -25,7 +27,7 @@ GB_API int gb_embed(const void* table, int table_dtype, const int* tokens, int T
     GB_REQUIRE(gb_is_dtype(table_dtype), "gb_embed: bad table dtype %d", table_dtype);
     GB_REQUIRE(T >= 0 && E > 0 && V > 0, "gb_embed: bad sizes T=%d E=%d V=%d", T, E, V);
     if (T == 0) return 0;
-    embed_kernel<<<T, 256, 0, stream>>>(table, table_dtype, tokens, E, V, out);
+    gb_launch(embed_kernel, dim3(T), dim3(256), 0, stream, table, table_dtype, tokens, E, V, out);
     GB_LAUNCH_OK("gb_embed");
     return 0;
 }
@@ -74,6 +76,8 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_vec_kernel(
     const int* __restrict__ rows, int E, const void* __restrict__ w, int w_dtype, float eps, void* __restrict__ out,
     int out_dtype, int write_x) {
     __shared__ float red[32];
+    gb_grid_launch_dependents();
+    gb_grid_wait();
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     const size_t base = size_t(s) * E;
@@ -144,9 +148,9 @@ GB_API int gb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_de
     auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     bool vec = E % 4 == 0 && E <= NORM_THREADS * NORM_MAX_VEC * 4 && aligned(x) && aligned(out) && aligned(w) &&
                (n_delta == 0 || (aligned(delta) && delta_stride % 4 == 0));
-#define NORM_LAUNCH(NV)                                                                                               \
-    add_rmsnorm_vec_kernel<NV><<<n_rows, NORM_THREADS, 0, stream>>>(x, delta, delta_dtype, n_delta, size_t(delta_stride), \
-                                                                     rows, E, w, w_dtype, eps, out, out_dtype, write_x)
+#define NORM_LAUNCH(NV)                                                                                              \
+    gb_launch(add_rmsnorm_vec_kernel<NV>, dim3(n_rows), dim3(NORM_THREADS), 0, stream, x, delta, delta_dtype, n_delta, \
+              size_t(delta_stride), rows, E, w, w_dtype, eps, out, out_dtype, write_x)
     if (vec) {
         int groups = (E / 4 + NORM_THREADS - 1) / NORM_THREADS;
         if (groups <= 1) NORM_LAUNCH(1);
@@ -177,6 +181,8 @@ __global__ void rope_kv_write_kernel(void* __restrict__ q, const void* __restric
                                      const int* __restrict__ pos, const int* __restrict__ table, int table_width,
                                      int ring_pages, void* __restrict__ kcache, void* __restrict__ vcache,
                                      int cache_dtype) {
+    gb_grid_launch_dependents();
+    gb_grid_wait();
     const int t = blockIdx.x, head = blockIdx.y;
     const int b = seq_of[t];
     if (b < 0) return;
@@ -241,8 +247,8 @@ GB_API int gb_rope_kv_write(void* q, const void* k, const void* v, int dtype, lo
     if (T == 0) return 0;
     int threads = ((hd / 2 + 31) / 32) * 32;
     dim3 grid(T, k ? nh + 2 * nkv : nh);
-    rope_kv_write_kernel<<<grid, threads, 0, stream>>>(q, k, v, dtype, ld, nh, nkv, hd, rotary_dim, pairing, inv_freq, seq_of,
-                                                       pos, table, table_width, ring_pages, kcache, vcache, cache_dtype);
+    gb_launch(rope_kv_write_kernel, grid, dim3(threads), 0, stream, q, k, v, dtype, ld, nh, nkv, hd, rotary_dim, pairing, inv_freq,
+              seq_of, pos, table, table_width, ring_pages, kcache, vcache, cache_dtype);
     GB_LAUNCH_OK("gb_rope_kv_write");
     return 0;
 }

@@ -40,7 +40,7 @@ template <int BN> struct TileCfg {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     // small token tiles keep the ring near 100 KB so that two CTAs share an SM (more tiles in flight,
     // no idle half wave when there are between one and two tiles per SM)
-    static constexpr int STAGES = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : BN >= 32 ? 5 : 6;
+    static constexpr int STAGES = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 4 : BN >= 32 ? 5 : 6;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;     // + slack to align the ring to 1024 bytes
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
 };
@@ -88,13 +88,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_d = tmem_base;
+    gb_grid_launch_dependents();                    // the next kernel may begin its own prologue
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---- producer: TMA loads into the ring
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int kb = kb_begin; kb < kb_end; ++kb) {
+            // ---- producer: TMA loads into the ring.  The weights do not depend on the kernel before
+            // this one, so the first round of weight tiles is requested at once; the activations only
+            // after that kernel has finished.
+            const int pre = min(Cfg::STAGES, kb_end - kb_begin);
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
+                tma_load_2d(ring + i * Cfg::STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full_bar[i]);
+            }
+            gb_grid_wait();
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(ring + i * Cfg::STAGE_BYTES + A_BYTES, &map_x, (kb_begin + i) * BK, t0, &full_bar[i]);
+            int stage = pre % Cfg::STAGES;
+            uint32_t phase = pre == Cfg::STAGES ? 1 : 0;
+            for (int kb = kb_begin + pre; kb < kb_end; ++kb) {
                 if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { atomicExch(p.status, 1); break; }
                 uint8_t* a = ring + stage * Cfg::STAGE_BYTES;
                 mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
@@ -131,6 +142,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         const int row = quarter * 32 + lane;        // feature within the tile = TMEM lane
         const int n = n0 + row;
         const bool waited = mbar_wait(&acc_bar, 0);
+        gb_grid_wait();                              // before anything is written that the kernel before may still read
         if (!waited && lane == 0) atomicExch(p.status, 3);
         tc_fence_after();
         const uint32_t taddr = tmem_d + (uint32_t(quarter * 32) << 16);
@@ -302,7 +314,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, c
         configured = true;
     }
     dim3 grid((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, p.splits);
-    gemm_tc_kernel<BN><<<grid, TC_THREADS, Cfg::SMEM, stream>>>(mw, mx, p);
+    gb_launch(gemm_tc_kernel<BN>, grid, dim3(TC_THREADS), Cfg::SMEM, stream, mw, mx, p);
     GB_LAUNCH_OK("gb_gemm_tc");
     return 0;
 }
@@ -313,8 +325,15 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, c
 GB_API int gb_gemm_tc_tile(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 
 // How many ways the kernel would split K for these sizes on a device with `sms` SMs (1 = no scratch needed).
+static int g_split_override = 0;      // > 0: every product uses this many splits (tuning aid)
+GB_API int gb_gemm_tc_set_splits(int s) { g_split_override = s; return 0; }
+
 GB_API int gb_gemm_tc_splits(int T, int N, int K, int sms) {
     int bn = gb_gemm_tc_tile(T);
+    if (g_split_override > 0) {
+        int kb0 = (K + BK - 1) / BK;
+        return g_split_override > kb0 ? kb0 : g_split_override;
+    }
     long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
     int kb = (K + BK - 1) / BK;
     int slots = bn <= 32 ? 2 * sms : sms;          // CTAs that can be resident at once

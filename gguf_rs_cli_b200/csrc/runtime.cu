@@ -32,3 +32,11 @@ GB_API int gb_sm_count() {
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
     return n;
 }
+
+// Programmatic dependent launch for the kernels that support it (on by default).
+static int g_pdl = 1;
+bool gb_pdl_enabled() { return g_pdl != 0; }
+GB_API int gb_set_pdl(int on) {
+    g_pdl = on;
+    return 0;
+}

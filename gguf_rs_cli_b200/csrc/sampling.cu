@@ -96,6 +96,8 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     __shared__ int chosen;
+    gb_grid_launch_dependents();
+    gb_grid_wait();
     int row = blockIdx.x, tid = threadIdx.x;
     int slot = slots[row];
     if (slot < 0) {
@@ -299,8 +301,8 @@ GB_API int gb_sample(float* logits, long long ld, int n, int V, const int* slots
     GB_REQUIRE(top_k >= 0 && top_p > 0.f && rep_penalty > 0.f, "gb_sample: bad parameters top_k=%d top_p=%g rep_penalty=%g",
                top_k, top_p, rep_penalty);
     if (n == 0) return 0;
-    sample_kernel<<<n, SM_THREADS, 0, stream>>>(logits, ld, V, slots, seeds, temperature, top_k, top_p, rep_penalty,
-                                               recent, count, out);
+    gb_launch(sample_kernel, dim3(n), dim3(SM_THREADS), 0, stream, logits, ld, V, slots, seeds, temperature, top_k, top_p,
+              rep_penalty, recent, count, out);
     GB_LAUNCH_OK("gb_sample");
     return 0;
 }

@@ -123,6 +123,7 @@ _P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_floa
 _SIGNATURES = {
     "gb_device_arch": [],
     "gb_sm_count": [],
+    "gb_set_pdl": [_I],
     "gb_embed": [_P, _I, _P, _I, _I, _I, _P, _P],
     "gb_add_rmsnorm": [_P, _P, _I, _I, _L, _P, _I, _I, _P, _I, _F, _P, _I, _I, _P],
     "gb_rope_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _P],
@@ -132,6 +133,7 @@ _SIGNATURES = {
     "gb_sample": [_P, _L, _I, _I, _P, _P, _F, _I, _F, _F, _P, _P, _P, _P],
     "gb_gemm_tc": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _I, _P],
     "gb_gemm_tc_tile": [_I],
+    "gb_gemm_tc_set_splits": [_I],
     "gb_gemm_tc_splits": [_I, _I, _I, _I],
     "gb_gemm_tc_scratch_floats": [_I, _I, _I, _I],
     "gb_gemm_tc_supported": [_P, _L, _P, _L, _I],
