@@ -168,9 +168,10 @@ GB_API int gb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_de
 }
 
 // ------------------------------------------------ rotation + cache write
-// One block per (token, head): the first nh blocks of a token rotate its q heads in place,
-// the next nkv rotate a k head into the cache, the last nkv copy a v head into the cache.
-// Each thread handles one pair (or two plain elements).  Angles are position * inv_freq[i]
+// One block per (token, group of heads): heads 0..nh-1 of a token are its q heads, rotated in
+// place; the next nkv its k heads, rotated into the cache; the last nkv its v heads, copied into
+// the cache.  Each thread handles one pair (or two plain elements) of every head of its block;
+// few tokens get one head per block (more blocks in flight), many tokens several.  Angles are position * inv_freq[i]
 // in 32-bit with the accurate sincosf.  pairing 0: (i, i + rot/2); pairing 1: (2i, 2i+1).
 // Dimensions beyond rotary_dim pass through.  Tokens of padding (seq_of < 0) are skipped.
 constexpr int ROPE_MAX_HALF = 256;
@@ -180,54 +181,46 @@ __global__ void rope_kv_write_kernel(void* __restrict__ q, const void* __restric
                                      const float* __restrict__ inv_freq, const int* __restrict__ seq_of,
                                      const int* __restrict__ pos, const int* __restrict__ table, int table_width,
                                      int ring_pages, void* __restrict__ kcache, void* __restrict__ vcache,
-                                     int cache_dtype) {
+                                     int cache_dtype, int heads_per_block) {
     gb_grid_launch_dependents();
     gb_grid_wait();
-    const int t = blockIdx.x, head = blockIdx.y;
+    const int t = blockIdx.x;
     const int b = seq_of[t];
     if (b < 0) return;
     const int p = pos[t];
     const int half = inv_freq ? rotary_dim / 2 : 0;
     const size_t row = size_t(t) * size_t(ld);
     const int i = threadIdx.x;                         // pair index, or element pair index beyond the rotation
-    const int pairs = hd / 2;
-    if (i >= pairs) return;
-    if (head < nh) {
-        if (!q || i >= half) return;                   // q's unrotated dimensions stay as they are
-        float sn, cs;
-        sincosf(float(p) * inv_freq[i], &sn, &cs);
-        const int d0 = pairing ? 2 * i : i, d1 = pairing ? 2 * i + 1 : i + half;
-        const size_t o = row + size_t(head) * hd;
-        const float x0 = gb_load(q, dtype, o + d0), x1 = gb_load(q, dtype, o + d1);
-        gb_store(q, dtype, o + d0, x0 * cs - x1 * sn);
-        gb_store(q, dtype, o + d1, x0 * sn + x1 * cs);
-        return;
-    }
-    if (!k) return;
-    const int* trow = table + size_t(b) * table_width;
-    if (head < nh + nkv) {
-        const int g = head - nh;
-        const size_t o = row + size_t(g) * hd;
-        const size_t c = gb_kv_offset(trow, ring_pages, p, g, nkv, hd);
-        if (i < half) {
-            float sn, cs;
-            sincosf(float(p) * inv_freq[i], &sn, &cs);
-            const int d0 = pairing ? 2 * i : i, d1 = pairing ? 2 * i + 1 : i + half;
+    if (i >= hd / 2) return;
+    float sn = 0.f, cs = 1.f;
+    if (i < half) sincosf(float(p) * inv_freq[i], &sn, &cs);     // one angle serves every head of the block
+    const int d0 = i < half ? (pairing ? 2 * i : i) : 2 * i;
+    const int d1 = i < half ? (pairing ? 2 * i + 1 : i + half) : 2 * i + 1;
+    const int total = k ? nh + 2 * nkv : nh;
+    const int head_end = min(total, (blockIdx.y + 1) * heads_per_block);
+    const int* trow = k ? table + size_t(b) * table_width : nullptr;
+    for (int head = blockIdx.y * heads_per_block; head < head_end; ++head) {
+        if (head < nh) {
+            if (!q || i >= half) continue;             // q's unrotated dimensions stay as they are
+            const size_t o = row + size_t(head) * hd;
+            const float x0 = gb_load(q, dtype, o + d0), x1 = gb_load(q, dtype, o + d1);
+            gb_store(q, dtype, o + d0, x0 * cs - x1 * sn);
+            gb_store(q, dtype, o + d1, x0 * sn + x1 * cs);
+        } else if (head < nh + nkv) {
+            const int g = head - nh;
+            const size_t o = row + size_t(g) * hd;
+            const size_t c = gb_kv_offset(trow, ring_pages, p, g, nkv, hd);
             const float x0 = gb_load(k, dtype, o + d0), x1 = gb_load(k, dtype, o + d1);
-            gb_store(kcache, cache_dtype, c + d0, x0 * cs - x1 * sn);
+            gb_store(kcache, cache_dtype, c + d0, x0 * cs - x1 * sn);     // beyond the rotation: cs = 1, sn = 0
             gb_store(kcache, cache_dtype, c + d1, x0 * sn + x1 * cs);
-        } else {                                       // the tail beyond the rotation: dims 2*half + 2*(i-half), +1
-            const int d = 2 * i;
-            gb_store(kcache, cache_dtype, c + d, gb_load(k, dtype, o + d));
-            gb_store(kcache, cache_dtype, c + d + 1, gb_load(k, dtype, o + d + 1));
+        } else {
+            const int g = head - nh - nkv;
+            const size_t o = row + size_t(g) * hd;
+            const size_t c = gb_kv_offset(trow, ring_pages, p, g, nkv, hd);
+            gb_store(vcache, cache_dtype, c + 2 * i, gb_load(v, dtype, o + 2 * i));
+            gb_store(vcache, cache_dtype, c + 2 * i + 1, gb_load(v, dtype, o + 2 * i + 1));
         }
-        return;
     }
-    const int g = head - nh - nkv;
-    const size_t o = row + size_t(g) * hd;
-    const size_t c = gb_kv_offset(trow, ring_pages, p, g, nkv, hd);
-    gb_store(vcache, cache_dtype, c + 2 * i, gb_load(v, dtype, o + 2 * i));
-    gb_store(vcache, cache_dtype, c + 2 * i + 1, gb_load(v, dtype, o + 2 * i + 1));
 }
 
 // q, k, v: first elements of the q, k and v parts of token 0's row; rows are `ld` elements
@@ -246,9 +239,11 @@ GB_API int gb_rope_kv_write(void* q, const void* k, const void* v, int dtype, lo
     GB_REQUIRE(nh + 2 * nkv <= 65535, "gb_rope_kv_write: too many heads");
     if (T == 0) return 0;
     int threads = ((hd / 2 + 31) / 32) * 32;
-    dim3 grid(T, k ? nh + 2 * nkv : nh);
+    int total = k ? nh + 2 * nkv : nh;
+    int heads_per_block = T >= 512 ? 8 : 1;
+    dim3 grid(T, (total + heads_per_block - 1) / heads_per_block);
     gb_launch(rope_kv_write_kernel, grid, dim3(threads), 0, stream, q, k, v, dtype, ld, nh, nkv, hd, rotary_dim, pairing, inv_freq,
-              seq_of, pos, table, table_width, ring_pages, kcache, vcache, cache_dtype);
+              seq_of, pos, table, table_width, ring_pages, kcache, vcache, cache_dtype, heads_per_block);
     GB_LAUNCH_OK("gb_rope_kv_write");
     return 0;
 }

@@ -7,10 +7,12 @@
 // uses 128x256 tiles; both operands are K-major, as the model folder stores W [out,in]
 // (src/tensor/dequant.rs:258-259) and activations are [tokens, in].
 //
-// One CTA per (feature tile, token tile, K split), 6 warps: warp 0 issues TMA loads of
+// Persistent CTAs (at most as many as fit the device at once) take units of work (feature
+// tile, token tile, K split) in turn.  6 warps: warp 0 issues TMA loads of
 // 128-byte-swizzled [rows x 64] bf16 tiles into a ring of shared-memory stages, warp 1
-// owns the TMEM allocation and issues the MMAs (one thread), warps 2..5 read the
-// accumulator back (each its quarter of the 128 lanes) and store.  Out-of-range rows
+// owns the TMEM allocation and issues the MMAs (one thread) into one of two accumulators,
+// warps 2..5 read the other accumulator back (each its quarter of the 128 lanes) and
+// store, so the epilogue of one unit runs under the main loop of the next.  Out-of-range rows
 // and the K tail are zero-filled by TMA, so any T, any N, and any K that is a multiple
 // of 8 (16-byte row pitch) work; other sizes are refused and the caller falls back to
 // the CUDA-core kernel.
@@ -42,7 +44,7 @@ template <int BN> struct TileCfg {
     // no idle half wave when there are between one and two tiles per SM)
     static constexpr int STAGES = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 4 : BN >= 32 ? 5 : 6;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;     // + slack to align the ring to 1024 bytes
-    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators
 };
 
 struct TcParams {
@@ -55,7 +57,24 @@ struct TcParams {
     int out_dtype, bias_dtype;
     int T, N, K, splits;
     int swiglu, N_out;    // swiglu: W's rows alternate gate, up; out has N_out features
+    int sms;
 };
+
+// One unit of work: a tile of 128 features x BN tokens over one split of K.  Units are numbered
+// unit = (feature tile * token tiles + token tile) * splits + split, and CTA c takes units c, c + grid, ...
+struct Unit {
+    int tile, split, n0, t0, kb_begin, kb_end;
+};
+__device__ __forceinline__ Unit unit_of(int u, const TcParams& p, int BN, int token_tiles, int kb_total) {
+    Unit w;
+    w.tile = u / p.splits;
+    w.split = u - w.tile * p.splits;
+    w.n0 = (w.tile / token_tiles) * BM;
+    w.t0 = (w.tile % token_tiles) * BN;
+    w.kb_begin = int((long long)w.split * kb_total / p.splits);
+    w.kb_end = int((long long)(w.split + 1) * kb_total / p.splits);
+    return w;
+}
 
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
@@ -63,19 +82,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     using Cfg = TileCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ uint64_t full_bar[Cfg::STAGES], empty_bar[Cfg::STAGES], acc_bar;
+    __shared__ uint64_t full_bar[Cfg::STAGES], empty_bar[Cfg::STAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base;
     __shared__ int last_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BM, t0 = blockIdx.y * BN, split = blockIdx.z;
     const int kb_total = (p.K + BK - 1) / BK;
-    const int kb_begin = int((long long)split * kb_total / p.splits);
-    const int kb_end = int((long long)(split + 1) * kb_total / p.splits);
+    const int token_tiles = (p.T + BN - 1) / BN;
+    const int n_units = ((p.N + BM - 1) / BM) * token_tiles * p.splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(&acc_bar, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
         fence_barrier_init();
         prefetch_tensormap(&map_w);
         prefetch_tensormap(&map_x);
@@ -92,141 +110,172 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---- producer: TMA loads into the ring.  The weights do not depend on the kernel before
-            // this one, so the first round of weight tiles is requested at once; the activations only
-            // after that kernel has finished.
-            const int pre = min(Cfg::STAGES, kb_end - kb_begin);
-            for (int i = 0; i < pre; ++i) {
-                mbar_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
-                tma_load_2d(ring + i * Cfg::STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full_bar[i]);
+            // ---- producer: TMA loads into the ring, unit after unit without a pause.  The weights do not
+            // depend on the kernel before this one, so the first round of weight tiles is requested at
+            // once; the activations only after that kernel has finished.
+            int issued = 0;
+            for (int u = blockIdx.x; u < n_units && issued < Cfg::STAGES; u += gridDim.x) {
+                Unit w = unit_of(u, p, BN, token_tiles, kb_total);
+                for (int kb = w.kb_begin; kb < w.kb_end && issued < Cfg::STAGES; ++kb, ++issued) {
+                    mbar_expect_tx(&full_bar[issued], Cfg::STAGE_BYTES);
+                    tma_load_2d(ring + issued * Cfg::STAGE_BYTES, &map_w, kb * BK, w.n0, &full_bar[issued]);
+                }
             }
+            const int pre = issued;
             gb_grid_wait();
-            for (int i = 0; i < pre; ++i)
-                tma_load_2d(ring + i * Cfg::STAGE_BYTES + A_BYTES, &map_x, (kb_begin + i) * BK, t0, &full_bar[i]);
-            int stage = pre % Cfg::STAGES;
-            uint32_t phase = pre == Cfg::STAGES ? 1 : 0;
-            for (int kb = kb_begin + pre; kb < kb_end; ++kb) {
-                if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { atomicExch(p.status, 1); break; }
-                uint8_t* a = ring + stage * Cfg::STAGE_BYTES;
-                mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
-                tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[stage]);
-                tma_load_2d(a + A_BYTES, &map_x, kb * BK, t0, &full_bar[stage]);
-                if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
+            int item = 0, stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                Unit w = unit_of(u, p, BN, token_tiles, kb_total);
+                for (int kb = w.kb_begin; kb < w.kb_end; ++kb, ++item) {
+                    uint8_t* a = ring + stage * Cfg::STAGE_BYTES;
+                    if (item >= pre) {
+                        if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { atomicExch(p.status, 1); ok = false; break; }
+                        mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+                        tma_load_2d(a, &map_w, kb * BK, w.n0, &full_bar[stage]);
+                    }
+                    tma_load_2d(a + A_BYTES, &map_x, kb * BK, w.t0, &full_bar[stage]);
+                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // ---- MMA issue
+            // ---- MMA issue: two accumulators in TMEM, so that unit j+1 is multiplied while unit j is stored
             constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
-            int stage = 0;
+            int stage = 0, j = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int kb = kb_begin; kb < kb_end; ++kb) {
-                if (!mbar_wait(&full_bar[stage], phase)) { atomicExch(p.status, 2); ok = false; break; }
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++j) {
+                Unit w = unit_of(u, p, BN, token_tiles, kb_total);
+                const int buf = j & 1;
+                if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1)) { atomicExch(p.status, 4); ok = false; break; }
                 tc_fence_after();
-                uint32_t a = smem_u32(ring + stage * Cfg::STAGE_BYTES);
-                uint32_t b = a + A_BYTES;
+                const uint32_t acc = tmem_d + buf * BN;
+                for (int kb = w.kb_begin; kb < w.kb_end; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase)) { atomicExch(p.status, 2); ok = false; break; }
+                    tc_fence_after();
+                    uint32_t a = smem_u32(ring + stage * Cfg::STAGE_BYTES);
+                    uint32_t b = a + A_BYTES;
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)
-                    mma_f16(tmem_d, smem_desc_sw128(a + k * UMMA_K * 2), smem_desc_sw128(b + k * UMMA_K * 2), idesc,
-                            (kb > kb_begin || k > 0) ? 1u : 0u);
-                mma_commit(&empty_bar[stage]);      // the stage is free once these MMAs have read it
-                if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        mma_f16(acc, smem_desc_sw128(a + k * UMMA_K * 2), smem_desc_sw128(b + k * UMMA_K * 2), idesc,
+                                (kb > w.kb_begin || k > 0) ? 1u : 0u);
+                    mma_commit(&empty_bar[stage]);      // the stage is free once these MMAs have read it
+                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
+                }
+                mma_commit(&acc_full[buf]);             // this unit's accumulator is complete
             }
-            (void)ok;
-            mma_commit(&acc_bar);                   // the accumulator is complete
         }
     } else {
         // ---- epilogue: 4 warps, warp w reads TMEM lanes 32*(w%4) .. +31
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;        // feature within the tile = TMEM lane
-        const int n = n0 + row;
-        const bool waited = mbar_wait(&acc_bar, 0);
-        gb_grid_wait();                              // before anything is written that the kernel before may still read
-        if (!waited && lane == 0) atomicExch(p.status, 3);
-        tc_fence_after();
-        const uint32_t taddr = tmem_d + (uint32_t(quarter * 32) << 16);
-        const int cols = min(BN, p.T - t0);         // valid tokens of this tile
-        float bias = 0.f;
-        if (p.bias && n < p.N) bias = gb_load(p.bias, p.bias_dtype, n);
-        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-        const float* partials = p.scratch + size_t(tile) * p.splits * (BN * BM);
-        bool finish = true;                          // does this CTA write the tile's result?
-        if (p.splits > 1) {
-            float* mine = p.scratch + (size_t(tile) * p.splits + split) * (BN * BM);
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (c0 >= cols) break;               // uniform over the warp
-                float v[16];
-                tmem_ld16(taddr + c0, v);
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (c0 + j < cols) mine[(c0 + j) * BM + row] = v[j];
+        bool first = true;
+        int j = 0;
+        for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
+            const Unit w = unit_of(u, p, BN, token_tiles, kb_total);
+            const int buf = j & 1;
+            const int n = w.n0 + row;
+            const bool waited = mbar_wait(&acc_full[buf], (j >> 1) & 1);
+            if (first) { gb_grid_wait(); first = false; }    // before anything is written that the kernel before may still read
+            if (!waited) {                               // the error path: give up on the remaining units too
+                if (lane == 0) atomicExch(p.status, 3);
+                break;
             }
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) {
-                int old = atomicAdd(&p.counters[tile], 1);
-                last_flag = (old == p.splits - 1);
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            finish = last_flag != 0;
-            if (finish) __threadfence();
-        }
-        if (finish) {
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (c0 >= cols) break;
-                float v[16];
-                if (p.splits == 1) {
+            tc_fence_after();
+            const uint32_t taddr = tmem_d + (uint32_t(quarter * 32) << 16) + buf * BN;
+            const int cols = min(BN, p.T - w.t0);       // valid tokens of this tile
+            float bias = 0.f;
+            if (p.bias && n < p.N) bias = gb_load(p.bias, p.bias_dtype, n);
+            const float* partials = p.scratch + size_t(w.tile) * p.splits * (BN * BM);
+            bool finish = true;                          // does this CTA write the tile's result?
+            if (p.splits > 1) {
+                float* mine = p.scratch + (size_t(w.tile) * p.splits + w.split) * (BN * BM);
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (c0 >= cols) break;               // uniform over the warp
+                    float v[16];
                     tmem_ld16(taddr + c0, v);
-                } else {
-                    // the splits' partial sums in ascending order; 4 columns x 4 splits of loads in flight
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
-#pragma unroll
-                    for (int j0 = 0; j0 < 16; j0 += 4) {
-                        if (c0 + j0 >= cols) break;
-                        for (int s0 = 0; s0 < p.splits; s0 += 4) {
-                            float ld[4][4];
-#pragma unroll
-                            for (int si = 0; si < 4; ++si)
-#pragma unroll
-                                for (int j = 0; j < 4; ++j)
-                                    ld[si][j] = (s0 + si < p.splits && c0 + j0 + j < cols)
-                                                    ? __ldcg(partials + size_t(s0 + si) * (BN * BM) + (c0 + j0 + j) * BM + row)
-                                                    : 0.f;
-#pragma unroll
-                            for (int si = 0; si < 4; ++si)
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) v[j0 + j] += ld[si][j];
-                        }
-                    }
+                    for (int jj = 0; jj < 16; ++jj)
+                        if (c0 + jj < cols) mine[(c0 + jj) * BM + row] = v[jj];
                 }
-                if (!p.swiglu) {
-                    if (n < p.N && waited) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (c0 + j < cols) gb_store(p.out, p.out_dtype, size_t(t0 + c0 + j) * p.ldo + n, v[j] + bias);
-                    }
-                } else {
-                    // even rows of the tile are gate features, odd rows the matching up features: the two
-                    // lanes of a pair swap halves of their 16 columns, the even lane finishes columns
-                    // 0..7 and the odd lane columns 8..15 of silu(gate) * up
-                    const bool odd = lane & 1;
-                    float other[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) other[j] = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[8 + j], 1);
-                    const int f = blockIdx.x * 64 + (row >> 1);      // output feature
-                    if (f < p.N_out && waited) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float gte = odd ? other[j] : v[j], u = odd ? v[8 + j] : other[j];
-                            const int c = c0 + (odd ? 8 : 0) + j;
-                            if (c < cols) gb_store(p.out, p.out_dtype, size_t(t0 + c) * p.ldo + f, gte / (1.f + expf(-gte)) * u);
-                        }
-                    }
+                tc_fence_before();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);     // the accumulator may be overwritten
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) {
+                    int old = atomicAdd(&p.counters[w.tile], 1);
+                    last_flag = (old == p.splits - 1);
                 }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                finish = last_flag != 0;
+                if (finish) __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag may be written again for the next unit
             }
-            if (p.splits > 1 && threadIdx.x == 64) p.counters[tile] = 0;       // ready for the next launch
+            if (finish) {
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (c0 >= cols) break;
+                    float v[16];
+                    if (p.splits == 1) {
+                        tmem_ld16(taddr + c0, v);
+                    } else {
+                        // the splits' partial sums in ascending order; 4 columns x 4 splits of loads in flight
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) v[jj] = 0.f;
+#pragma unroll
+                        for (int j0 = 0; j0 < 16; j0 += 4) {
+                            if (c0 + j0 >= cols) break;
+                            for (int s0 = 0; s0 < p.splits; s0 += 4) {
+                                float ld[4][4];
+#pragma unroll
+                                for (int si = 0; si < 4; ++si)
+#pragma unroll
+                                    for (int jj = 0; jj < 4; ++jj)
+                                        ld[si][jj] = (s0 + si < p.splits && c0 + j0 + jj < cols)
+                                                         ? __ldcg(partials + size_t(s0 + si) * (BN * BM) + (c0 + j0 + jj) * BM + row)
+                                                         : 0.f;
+#pragma unroll
+                                for (int si = 0; si < 4; ++si)
+#pragma unroll
+                                    for (int jj = 0; jj < 4; ++jj) v[j0 + jj] += ld[si][jj];
+                            }
+                        }
+                    }
+                    if (!p.swiglu) {
+                        if (n < p.N && waited) {
+#pragma unroll
+                            for (int jj = 0; jj < 16; ++jj)
+                                if (c0 + jj < cols)
+                                    gb_store(p.out, p.out_dtype, size_t(w.t0 + c0 + jj) * p.ldo + n, v[jj] + bias);
+                        }
+                    } else {
+                        // even rows of the tile are gate features, odd rows the matching up features: the two
+                        // lanes of a pair swap halves of their 16 columns, the even lane finishes columns
+                        // 0..7 and the odd lane columns 8..15 of silu(gate) * up
+                        const bool odd = lane & 1;
+                        float other[8];
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) other[jj] = __shfl_xor_sync(0xffffffffu, odd ? v[jj] : v[8 + jj], 1);
+                        const int f = (w.n0 >> 1) + (row >> 1);          // output feature
+                        if (f < p.N_out && waited) {
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) {
+                                const float gte = odd ? other[jj] : v[jj], up = odd ? v[8 + jj] : other[jj];
+                                const int c = c0 + (odd ? 8 : 0) + jj;
+                                if (c < cols)
+                                    gb_store(p.out, p.out_dtype, size_t(w.t0 + c) * p.ldo + f, gte / (1.f + expf(-gte)) * up);
+                            }
+                        }
+                    }
+                }
+                if (p.splits > 1 && threadIdx.x == 64) p.counters[w.tile] = 0;       // ready for the next launch
+            }
+            if (p.splits == 1) {
+                tc_fence_before();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);     // all of this warp's TMEM loads are done
+            }
         }
     }
     tc_fence_before();
@@ -313,7 +362,9 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, c
             return gb_fail("gb_gemm_tc: cannot get %d bytes of shared memory", Cfg::SMEM);
         configured = true;
     }
-    dim3 grid((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, p.splits);
+    long long units = (long long)((p.N + BM - 1) / BM) * ((p.T + BN - 1) / BN) * p.splits;
+    int slots = (Cfg::SMEM <= 112 * 1024 ? 2 : 1) * p.sms;        // CTAs that can be resident at once
+    dim3 grid((unsigned)(units < slots ? units : slots));
     gb_launch(gemm_tc_kernel<BN>, grid, dim3(TC_THREADS), Cfg::SMEM, stream, mw, mx, p);
     GB_LAUNCH_OK("gb_gemm_tc");
     return 0;
@@ -324,12 +375,20 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, c
 // Tokens per tile for T tokens.
 GB_API int gb_gemm_tc_tile(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 
+// The same with the number of output features known: a few hundred tokens with few features would
+// give 256-token tiles for less than half of the SMs, so they take 128-token tiles.
+static int tile_for(int T, int N, int sms) {
+    int bn = gb_gemm_tc_tile(T);
+    if (bn == 256 && 2LL * ((N + BM - 1) / BM) * ((T + 255) / 256) <= sms) bn = 128;
+    return bn;
+}
+
 // How many ways the kernel would split K for these sizes on a device with `sms` SMs (1 = no scratch needed).
 static int g_split_override = 0;      // > 0: every product uses this many splits (tuning aid)
 GB_API int gb_gemm_tc_set_splits(int s) { g_split_override = s; return 0; }
 
 GB_API int gb_gemm_tc_splits(int T, int N, int K, int sms) {
-    int bn = gb_gemm_tc_tile(T);
+    int bn = tile_for(T, N, sms);
     if (g_split_override > 0) {
         int kb0 = (K + BK - 1) / BK;
         return g_split_override > kb0 ? kb0 : g_split_override;
@@ -348,7 +407,7 @@ GB_API int gb_gemm_tc_splits(int T, int N, int K, int sms) {
 GB_API long long gb_gemm_tc_scratch_floats(int T, int N, int K, int sms) {
     int s = gb_gemm_tc_splits(T, N, K, sms);
     if (s == 1) return 0;
-    int bn = gb_gemm_tc_tile(T);
+    int bn = tile_for(T, N, sms);
     long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
     return tiles * s * bn * BM;
 }
@@ -379,15 +438,14 @@ GB_API int gb_gemm_tc(const void* X, long long ldx, const void* W, long long ldw
                K, ldx, ldw);
     if (T == 0) return 0;
     if (ensure_status()) return 1;
-    int bn = gb_gemm_tc_tile(T);
+    int bn = tile_for(T, N, sms);
     TcParams p;
     p.out = out; p.bias = bias; p.scratch = scratch; p.counters = counters; p.status = g_status_dev;
     p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype; p.T = T; p.N = N; p.K = K;
     p.splits = (scratch && counters) ? gb_gemm_tc_splits(T, N, K, sms) : 1;
-    p.swiglu = swiglu_features > 0; p.N_out = swiglu_features;
+    p.swiglu = swiglu_features > 0; p.N_out = swiglu_features; p.sms = sms;
     long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
     GB_REQUIRE(p.splits == 1 || tiles <= n_counters, "gb_gemm_tc: %lld tiles need as many counters, %d given", tiles, n_counters);
-    GB_REQUIRE((T + bn - 1) / bn <= 65535, "gb_gemm_tc: T=%d is too many rows for one launch", T);
     CUtensorMap mw, mx;
     if (tensor_map_2d(W, N, K, ldw, BM, &mw)) return 1;
     if (tensor_map_2d(X, T, K, ldx, bn, &mx)) return 1;
@@ -480,8 +538,7 @@ GB_API int gb_gemm_tc_noalloc(const void* X, long long ldx, const void* W, long 
     if (cudaGetDevice(&dev) != cudaSuccess) return gb_fail("gb_gemm_tc_noalloc: no current device");
     NoallocDevice* d = nullptr;
     if (noalloc_setup(dev, &d)) return 1;
-    const int bn = gb_gemm_tc_tile(T);
-    GB_REQUIRE((T + bn - 1) / bn <= 65535, "gb_gemm_tc_noalloc: T=%d is too many rows for one launch", T);
+    const int bn = tile_for(T, N, d->sms);
     const long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
     const int splits = gb_gemm_tc_splits(T, N, K, d->sms);
     if (splits > 1) {
@@ -497,7 +554,7 @@ GB_API int gb_gemm_tc_noalloc(const void* X, long long ldx, const void* W, long 
     TcParams p;
     p.out = out; p.bias = bias; p.scratch = d->scratch; p.counters = d->counters; p.status = d->status;
     p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype; p.T = T; p.N = N; p.K = K;
-    p.splits = splits; p.swiglu = 0; p.N_out = 0;
+    p.splits = splits; p.swiglu = 0; p.N_out = 0; p.sms = d->sms;
     CUtensorMap mw, mx;
     if (encode_map_2d(W, N, K, ldw, BM, &mw)) return 1;
     if (encode_map_2d(X, T, K, ldx, bn, &mx)) return 1;

@@ -222,10 +222,13 @@ def attention_prefill_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim:
 def attention_prefill_tiles(qlens) -> list:
     """(sequence row, first query) of every tile of queries, flat, for the step's sequences."""
     bm = native.library().gb_attention_prefill_tile()
+    tiles = [(b, q0) for b, n in enumerate(qlens) for q0 in range(0, n, bm)]
+    # the later queries of a sequence see more keys: their tiles start first, so that the last CTAs to
+    # start are the short ones (the order changes no result)
+    tiles.sort(key=lambda t: -t[1])
     flat = []
-    for b, n in enumerate(qlens):
-        for q0 in range(0, n, bm):
-            flat += [b, q0]
+    for b, q0 in tiles:
+        flat += [b, q0]
     return flat
 
 

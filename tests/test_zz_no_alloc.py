@@ -27,6 +27,8 @@ def entry_point():
     fn.restype = I
     lib.gb_last_error.restype = ctypes.c_char_p
     lib.gb_gemm_tc_noalloc_status.restype = I
+    lib.gb_gemm_tc_scratch_floats.restype = L
+    lib.gb_gemm_tc_scratch_floats.argtypes = [I, I, I, I]
     return lib, fn
 
 
@@ -69,7 +71,8 @@ def test_no_alloc_entry_point_gives_the_ordinary_result_twice(T, N, K, out_dtype
 
 def test_no_alloc_entry_point_refuses_what_its_scratch_cannot_hold():
     lib, fn = entry_point()
-    T, N, K = 256, 4096, 8192                                # 32 tiles x 4 splits x 256 x 128 floats = 4 Mi > 2 Mi floats
+    T, N, K = 128, 8192 + 128, 8192                          # 65 tiles x 2 splits x 128 x 128 floats > 2 Mi floats
+    assert lib.gb_gemm_tc_scratch_floats(T, N, K, lib.gb_sm_count()) > 2 * 1024 * 1024
     x = torch.zeros(T, K, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(N, K, dtype=torch.bfloat16, device=DEV)
     out = torch.zeros(T, N, dtype=torch.bfloat16, device=DEV)
