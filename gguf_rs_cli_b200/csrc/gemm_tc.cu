@@ -364,7 +364,9 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, c
     }
     long long units = (long long)((p.N + BM - 1) / BM) * ((p.T + BN - 1) / BN) * p.splits;
     int slots = (Cfg::SMEM <= 112 * 1024 ? 2 : 1) * p.sms;        // CTAs that can be resident at once
-    dim3 grid((unsigned)(units < slots ? units : slots));
+    // every CTA gets the same number of units (or one less): rounds = ceil(units / slots), grid = ceil(units / rounds)
+    long long rounds = (units + slots - 1) / slots;
+    dim3 grid((unsigned)((units + rounds - 1) / rounds));
     gb_launch(gemm_tc_kernel<BN>, grid, dim3(TC_THREADS), Cfg::SMEM, stream, mw, mx, p);
     GB_LAUNCH_OK("gb_gemm_tc");
     return 0;
