@@ -5,6 +5,7 @@ from typing import List, Sequence
 
 import torch
 
+from .. import kernels
 from ..cache.pool import pages_for
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
@@ -76,7 +77,10 @@ class EngineBackend:
         runs the same kernels eagerly (and sizes every buffer), the second captures."""
         from .. import native
         eng, n = self.engine, len(slots)
-        key = (bucket_of(n), params.temperature, params.top_k, params.top_p, params.rep_penalty)
+        # the attention kernels' page splits are fixed in a captured graph: one graph per class of length
+        longest = max(eng.cache.length(s) for s in slots) + 1
+        key = (bucket_of(n), kernels.decode_split_class(longest), params.temperature, params.top_k, params.top_p,
+               params.rep_penalty)
         dg = self._graphs.get(key)
         if dg is None:
             dg = self._graphs[key] = DecodeGraph(eng, key[0])

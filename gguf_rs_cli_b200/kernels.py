@@ -180,6 +180,22 @@ def attention_decode_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim: 
     return bool(native.library().gb_attention_decode_supported(head_dim, dtype_code(kcache), dtype_code(q)))
 
 
+def decode_split_class(max_kv: int) -> int:
+    """Sequences up to max_kv positions long want this many splits of their pages, if the
+    batch is too small to fill the device without (a captured graph is made per class)."""
+    return max(1, min(32, ((max_kv + 63) // 64) // 16))
+
+
+def decode_splits(T: int, n_heads: int, n_kv_heads: int, max_kv: int, sms: int, mma: bool) -> int:
+    """Splits of each sequence's pages for a decode step: at least 16 pages per split (merging
+    the splits costs more than it saves below that), and no more than it takes to give every SM
+    two CTAs."""
+    group = n_heads // n_kv_heads
+    tile = 16 if mma else (8 if group >= 8 else 4 if group > 2 else group)
+    ctas = T * n_kv_heads * ((group + tile - 1) // tile)
+    return max(1, min(decode_split_class(max_kv), (2 * sms + ctas - 1) // ctas))
+
+
 def attention_decode_mma_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> bool:
     return bool(native.library().gb_attention_decode_mma_supported(head_dim, dtype_code(kcache), dtype_code(q)))
 
@@ -187,7 +203,7 @@ def attention_decode_mma_supported(q: torch.Tensor, kcache: torch.Tensor, head_d
 def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                      seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, ring_pages: int,
                      kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float,
-                     splits: Optional[int] = None, mma: Optional[bool] = None) -> torch.Tensor:
+                     splits: Optional[int] = None, mma: Optional[bool] = None, max_kv: Optional[int] = None) -> torch.Tensor:
     """One token per sequence over the bf16 cache; all heads of a group share one pass over
     the keys and values.  mma: the tensor-core kernel (head sizes 64 and 128; the default
     where it fits) or the CUDA-core one (any head size that is a multiple of 16)."""
@@ -201,7 +217,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_head
         mma = attention_decode_mma_supported(q, kcache, head_dim)
     entry = "gb_attention_decode_mma" if mma else "gb_attention_decode"
     if splits is None:
-        splits = getattr(lib, entry + "_splits")(T, n_heads, n_kv_heads, sc.sms, table.shape[1])
+        splits = decode_splits(T, n_heads, n_kv_heads, max_kv if max_kv else table.shape[1] * 64, sc.sms, mma)
     need = lib.gb_attention_decode_scratch_floats(T, n_heads, head_dim, splits)
     scratch = counters = None
     if need:
@@ -275,7 +291,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int,
     """Attention of one step over the cache; picks the kernel for the step's shape."""
     if ctx.decode and attention_decode_supported(q, kcache, head_dim):
         return attention_decode(q, out, n_heads, n_kv_heads, head_dim, ctx.seq_of, ctx.pos, table, ring_pages, kcache,
-                                vcache, window, scale)
+                                vcache, window, scale, max_kv=min(ctx.max_kv, window) if window else ctx.max_kv)
     if not ctx.decode and ctx.tiles is not None and attention_prefill_supported(q, kcache, head_dim):
         return attention_prefill(q, out, n_heads, n_kv_heads, head_dim, ctx.tiles, ctx.cu, ctx.starts, ctx.qlens, table,
                                  ring_pages, kcache, vcache, window, scale)
