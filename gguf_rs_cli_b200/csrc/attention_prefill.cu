@@ -68,7 +68,7 @@ template <int HD> __device__ __forceinline__ int swz(int row, int chunk) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(ApParams p) {
+__global__ void __launch_bounds__(AP_THREADS, 2) attention_prefill_kernel(ApParams p) {
     constexpr int CH = HD / 8;            // 16-byte chunks per row
     constexpr int KS = HD / 16;           // k-steps of Q.K^T
     constexpr int NT = AP_BN / 8;         // score n-tiles per warp (8 keys each)
@@ -80,8 +80,10 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(ApParams 
 
     gb_grid_launch_dependents();
     gb_grid_wait();
-    const int b = p.tiles[2 * blockIdx.x], q0 = p.tiles[2 * blockIdx.x + 1];
-    const int h = blockIdx.y, g = h / (p.nh / p.nkv);
+    // blockIdx.x (which varies fastest in the order CTAs start) is the head, blockIdx.y the tile: all heads of
+    // the first tile in the caller's list start before any head of the second
+    const int b = p.tiles[2 * blockIdx.y], q0 = p.tiles[2 * blockIdx.y + 1];
+    const int h = blockIdx.x, g = h / (p.nh / p.nkv);
     const int start = p.starts[b], qlen = p.qlens[b], tok0 = p.cu[b] + q0;
     const int rows = min(AP_BM, qlen - q0);                   // valid queries of this tile
     const int last_pos = start + qlen - 1;                    // last position the cache holds for this sequence
@@ -123,7 +125,6 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(ApParams 
 #pragma unroll
     for (int i = 0; i < OT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-    unsigned qf[KS][4];
 
     for (int kb = kb_begin; kb < kb_end; ++kb) {
         const int buf = (kb - kb_begin) & 1;
@@ -131,12 +132,6 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(ApParams 
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        if (kb == kb_begin) {
-#pragma unroll
-            for (int k = 0; k < KS; ++k)
-                ldmatrix_x4(qf[k][0], qf[k][1], qf[k][2], qf[k][3],
-                            qs + swz<HD>(warp * 16 + (lane & 15), 2 * k + (lane >> 4)));
-        }
         const __nv_bfloat16* kt = ks + buf * AP_BN * HD;
         const __nv_bfloat16* vt = vs + buf * AP_BN * HD;
 
@@ -146,14 +141,18 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(ApParams 
         for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
         for (int k = 0; k < KS; ++k) {
+            // the query fragment is read from shared memory at every step: holding all of Q in registers
+            // would leave room for one CTA per SM only
+            unsigned qf[4];
+            ldmatrix_x4(qf[0], qf[1], qf[2], qf[3], qs + swz<HD>(warp * 16 + (lane & 15), 2 * k + (lane >> 4)));
 #pragma unroll
             for (int j2 = 0; j2 < NT / 2; ++j2) {
                 unsigned b0, b1, b2, b3;
                 // keys 16*j2 .. +15; lanes 0-7 / 8-15 / 16-23 / 24-31 address (keys 0-7, d lo), (keys 0-7, d hi),
                 // (keys 8-15, d lo), (keys 8-15, d hi)
                 ldmatrix_x4(b0, b1, b2, b3, kt + swz<HD>(j2 * 16 + (lane & 7) + ((lane >> 4) << 3), 2 * k + ((lane >> 3) & 1)));
-                mma_bf16(s[2 * j2], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b0, b1);
-                mma_bf16(s[2 * j2 + 1], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b2, b3);
+                mma_bf16(s[2 * j2], qf[0], qf[1], qf[2], qf[3], b0, b1);
+                mma_bf16(s[2 * j2 + 1], qf[0], qf[1], qf[2], qf[3], b2, b3);
             }
         }
         // ---- mask and online softmax (two rows per thread: r0 in c0,c1 and r1 in c2,c3)
@@ -237,7 +236,7 @@ template <int HD> int launch_ap(const ApParams& p, int n_tiles, cudaStream_t str
             return gb_fail("gb_attention_prefill: cannot get %d bytes of shared memory", SMEM);
         configured = true;
     }
-    gb_launch(attention_prefill_kernel<HD>, dim3(n_tiles, p.nh), dim3(AP_THREADS), SMEM, stream, p);
+    gb_launch(attention_prefill_kernel<HD>, dim3(p.nh, n_tiles), dim3(AP_THREADS), SMEM, stream, p);
     GB_LAUNCH_OK("gb_attention_prefill");
     return 0;
 }
@@ -257,7 +256,8 @@ GB_API int gb_attention_prefill(const void* q, long long ldq, void* out, long lo
                                 const int* table, int table_width, int ring_pages, const void* kcache,
                                 const void* vcache, int window, float scale, cudaStream_t stream) {
     GB_REQUIRE(gb_attention_prefill_supported(hd, GB_BF16, GB_BF16), "gb_attention_prefill: head_dim %d is not 64 or 128", hd);
-    GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && nh <= 65535, "gb_attention_prefill: bad head counts %d / %d", nh, nkv);
+    GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "gb_attention_prefill: bad head counts %d / %d", nh, nkv);
+    GB_REQUIRE(n_tiles <= 65535, "gb_attention_prefill: %d tiles of queries are too many for one launch", n_tiles);
     GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0, "gb_attention_prefill: bad cache geometry");
     GB_REQUIRE((ldq % 8) == 0 && (ldo % 2) == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(kcache) & 15) == 0 && (reinterpret_cast<uintptr_t>(vcache) & 15) == 0,
