@@ -379,9 +379,16 @@ GB_API int gb_gemm_tc_tile(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64
 
 // The same with the number of output features known: a few hundred tokens with few features would
 // give 256-token tiles for less than half of the SMs, so they take 128-token tiles.
+static int g_tile_override = 0;       // > 0: tokens per tile for every product (tuning aid)
+GB_API int gb_gemm_tc_set_tile(int bn) { g_tile_override = bn; return 0; }
+
 static int tile_for(int T, int N, int sms) {
+    if (g_tile_override > 0) return g_tile_override;
     int bn = gb_gemm_tc_tile(T);
     if (bn == 256 && 2LL * ((N + BM - 1) / BM) * ((T + 255) / 256) <= sms) bn = 128;
+    // a few dozen tokens and fewer feature tiles than SMs: two half-size token tiles give twice the units
+    // without splitting K further (measured faster at 32 and 64 tokens; the second read of W hits L2)
+    if (bn > 16 && bn <= 64 && (N + BM - 1) / BM < sms) bn /= 2;
     return bn;
 }
 
