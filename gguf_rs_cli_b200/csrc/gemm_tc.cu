@@ -61,7 +61,11 @@ struct TcParams {
 };
 
 // One unit of work: a tile of 128 features x BN tokens over one split of K.  Units are numbered
-// unit = (feature tile * token tiles + token tile) * splits + split, and CTA c takes units c, c + grid, ...
+// unit = tile * splits + split, and CTA c takes units c, c + grid, ...  Tiles are numbered so that the CTAs
+// running at one time share operands in L2: token tiles in groups of TILE_GROUP, inside a group feature tile
+// by feature tile with the group's token tiles innermost (many tokens: the group's activations stay in L2
+// while the weights stream; few tokens: one group, feature-major as the weights lie in memory).
+constexpr int TILE_GROUP = 16;
 struct Unit {
     int tile, split, n0, t0, kb_begin, kb_end;
 };
@@ -69,8 +73,14 @@ __device__ __forceinline__ Unit unit_of(int u, const TcParams& p, int BN, int to
     Unit w;
     w.tile = u / p.splits;
     w.split = u - w.tile * p.splits;
-    w.n0 = (w.tile / token_tiles) * BM;
-    w.t0 = (w.tile % token_tiles) * BN;
+    const int feature_tiles = (p.N + BM - 1) / BM;
+    const int per_group = TILE_GROUP * feature_tiles;
+    const int group = w.tile / per_group, r = w.tile - group * per_group;
+    const int group_start = group * TILE_GROUP;
+    const int group_size = min(TILE_GROUP, token_tiles - group_start);
+    const int ft = r / group_size;
+    w.n0 = ft * BM;
+    w.t0 = (group_start + (r - ft * group_size)) * BN;
     w.kb_begin = int((long long)w.split * kb_total / p.splits);
     w.kb_end = int((long long)(w.split + 1) * kb_total / p.splits);
     return w;
