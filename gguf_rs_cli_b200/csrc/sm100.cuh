@@ -109,6 +109,41 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// The reverse: 32 consecutive 32-bit columns of this thread's TMEM lane are written.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+          "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+          "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+          "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory operand descriptor: K-major tile whose rows are 128 bytes (64 bf16) with
 // the 128-byte swizzle; groups of 8 rows are 1024 bytes apart.  `addr` is a shared
 // address inside a 1024-byte-aligned tile; advancing it by 32 bytes steps 16 elements
@@ -123,6 +158,24 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return d;
 }
 
+// The same swizzle for an operand stored with its M or N index contiguous ("MN-major"): rows are K indices,
+// each row 128 bytes = 64 consecutive N (or M) elements; groups of 8 rows (8 K) are 1024 bytes apart and
+// blocks of 64 N elements `n_block_bytes` apart.  Advancing `addr` by 16 rows (2048 bytes) steps 16 along K.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t addr, uint32_t n_block_bytes) {
+    uint64_t d = 0;
+    d |= uint64_t((addr & 0x3FFFF) >> 4);
+    d |= uint64_t((n_block_bytes >> 4) & 0x3FFF) << 16;     // leading byte offset: next block of 64 elements along N
+    d |= uint64_t(1024 >> 4) << 32;                          // stride byte offset: next 8 rows along K
+    d |= uint64_t(1) << 46;
+    d |= uint64_t(2) << 61;
+    return d;
+}
+
+// Instruction descriptor of kind::f16 with B stored N-contiguous (A K-major).
+__host__ __device__ constexpr uint32_t instr_desc_bf16_b_mn(int M, int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+}
+
 // Instruction descriptor of kind::f16: bf16 x bf16 -> f32, both operands K-major, M x N tile.
 __host__ __device__ constexpr uint32_t instr_desc_bf16(int M, int N) {
     return (1u << 4)                  // D is f32
@@ -131,5 +184,9 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int M, int N) {
            | (uint32_t(N >> 3) << 17) // N / 8
            | (uint32_t(M >> 4) << 24);  // M / 16
 }
+
+// Tensor map of a row-major bf16 matrix [rows, cols] with pitch ld (elements): boxes of box_rows x 64
+// columns, 128-byte swizzle, zero fill outside.  Host side; returns 0 or sets the error text.
+int tensor_map_bf16_2d(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out);
 
 }  // namespace sm100

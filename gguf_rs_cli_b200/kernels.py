@@ -248,15 +248,29 @@ def attention_prefill_tiles(qlens) -> list:
     return flat
 
 
+def attention_prefill_tc_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> bool:
+    return bool(native.library().gb_attention_prefill_tc_supported(head_dim, dtype_code(kcache), dtype_code(q))) \
+        and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+
+
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                       tiles: torch.Tensor, cu: torch.Tensor, starts: torch.Tensor, qlens: torch.Tensor,
                       table: torch.Tensor, ring_pages: int, kcache: torch.Tensor, vcache: torch.Tensor, window: int,
-                      scale: float) -> torch.Tensor:
+                      scale: float, tc: Optional[bool] = None) -> torch.Tensor:
     """Many tokens per sequence over the bf16 cache (which already holds their keys and
-    values), flash style on mma.sync."""
+    values), flash style.  tc: both products on tcgen05 with S and PV in TMEM (head size 128; the
+    default where it fits), else on mma.sync (head sizes 64 and 128)."""
     _cuda(q, out, tiles, cu, starts, qlens, table, kcache, vcache)
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (q.shape[0], n_heads * head_dim)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
+    if tc is None:
+        tc = attention_prefill_tc_supported(q, kcache, head_dim)
+    if tc:
+        assert kcache.is_contiguous() and vcache.is_contiguous()
+        call("gb_attention_prefill_tc", ptr(q), q.stride(0), ptr(out), out.stride(0), q.shape[0], n_heads, n_kv_heads,
+             head_dim, ptr(tiles), tiles.numel() // 2, ptr(cu), ptr(starts), ptr(qlens), ptr(table), table.shape[1],
+             ring_pages, ptr(kcache), ptr(vcache), kcache.shape[0], int(window or 0), float(scale), stream_ptr())
+        return out
     call("gb_attention_prefill", ptr(q), q.stride(0), ptr(out), out.stride(0), n_heads, n_kv_heads, head_dim, ptr(tiles),
          tiles.numel() // 2, ptr(cu), ptr(starts), ptr(qlens), ptr(table), table.shape[1], ring_pages, ptr(kcache),
          ptr(vcache), int(window or 0), float(scale), stream_ptr())
@@ -270,11 +284,16 @@ def tc_status() -> int:
 
 
 def check_tc_status() -> None:
+    lib = native.library()
     code = tc_status()
     if code:
-        native.library().gb_tc_status_clear()
-        raise native.NativeError(f"a tensor-core kernel gave up waiting (code {code}: 1 a stage never came free, "
-                                 f"2 a load never arrived, 3 the accumulator never completed); its output is invalid")
+        lib.gb_tc_status_clear()
+        raise native.NativeError(f"a tensor-core product gave up waiting (code {code}: 1 a stage never came free, "
+                                 f"2 a load never arrived, 3/4 an accumulator never completed); its output is invalid")
+    code = lib.gb_attention_tc_status()
+    if code:
+        lib.gb_attention_tc_status_clear()
+        raise native.NativeError(f"the tensor-core attention kernel gave up waiting (code {code}); its output is invalid")
 
 
 # ------------------------------------------------------------------ dispatch

@@ -148,6 +148,11 @@ _SIGNATURES = {
     "gb_attention_prefill": [_P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _P],
     "gb_attention_prefill_supported": [_I, _I, _I],
     "gb_attention_prefill_tile": [],
+    "gb_attention_prefill_tc": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _L, _I, _F, _P],
+    "gb_attention_prefill_tc_supported": [_I, _I, _I],
+    "gb_attention_prefill_tc_tile": [],
+    "gb_attention_tc_status": [],
+    "gb_attention_tc_status_clear": [],
     "gb_tc_status": [],
     "gb_tc_status_clear": [],
 }

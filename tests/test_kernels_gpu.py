@@ -426,15 +426,20 @@ def prefill_meta(lens, qlens):
     return ti(k.attention_prefill_tiles(qlens)), ti(cu), ti(starts), ti(qlens)
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(6, 3, 64), (4, 1, 128), (8, 8, 64), (8, 2, 128)])
-def test_attention_prefill(nh, nkv, hd):
+@pytest.mark.parametrize("nh,nkv,hd", [(6, 3, 64), (4, 1, 128), (8, 8, 64), (8, 2, 128), (5, 5, 128)])
+@pytest.mark.parametrize("tc", [False, True])
+def test_attention_prefill(nh, nkv, hd, tc):
     k = K()
+    if tc and hd != 128:
+        pytest.skip("the tcgen05 attention kernel takes head size 128")
     lens, qlens = [200, 1, 65, 130, 300, 513], [200, 1, 3, 40, 129, 513]   # whole prompts and further pieces
     q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, qlens, BF, seed=hd + nh)
     tiles, cu, starts, ql = prefill_meta(lens, qlens)
     out = torch.full((q.shape[0], nh * hd), float("nan"), dtype=BF, device=DEV)
     assert k.attention_prefill_supported(q, kc, hd)
-    k.attention_prefill(q, out, nh, nkv, hd, tiles, cu, starts, ql, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd))
+    k.attention_prefill(q, out, nh, nkv, hd, tiles, cu, starts, ql, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd), tc=tc)
+    torch.cuda.synchronize()
+    k.check_tc_status()
     assert rel_err(out, want) < 1e-2
     twin = torch.empty_like(out)
     k.attention_generic(q, twin, nh, nkv, hd, seq_of, pos, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd))
@@ -442,23 +447,25 @@ def test_attention_prefill(nh, nkv, hd):
 
 
 @pytest.mark.parametrize("window", [1, 64, 65, 100, 300])
-def test_attention_prefill_far_key_and_window(window):
+@pytest.mark.parametrize("hd,tc", [(64, False), (128, False), (128, True)])
+def test_attention_prefill_far_key_and_window(window, hd, tc):
     k = K()
-    nh, nkv, hd = 8, 2, 64
+    nh, nkv = 8, 2
     lens, qlens = [700, 300], [700, 150]
     scale = 1 / math.sqrt(hd)
     q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, qlens, BF, 5, boost=(0, 3, 2))
     tiles, cu, starts, ql = prefill_meta(lens, qlens)
     out = torch.empty(q.shape[0], nh * hd, dtype=BF, device=DEV)
-    k.attention_prefill(q, out, nh, nkv, hd, tiles, cu, starts, ql, table, 1 << 20, kc, vc, 0, scale)
+    k.attention_prefill(q, out, nh, nkv, hd, tiles, cu, starts, ql, table, 1 << 20, kc, vc, 0, scale, tc=tc)
     assert rel_err(out, want) < 1e-2
     _, _, _, _, _, _, want_w = attention_case(nh, nkv, hd, lens, qlens, BF, 5, window=window, boost=(0, 3, 2))
-    k.attention_prefill(q, out, nh, nkv, hd, tiles, cu, starts, ql, table, 1 << 20, kc, vc, window, scale)
+    k.attention_prefill(q, out, nh, nkv, hd, tiles, cu, starts, ql, table, 1 << 20, kc, vc, window, scale, tc=tc)
     assert rel_err(out, want_w) < 1e-2, f"window {window}"
     assert rel_err(want_w, want) > 0.05
 
 
-def test_attention_prefill_ignores_unwritten_cache_rows():
+@pytest.mark.parametrize("tc", [False, True])
+def test_attention_prefill_ignores_unwritten_cache_rows(tc):
     """Rows of a page beyond the sequence's end hold NaN here; they must not reach the output."""
     k = K()
     nh, nkv, hd = 4, 2, 128
@@ -467,7 +474,9 @@ def test_attention_prefill_ignores_unwritten_cache_rows():
     assert torch.isnan(kc[int(table[0, 1]), :, 10:, :].float()).all()
     tiles, cu, starts, ql = prefill_meta(lens, qlens)
     out = torch.empty(70, nh * hd, dtype=BF, device=DEV)
-    k.attention_prefill(q, out, nh, nkv, hd, tiles, cu, starts, ql, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd))
+    k.attention_prefill(q, out, nh, nkv, hd, tiles, cu, starts, ql, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd), tc=tc)
+    torch.cuda.synchronize()
+    k.check_tc_status()
     assert rel_err(out, want) < 1e-2
 
 
