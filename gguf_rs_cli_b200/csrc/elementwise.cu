@@ -32,6 +32,44 @@ GB_API int gb_embed(const void* table, int table_dtype, const int* tokens, int T
     return 0;
 }
 
+// The same, and for the deferred norm of the first layer: xb[t,:] = bf16(x[t,:]) and ssq[t] = sum(x[t,:]^2).
+__global__ void embed_shadow_kernel(const void* __restrict__ table, int table_dtype, const int* __restrict__ tokens,
+                                    int E, int V, float* __restrict__ out, __nv_bfloat16* __restrict__ xb,
+                                    float* __restrict__ ssq) {
+    __shared__ float red[32];
+    gb_grid_launch_dependents();
+    gb_grid_wait();
+    int t = blockIdx.x;
+    int tok = tokens[t];
+    bool ok = tok >= 0 && tok < V;
+    size_t base = size_t(ok ? tok : 0) * E;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        float v = ok ? gb_load(table, table_dtype, base + i) : 0.f;
+        out[size_t(t) * E + i] = v;
+        xb[size_t(t) * E + i] = __float2bfloat16_rn(v);
+        ss += v * v;
+    }
+    ss = gb_warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+        ssq[t] = tot;
+    }
+}
+
+GB_API int gb_embed_shadow(const void* table, int table_dtype, const int* tokens, int T, int E, int V, float* out,
+                           void* xb, float* ssq, cudaStream_t stream) {
+    GB_REQUIRE(gb_is_dtype(table_dtype), "gb_embed_shadow: bad table dtype %d", table_dtype);
+    GB_REQUIRE(T >= 0 && E > 0 && V > 0 && xb && ssq, "gb_embed_shadow: bad arguments");
+    if (T == 0) return 0;
+    gb_launch(embed_shadow_kernel, dim3(T), dim3(256), 0, stream, table, table_dtype, tokens, E, V, out, (__nv_bfloat16*)xb, ssq);
+    GB_LAUNCH_OK("gb_embed_shadow");
+    return 0;
+}
+
 // --------------------------------------------------------- add + RMS norm
 // For each output row r (source row s = rows ? rows[r] : r):
 //   v = x[s,:] + sum_d delta[d][s,:]            (32-bit sum; written back to x when write_x)

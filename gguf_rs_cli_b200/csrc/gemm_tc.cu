@@ -58,6 +58,17 @@ struct TcParams {
     int T, N, K, splits;
     int swiglu, N_out;    // swiglu: W's rows alternate gate, up; out has N_out features
     int sms;
+    // deferred RMS norm of the input: X holds the un-normalised rows (the norm's weight is folded into W), and
+    // the result is scaled per token by 1 / sqrt(sum_i row_ssq[i][t] / norm_size + eps)
+    const float* row_ssq;
+    int ssq_parts, norm_size;
+    float eps;
+    // residual epilogue: x[t,n] += result (32-bit, in place), xb = bf16(x), and the sum over this tile's 128
+    // features of x^2 goes to ssq_out[feature tile][t] for the norm that comes next
+    float* resid_x;
+    __nv_bfloat16* resid_xb;
+    float* ssq_out;
+    long long ld_x;
 };
 
 // One unit of work: a tile of 128 features x BN tokens over one split of K.  Units are numbered
@@ -95,6 +106,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     __shared__ uint64_t full_bar[Cfg::STAGES], empty_bar[Cfg::STAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base;
     __shared__ int last_flag;
+    __shared__ float rstd_s[BN];            // per token of the tile: the deferred norm's scale
+    __shared__ float part_s[128];
+    __shared__ float ssq_s[4][BN];          // per epilogue warp and token: sum of squares of the new residual
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kb_total = (p.K + BK - 1) / BK;
@@ -199,6 +213,37 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             const int cols = min(BN, p.T - w.t0);       // valid tokens of this tile
             float bias = 0.f;
             if (p.bias && n < p.N) bias = gb_load(p.bias, p.bias_dtype, n);
+            if (p.row_ssq) {
+                // the scale of each token of this tile (the splits of one tile all compute the same numbers): the
+                // 128 threads share the loads, GROUPS threads per token each summing every GROUPS-th part with
+                // several loads in flight, then one of them adds the groups' sums in order
+                constexpr int SLOTS = BN < 128 ? BN : 128, GROUPS = 128 / SLOTS;
+                const int slot = row % SLOTS, grp = row / SLOTS;
+                for (int c0 = 0; c0 < BN; c0 += SLOTS) {
+                    const int c = c0 + slot;
+                    float ss = 0.f;
+                    if (c < cols) {
+                        const float* src = p.row_ssq + w.t0 + c;
+                        for (int i = grp; i < p.ssq_parts; i += 4 * GROUPS) {
+                            float ld[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                ld[e] = i + e * GROUPS < p.ssq_parts ? __ldcg(src + size_t(i + e * GROUPS) * p.T) : 0.f;
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) ss += ld[e];
+                        }
+                    }
+                    part_s[grp * SLOTS + slot] = ss;
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (grp == 0 && c < cols) {
+                        float tot = 0.f;
+#pragma unroll
+                        for (int gi = 0; gi < GROUPS; ++gi) tot += part_s[gi * SLOTS + slot];
+                        rstd_s[c] = 1.f / sqrtf(tot / float(p.norm_size) + p.eps);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
+            }
             const float* partials = p.scratch + size_t(w.tile) * p.splits * (BN * BM);
             bool finish = true;                          // does this CTA write the tile's result?
             if (p.splits > 1) {
@@ -253,7 +298,35 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                             }
                         }
                     }
-                    if (!p.swiglu) {
+                    if (p.row_ssq) {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) v[jj] *= rstd_s[min(c0 + jj, BN - 1)];
+                    }
+                    if (p.resid_x) {
+                        // x += result; the bf16 copy and the tile's share of sum(x^2) per token for the next norm.
+                        // All of x is read before anything is written, so that the loads are in flight together.
+                        float xv[16];
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj)
+                            xv[jj] = (n < p.N && c0 + jj < cols) ? __ldcg(p.resid_x + size_t(w.t0 + c0 + jj) * p.ld_x + n) : 0.f;
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) {
+                            float sq = 0.f;
+                            if (n < p.N && c0 + jj < cols) {
+                                const size_t at = size_t(w.t0 + c0 + jj) * p.ld_x + n;
+                                const float xn = xv[jj] + v[jj] + bias;
+                                p.resid_x[at] = xn;
+                                p.resid_xb[at] = __float2bfloat16_rn(xn);
+                                sq = xn * xn;
+                            }
+                            v[jj] = sq;
+                        }
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) {
+                            const float sq = gb_warp_sum(v[jj]);
+                            if (lane == 0) ssq_s[quarter][c0 + jj] = sq;
+                        }
+                    } else if (!p.swiglu) {
                         if (n < p.N && waited) {
 #pragma unroll
                             for (int jj = 0; jj < 16; ++jj)
@@ -279,6 +352,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                             }
                         }
                     }
+                }
+                if (p.resid_x) {
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    for (int c = row; c < cols; c += 128)
+                        p.ssq_out[size_t(w.n0 / BM) * p.T + w.t0 + c] = ssq_s[0][c] + ssq_s[1][c] + ssq_s[2][c] + ssq_s[3][c];
+                    asm volatile("bar.sync 1, 128;" ::: "memory");     // ssq_s is written again by the next unit
                 }
                 if (p.splits > 1 && threadIdx.x == 64) p.counters[w.tile] = 0;       // ready for the next launch
             }
@@ -443,12 +522,42 @@ GB_API int gb_gemm_tc_supported(const void* X, long long ldx, const void* W, lon
 // swiglu_features > 0: W is [2*64*ceil(F/64), K], row 2f being gate row f and row 2f+1 up row f (zero
 // rows pad the last tile), F = swiglu_features, and
 // out[t,f] = silu(gate_f) * up_f has F columns (src/model/llama.rs:399-401 in the product's epilogue).
+static int gemm_tc_impl(const void* X, long long ldx, const void* W, long long ldw, const void* bias, int bias_dtype,
+                        void* out, int out_dtype, long long ldo, int T, int N, int K, float* scratch, int* counters,
+                        int n_counters, int sms, int swiglu_features, const float* row_ssq, int ssq_parts, int norm_size,
+                        float eps, float* resid_x, void* resid_xb, float* ssq_out, long long ld_x, cudaStream_t stream);
+
 GB_API int gb_gemm_tc(const void* X, long long ldx, const void* W, long long ldw, const void* bias, int bias_dtype,
                       void* out, int out_dtype, long long ldo, int T, int N, int K, float* scratch, int* counters,
                       int n_counters, int sms, int swiglu_features, cudaStream_t stream) {
+    return gemm_tc_impl(X, ldx, W, ldw, bias, bias_dtype, out, out_dtype, ldo, T, N, K, scratch, counters, n_counters, sms,
+                        swiglu_features, nullptr, 0, 0, 0.f, nullptr, nullptr, nullptr, 0, stream);
+}
+
+// The same product with a deferred RMS norm on its input and/or a residual epilogue:
+//  - row_ssq [ssq_parts, T] (f32): X holds rows that were not normalised (the norm's weight is folded into W);
+//    every result is scaled by 1 / sqrt(sum_i row_ssq[i][t] / norm_size + eps) before bias and activation;
+//  - resid_x [T, N] f32 with pitch ld_x: instead of writing `out`, x += result (+ bias) in place, resid_xb (bf16,
+//    same pitch) gets the rounded copy, and ssq_out [ceil(N/128), T] the sums of squares of the new x over each
+//    tile of 128 features: the row_ssq of the product that reads xb next.
+GB_API int gb_gemm_tc_fused(const void* X, long long ldx, const void* W, long long ldw, const void* bias, int bias_dtype,
+                            void* out, int out_dtype, long long ldo, int T, int N, int K, float* scratch, int* counters,
+                            int n_counters, int sms, int swiglu_features, const float* row_ssq, int ssq_parts,
+                            int norm_size, float eps, float* resid_x, void* resid_xb, float* ssq_out, long long ld_x,
+                            cudaStream_t stream) {
+    GB_REQUIRE(!row_ssq || (ssq_parts > 0 && norm_size > 0 && eps > 0.f), "gb_gemm_tc_fused: bad norm parameters");
+    GB_REQUIRE(!resid_x || (resid_xb && ssq_out && ld_x >= N && !swiglu_features), "gb_gemm_tc_fused: bad residual parameters");
+    return gemm_tc_impl(X, ldx, W, ldw, bias, bias_dtype, out, out_dtype, ldo, T, N, K, scratch, counters, n_counters, sms,
+                        swiglu_features, row_ssq, ssq_parts, norm_size, eps, resid_x, resid_xb, ssq_out, ld_x, stream);
+}
+
+static int gemm_tc_impl(const void* X, long long ldx, const void* W, long long ldw, const void* bias, int bias_dtype,
+                        void* out, int out_dtype, long long ldo, int T, int N, int K, float* scratch, int* counters,
+                        int n_counters, int sms, int swiglu_features, const float* row_ssq, int ssq_parts, int norm_size,
+                        float eps, float* resid_x, void* resid_xb, float* ssq_out, long long ld_x, cudaStream_t stream) {
     GB_REQUIRE(gb_is_dtype(out_dtype) && (!bias || gb_is_dtype(bias_dtype)), "gb_gemm_tc: bad dtype");
     GB_REQUIRE(T >= 0 && N > 0 && K > 0, "gb_gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
-    GB_REQUIRE(swiglu_features >= 0 && ldo >= (swiglu_features ? swiglu_features : N), "gb_gemm_tc: output pitch %lld too small", ldo);
+    GB_REQUIRE(swiglu_features >= 0 && (resid_x || ldo >= (swiglu_features ? swiglu_features : N)), "gb_gemm_tc: output pitch %lld too small", ldo);
     GB_REQUIRE(!swiglu_features || (N == 128 * ((swiglu_features + 63) / 64) && !bias),
                "gb_gemm_tc: a gated product of %d features needs %d interleaved rows and no bias, got %d", swiglu_features,
                128 * ((swiglu_features + 63) / 64), N);
@@ -463,6 +572,8 @@ GB_API int gb_gemm_tc(const void* X, long long ldx, const void* W, long long ldw
     p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype; p.T = T; p.N = N; p.K = K;
     p.splits = (scratch && counters) ? gb_gemm_tc_splits(T, N, K, sms) : 1;
     p.swiglu = swiglu_features > 0; p.N_out = swiglu_features; p.sms = sms;
+    p.row_ssq = row_ssq; p.ssq_parts = ssq_parts; p.norm_size = norm_size; p.eps = eps;
+    p.resid_x = resid_x; p.resid_xb = (__nv_bfloat16*)resid_xb; p.ssq_out = ssq_out; p.ld_x = ld_x;
     long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
     GB_REQUIRE(p.splits == 1 || tiles <= n_counters, "gb_gemm_tc: %lld tiles need as many counters, %d given", tiles, n_counters);
     CUtensorMap mw, mx;
@@ -574,6 +685,8 @@ GB_API int gb_gemm_tc_noalloc(const void* X, long long ldx, const void* W, long 
     p.out = out; p.bias = bias; p.scratch = d->scratch; p.counters = d->counters; p.status = d->status;
     p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype; p.T = T; p.N = N; p.K = K;
     p.splits = splits; p.swiglu = 0; p.N_out = 0; p.sms = d->sms;
+    p.row_ssq = nullptr; p.ssq_parts = 0; p.norm_size = 0; p.eps = 0.f;
+    p.resid_x = nullptr; p.resid_xb = nullptr; p.ssq_out = nullptr; p.ld_x = 0;
     CUtensorMap mw, mx;
     if (encode_map_2d(W, N, K, ldw, BM, &mw)) return 1;
     if (encode_map_2d(X, T, K, ldx, bn, &mx)) return 1;

@@ -27,6 +27,17 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch
     return out
 
 
+def embed_shadow(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, xb: torch.Tensor, ssq: torch.Tensor) -> None:
+    """embed plus what a deferred norm needs: xb = bfloat16(out), ssq[t] = sum(out[t,:]^2)."""
+    _cuda(table, tokens, out, xb, ssq)
+    V, E = table.shape
+    T = tokens.numel()
+    assert out.dtype == torch.float32 and out.shape == (T, E) and out.is_contiguous() and tokens.dtype == torch.int32
+    assert xb.dtype == torch.bfloat16 and xb.shape == (T, E) and xb.is_contiguous() and ssq.dtype == torch.float32
+    assert ssq.numel() >= T
+    call("gb_embed_shadow", ptr(table), dtype_code(table), ptr(tokens), T, E, V, ptr(out), ptr(xb), ptr(ssq), stream_ptr())
+
+
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
                 rows: Optional[torch.Tensor] = None, write_x: bool = True) -> torch.Tensor:
     """x: float32 [T,E] residual stream.  delta: None, [T,E] or [S,T,E] terms still to be
@@ -153,16 +164,30 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack([gate, up], dim=1).reshape(2 * (F + pad), K).contiguous()
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-            split_k: bool = True, swiglu_features: int = 0) -> torch.Tensor:
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor],
+            split_k: bool = True, swiglu_features: int = 0, row_ssq: Optional[torch.Tensor] = None, ssq_parts: int = 0,
+            norm_size: int = 0, eps: float = 0.0, resid_x: Optional[torch.Tensor] = None,
+            resid_xb: Optional[torch.Tensor] = None, ssq_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """bf16 x bf16 -> f32 accumulate on tcgen05; out bf16 or f32.  Refuses what
     gemm_tc_supported refuses.  With swiglu_features = F, w is interleave_gate_up(gate, up)
-    and out [T, F] = silu(x gate^T) * (x up^T)."""
-    _cuda(x, w, bias, out)
+    and out [T, F] = silu(x gate^T) * (x up^T).
+
+    row_ssq [ssq_parts, T]: x holds rows whose RMS norm is deferred (its weight folded into w); each
+    token's results are scaled by 1 / sqrt(sum_i row_ssq[i, t] / norm_size + eps).
+    resid_x (f32 [T, N]): instead of writing `out`, resid_x += result in place, resid_xb gets the
+    bfloat16 copy and ssq_out [ceil(N/128), T] the sums of squares per tile of 128 features."""
+    _cuda(x, w, bias, out, row_ssq, resid_x, resid_xb, ssq_out)
     T, K = x.shape
     N = w.shape[0]
-    assert w.shape[1] == K and out.shape == (T, swiglu_features or N) and out.stride(1) == 1
-    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert w.shape[1] == K and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    if resid_x is None:
+        assert out.shape == (T, swiglu_features or N) and out.stride(1) == 1
+    else:
+        assert resid_x.shape == (T, N) and resid_x.dtype == torch.float32 and resid_x.stride(1) == 1
+        assert resid_xb.shape == (T, N) and resid_xb.dtype == torch.bfloat16 and resid_xb.stride(0) == resid_x.stride(0)
+        assert ssq_out.dtype == torch.float32 and ssq_out.numel() >= ((N + 127) // 128) * T
+    if row_ssq is not None:
+        assert row_ssq.dtype == torch.float32 and row_ssq.numel() >= ssq_parts * T and ssq_parts > 0
     sc = tc_scratch(x.device)
     scratch = counters = None
     if split_k:
@@ -170,9 +195,11 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
         if need:
             sc.ensure(need)
             scratch, counters = sc.floats, sc.counters
-    call("gb_gemm_tc", ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(bias), 0 if bias is None else dtype_code(bias),
-         ptr(out), dtype_code(out), out.stride(0), T, N, K, ptr(scratch), ptr(counters),
-         0 if counters is None else counters.numel(), sc.sms, int(swiglu_features), stream_ptr())
+    call("gb_gemm_tc_fused", ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(bias), 0 if bias is None else dtype_code(bias),
+         ptr(out), 1 if out is None else dtype_code(out), 0 if out is None else out.stride(0), T, N, K, ptr(scratch),
+         ptr(counters), 0 if counters is None else counters.numel(), sc.sms, int(swiglu_features), ptr(row_ssq),
+         int(ssq_parts), int(norm_size), float(eps), ptr(resid_x), ptr(resid_xb), ptr(ssq_out),
+         0 if resid_x is None else resid_x.stride(0), stream_ptr())
     return out
 
 

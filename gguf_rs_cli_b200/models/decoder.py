@@ -86,6 +86,10 @@ class Decoder:
         for p in self.parts():
             p.load(store)
         store.release()
+        for layer in self.layers:
+            fuse = getattr(layer.block, "fuse", None)
+            if fuse:
+                fuse()
         return self
 
     # ------------------------------------------------------------------ cache
@@ -117,7 +121,8 @@ class Decoder:
     # ---------------------------------------------------------------- forward
     def forward(self, ctx: StepContext, runs: List[RunView], want_rows: torch.Tensor) -> torch.Tensor:
         """Logits float32 [len(want_rows), V] at the packed token rows asked for."""
-        stream = Stream(self.embedding.forward(ctx.tokens, ctx))
+        make = getattr(self.embedding, "forward_stream", None)
+        stream = make(ctx.tokens, ctx) if make else Stream(self.embedding.forward(ctx.tokens, ctx))
         for view in runs:
             self.layers[view.layer].block.forward(stream, ctx, view)
         h = self.final_norm.apply(stream, ctx, rows=want_rows, buffer="final_normed")

@@ -125,6 +125,8 @@ _SIGNATURES = {
     "gb_sm_count": [],
     "gb_set_pdl": [_I],
     "gb_embed": [_P, _I, _P, _I, _I, _I, _P, _P],
+    "gb_embed_shadow": [_P, _I, _P, _I, _I, _I, _P, _P, _P, _P],
+    "gb_gemm_tc_fused": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _F, _P, _P, _P, _L, _P],
     "gb_add_rmsnorm": [_P, _P, _I, _I, _L, _P, _I, _I, _P, _I, _F, _P, _I, _I, _P],
     "gb_rope_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _P],
     "gb_swiglu": [_P, _L, _P, _I, _I, _I, _P],

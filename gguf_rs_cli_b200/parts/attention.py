@@ -72,7 +72,17 @@ class Attention(Part):
         self.qkv = Linear(w, b, name="attn.qkv")
         self.o = Linear(store.get(req[t["o"]]), name="attn.o")
 
-    def forward(self, h: torch.Tensor, ctx: StepContext, run: RunView) -> torch.Tensor:
+    accepts_residual = True
+
+    def absorb_input_norm(self, weight: torch.Tensor) -> bool:
+        """Multiplies the weight of the norm in front of this mixer into the q/k/v matrix, where
+        the tensor-core product (which can apply the norm's per-token scale) will run it."""
+        if not self.qkv.tensor_core():
+            return False
+        self.qkv.fold_input_scale(weight)
+        return True
+
+    def forward(self, h, ctx: StepContext, run: RunView, residual=None) -> Optional[torch.Tensor]:
         nh, nkv, hd = self.nh, self.nkv, self.hd
         qkv = self.qkv(h, ctx)
         q = qkv[:, :nh * hd]
@@ -87,4 +97,4 @@ class Attention(Part):
                               run.v if k is not None else None)
         out = ctx.ws.get("attn.out", (h.shape[0], nh * hd), ctx.dtype)
         kernels.attention(q, out, nh, nkv, hd, ctx, table, run.ring_pages, run.k, run.v, self.window or 0, self.scale)
-        return self.o(out, ctx)
+        return self.o(out, ctx, residual=residual)

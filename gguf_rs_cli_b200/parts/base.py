@@ -6,12 +6,17 @@ takes them from the store (`load`), and computes on the tokens of one step.  No 
 knows which model it is in.
 
 Roles:
-  norm          apply(stream, ctx, rows=None) -> normalised rows in ctx.dtype; folds the
-                stream's pending term into x (32-bit sum) on the way
+  norm          apply(stream, ctx, rows=None, absorbed=False) -> normalised rows in ctx.dtype; folds
+                the stream's pending term into x (32-bit sum) on the way.  Optional `fold_weight()`
+                gives its weight to a consumer that can multiply it into its own matrix
+                (`absorb_input_norm(w) -> bool`); the block then calls apply(absorbed=True), which
+                leaves the weight out and may return a DeferredNorm instead of rows
   position      gives the mixer what it needs to encode positions (for "rope": inv_freq,
                 rotary_dim, pairing)
   mixer         kv_spec() -> KVSpec or None; state_spec() -> {name: (shape, dtype name)};
-                forward(h, ctx, run) -> term [T, E] (or [S, T, E] partial sums) to add to x
+                forward(h, ctx, run) -> term [T, E] (or [S, T, E] partial sums) to add to x.
+                A part with `accepts_residual = True` is called with residual=stream and may add
+                its term to the stream itself (returning None)
   feed-forward  forward(h, ctx) -> term to add to x
   block         forward(stream, ctx, run): wires norms, mixer and feed-forward around x
   embedding     forward(tokens, ctx) -> float32 x [T, E]
@@ -105,10 +110,42 @@ class StepContext:
         return self.cache.states[name]
 
 
+# Steps of at most this many tokens fold residual adds and norms into the products' epilogues (there the
+# step is bound by launches and bandwidth); larger steps keep the separate norm kernel, whose cost the
+# compute-bound products would otherwise carry in their epilogues.
+FUSE_MAX_TOKENS = 128
+
+
 class Stream:
     """The residual stream: x in float32 plus a term that has not been added yet.  The
-    next norm adds it in 32-bit in the same kernel that normalises."""
+    next norm adds it in 32-bit in the same kernel that normalises.
+
+    A producer that adds its term to x itself (a product's residual epilogue, the embedding)
+    may leave a shadow for the norm that follows: xb = bfloat16(x) and ssq [parts, T], partial
+    sums of x^2 per token.  The shadow is valid while nothing is pending and x is unchanged."""
 
     def __init__(self, x: torch.Tensor):
         self.x = x
         self.pending: Optional[torch.Tensor] = None
+        self.xb: Optional[torch.Tensor] = None
+        self.ssq: Optional[torch.Tensor] = None
+        self.ssq_parts = 0
+
+    def drop_shadow(self) -> None:
+        self.xb, self.ssq, self.ssq_parts = None, None, 0
+
+
+@dataclass
+class DeferredNorm:
+    """Rows whose RMS norm has not been applied: the consumer (a product that has folded the
+    norm's weight into its matrix) scales its results per token by
+    1 / sqrt(sum_i ssq[i, t] / size + eps) instead."""
+    xb: torch.Tensor
+    ssq: torch.Tensor
+    parts: int
+    size: int
+    eps: float
+
+    @property
+    def shape(self):
+        return self.xb.shape

@@ -9,7 +9,7 @@ import torch
 
 from .. import kernels
 from ..weights.loader import TensorRequest, WeightStore
-from .base import Part, StepContext
+from .base import FUSE_MAX_TOKENS, Part, StepContext, Stream
 from .linear import Linear
 from .registry import register_embedding, register_head
 
@@ -27,6 +27,19 @@ class Embedding(Part):
     def forward(self, tokens: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         x = ctx.ws.get("x", (tokens.numel(), self.p["hidden_size"]), torch.float32)
         return kernels.embed(self.weight, tokens, x)
+
+    def forward_stream(self, tokens: torch.Tensor, ctx: StepContext) -> Stream:
+        """The residual stream of a step; in bfloat16 mode with the shadow (bfloat16 copy and sums of
+        squares per token) that lets the first norm be deferred into the product after it."""
+        if ctx.dtype != torch.bfloat16 or tokens.numel() > FUSE_MAX_TOKENS:
+            return Stream(self.forward(tokens, ctx))
+        T, E = tokens.numel(), self.p["hidden_size"]
+        stream = Stream(ctx.ws.get("x", (T, E), torch.float32))
+        stream.xb = ctx.ws.get("stream.xb", (T, E), torch.bfloat16)
+        stream.ssq = ctx.ws.get("stream.ssq", ((E + 127) // 128, T), torch.float32)
+        stream.ssq_parts = 1
+        kernels.embed_shadow(self.weight, tokens, stream.x, stream.xb, stream.ssq)
+        return stream
 
 
 @register_head("lm_head")

@@ -9,7 +9,9 @@ import torch
 
 from .. import kernels
 from ..weights.loader import TensorRequest, WeightStore
-from .base import Part, StepContext
+from typing import Optional
+
+from .base import DeferredNorm, Part, StepContext
 from .linear import Linear
 from .registry import register_feed_forward
 
@@ -41,13 +43,25 @@ class GatedMLP(Part):
             self.gate_up = Linear(torch.cat([g, u], dim=0), name="ff.gate_up")
         self.down = Linear(d, name="ff.down")
 
-    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    accepts_residual = True
+
+    def absorb_input_norm(self, weight: torch.Tensor) -> bool:
+        """Multiplies the weight of the norm in front of this part into the gate/up matrix (only
+        where the tensor-core product, which can apply the norm's per-token scale, runs it)."""
+        if not self.fused:
+            return False
+        self.gate_up_tiles = (self.gate_up_tiles.float() * weight.float()[None, :]).to(torch.bfloat16).contiguous()
+        return True
+
+    def forward(self, h, ctx: StepContext, residual=None) -> Optional[torch.Tensor]:
         F = self.p["intermediate_size"]
         act = ctx.ws.get("ff.act", (h.shape[0], F), ctx.dtype)
-        if self.fused and kernels.gemm_tc_supported(h, self.gate_up_tiles):
-            kernels.gemm_tc(h, self.gate_up_tiles, None, act, swiglu_features=F)
+        norm = dict(row_ssq=h.ssq, ssq_parts=h.parts, norm_size=h.size, eps=h.eps) if isinstance(h, DeferredNorm) else {}
+        rows = h.xb if norm else h
+        if self.fused and kernels.gemm_tc_supported(rows, self.gate_up_tiles):
+            kernels.gemm_tc(rows, self.gate_up_tiles, None, act, swiglu_features=F, **norm)
         elif self.fused:
             raise RuntimeError("gated_mlp: the activations given do not fit the fused product it was loaded for")
         else:
             kernels.swiglu(self.gate_up(h, ctx), act)
-        return self.down(act, ctx)
+        return self.down(act, ctx, residual=residual)

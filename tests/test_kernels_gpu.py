@@ -501,3 +501,57 @@ def test_gemm_tensor_core_gated(T, F, Kd):
     out32 = torch.empty(T, F, dtype=F32, device=DEV)
     k.gemm_tc(x, w, None, out32, swiglu_features=F)
     assert rel_err(out32, want) < 1e-5
+
+
+# --------------------------- deferred norm and residual epilogue of the product
+@pytest.mark.parametrize("T,N,Kd", [(1, 256, 512), (8, 520, 320), (16, 4096, 4096), (70, 384, 1024), (300, 640, 328),
+                                    (2100, 512, 256)])
+def test_gemm_tensor_core_deferred_norm_and_residual(T, N, Kd):
+    k = K()
+    g = torch.Generator().manual_seed(T * 7 + N)
+    eps = 1e-5
+    # a producer leaves x (f32), its bf16 copy and per-tile sums of squares; the consumer scales by them
+    x = torch.randn(T, Kd, generator=g) * 3
+    wn = 1 + 0.2 * torch.randn(Kd, generator=g)
+    w = (torch.randn(N, Kd, generator=g) * 0.1)
+    wf = (w * wn).to(BF)                                        # the norm's weight folded into the matrix
+    b = torch.randn(N, generator=g)
+    xb = x.to(BF)
+    parts = (Kd + 127) // 128
+    ssq = torch.zeros(parts, T)
+    for i in range(parts):
+        ssq[i] = (x[:, 128 * i:128 * (i + 1)] ** 2).sum(1)
+    rstd = 1 / torch.sqrt((x.double() ** 2).sum(1, keepdim=True) / Kd + eps)
+    want = (xb.double() * rstd) @ wf.double().t() + b.double()
+    out = torch.full((T, N), float("nan"), dtype=F32, device=DEV)
+    k.gemm_tc(xb.to(DEV), wf.to(DEV), b.to(DEV), out, row_ssq=ssq.to(DEV), ssq_parts=parts, norm_size=Kd, eps=eps)
+    torch.cuda.synchronize()
+    k.check_tc_status()
+    assert rel_err(out, want) < 1e-5
+    # residual epilogue: r += x W^T + b, its bf16 copy, and sums of squares per 128 features
+    r0 = torch.randn(T, N, generator=g) * 2
+    r = r0.to(DEV).clone()
+    rb = torch.zeros(T, N, dtype=BF, device=DEV)
+    tiles = (N + 127) // 128
+    ssq_out = torch.full((tiles, T), float("nan"), device=DEV)
+    k.gemm_tc(xb.to(DEV), wf.to(DEV), b.to(DEV), None, resid_x=r, resid_xb=rb, ssq_out=ssq_out)
+    torch.cuda.synchronize()
+    k.check_tc_status()
+    want_r = r0.double() + xb.double() @ wf.double().t() + b.double()
+    assert rel_err(r, want_r) < 1e-5
+    assert torch.equal(rb.cpu(), r.cpu().to(BF))
+    want_ssq = torch.stack([(r.cpu().double()[:, 128 * i:128 * (i + 1)] ** 2).sum(1) for i in range(tiles)])
+    assert rel_err(ssq_out, want_ssq) < 1e-5
+
+
+def test_embed_shadow():
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(300, 200, generator=g).to(BF)
+    toks = torch.randint(0, 300, (33,), generator=g)
+    out = torch.empty(33, 200, dtype=F32, device=DEV)
+    xb = torch.empty(33, 200, dtype=BF, device=DEV)
+    ssq = torch.empty(33, dtype=F32, device=DEV)
+    K().embed_shadow(table.to(DEV), toks.to(torch.int32).to(DEV), out, xb, ssq)
+    want = P.embedding(table.float(), toks.tolist())
+    assert torch.equal(out.cpu(), want) and torch.equal(xb.cpu(), want.to(BF))
+    assert rel_err(ssq, (want.double() ** 2).sum(1)) < 1e-6

@@ -92,9 +92,13 @@ def test_attention_and_feed_forward_alone(name, dtype):
     run = eng.runs[1]
     got = layer.mixer.forward(h.to(DEV), ctx, run)
     inv = P.inv_freq_table(cfg)
+    # a part that took the weight of the norm in front of it into its matrix expects rows without it
+    wn_m = w[p + "input_layernorm.weight"] if layer.block.absorbed["mixer"] else 1.0
+    wn_f = w[p + "post_attention_layernorm.weight"] if layer.block.absorbed["feed_forward"] else 1.0
+    assert layer.block.absorbed["mixer"] == layer.block.absorbed["feed_forward"] == (dtype == "bfloat16")
     want, t0 = [], 0
     for n in lens:
-        hh = h[t0:t0 + n].float()
+        hh = h[t0:t0 + n].float() * wn_m
         q = P.linear(hh, w[p + "self_attn.q_proj.weight"], w.get(p + "self_attn.q_proj.bias")).reshape(n, nh, hd)
         k = P.linear(hh, w[p + "self_attn.k_proj.weight"], w.get(p + "self_attn.k_proj.bias")).reshape(n, nkv, hd)
         v = P.linear(hh, w[p + "self_attn.v_proj.weight"], w.get(p + "self_attn.v_proj.bias")).reshape(n, nkv, hd)
@@ -104,7 +108,7 @@ def test_attention_and_feed_forward_alone(name, dtype):
         t0 += n
     assert_close(got, torch.cat(want), dtype, "attention part")
     got_ff = layer.feed_forward.forward(h.to(DEV), ctx)
-    want_ff = P.feed_forward(h.float(), w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+    want_ff = P.feed_forward(h.float() * wn_f, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                              w[p + "mlp.down_proj.weight"])
     assert_close(got_ff, want_ff, dtype, "feed-forward part")
 
