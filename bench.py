@@ -168,15 +168,18 @@ def measure_prefill(llm, cfg, layers, reps=3):
     return best
 
 
-def measure_e2e(llm, cfg, batch, steps):
+def measure_e2e(llm, cfg, batch, steps, warmup):
     """Through generate(): host ids in, host ids out.  Decode tokens a second from the
-    loop's own clock (synchronised on both sides of every step)."""
+    loop's own clock (synchronised on both sides of every step).  A short untimed call
+    comes first: it is the warm-up (the first steps of a batch size build its graph)."""
     import torch
     from gguf_rs_cli_b200.api import generate
     from gguf_rs_cli_b200.engine.generate import GenerationStats
     g = torch.Generator().manual_seed(100 + batch)
     prompts = [torch.randint(0, cfg["vocab_size"], (PROMPT,), generator=g).tolist() for _ in range(batch)]
     backend = llm.backend(n_tokens=64 * CONTEXT, n_slots=64, max_len=CONTEXT)
+    h0, d0 = backend.h2d_bytes, backend.d2h_bytes
+    generate(llm, prompts, max_tokens=warmup + 2, temperature=0.0, stop_token_ids=[], max_batch=64, ctx_len=CONTEXT)
     h0, d0 = backend.h2d_bytes, backend.d2h_bytes
     stats = GenerationStats()
     out = generate(llm, prompts, max_tokens=steps, temperature=0.0, stop_token_ids=[], max_batch=64, ctx_len=CONTEXT,
@@ -253,7 +256,7 @@ def main():
             points[f"decode_b{b}"] = round(p_tok_s, 2)
             points[f"decode_b{b}_ms"] = round(p_ms, 4)
         line["points"] = points
-        e_tok_s, h2d, d2h = measure_e2e(llm, cfg, args.batch, args.steps)
+        e_tok_s, h2d, d2h = measure_e2e(llm, cfg, args.batch, args.steps, warmup)
         line["e2e"] = {"value": round(e_tok_s, 2), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
                        "d2h_bytes_per_step": int(d2h)}
     sampler.stop()

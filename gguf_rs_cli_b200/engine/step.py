@@ -178,7 +178,8 @@ class Engine:
             slots=view("slots"), starts=view("starts"), qlens=view("qlens"), cu=view("cu"),
             tables=[dev[a:a + b * w].view(b, w) for a, b, w in table_offs], cache=self.cache, ws=self.ws,
             decode=max(qlens) == 1, max_qlen=max(qlens), max_kv=max_kv,
-            host={"slots": slots, "starts": starts, "qlens": qlens, "h2d_bytes": 4 * len(flat)},
+            host={"slots": slots, "starts": starts, "qlens": qlens, "h2d_bytes": 4 * len(flat), "layout": offs,
+                  "table_offs": table_offs, "n_words": len(flat)},
             tiles=view("tiles").view(-1, 2) if tiles else None)
         return ctx, view("want"), len(want)
 

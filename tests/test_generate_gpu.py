@@ -116,3 +116,28 @@ def test_graph_and_eager_decode_agree():
         outs.append(generate_ids(backend, prompts, 9, SamplingParams(temperature=0.9, seed=5), [stop]))
         assert eng.cache.slots.held_count == 0
     assert outs[0] == outs[2] and outs[1] == outs[3]
+
+
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_decode_steps_updated_in_place_cross_pages(name):
+    """While a batch goes on token by token, the captured step's index arrays are only
+    updated; sequences that enter a new page (positions 64, 128) and one that ends early
+    must give the tokens of the step that is laid out anew every time, and of the plain code."""
+    from gguf_rs_cli_b200.engine.backend import EngineBackend
+    from gguf_rs_cli_b200.engine.generate import generate_ids
+    from gguf_rs_cli_b200.sampling import SamplingParams
+    prompts = [tokens_of(name, n, 300 + n) for n in (60, 3, 125, 62, 64)]
+    want = plain_generate(name, prompts, 10)
+    params = SamplingParams(temperature=0.0)
+    for graphs in (False, True):
+        eng = new_engine(name, "float32", n_tokens=64 * 24, n_slots=8)
+        backend = EngineBackend(eng, use_graphs=graphs)
+        for _ in range(2):                                   # the second pass replays captured graphs on used slots
+            got = generate_ids(backend, prompts, 10, params, [])
+            assert got == want
+            eng.cache.check()
+        stop = want[1][4]
+        got = generate_ids(backend, prompts, 10, params, [stop])
+        for g, w in zip(got, want):
+            assert g == (w[:w.index(stop)] if stop in w else w)        # the stop token itself is not given out
+        assert eng.cache.slots.held_count == 0
