@@ -33,6 +33,17 @@ struct DmParams {
     long long ldq, ldo;
     int nh, nkv, table_width, ring_pages, window, splits;
     float scale_log2;
+    // rotation and cache write in the same kernel (rotate != 0): q, k_new and v_new are the products as they
+    // come from the projection; the kernel rotates q on its way into shared memory, and the CTA that reads a
+    // token's last page puts the token's own rotated key and its value into that page (in shared memory, and
+    // one CTA per KV head in the cache too).  k_new null: the cache belongs to another run, only q is rotated.
+    int rotate;
+    const __nv_bfloat16* k_new;
+    const __nv_bfloat16* v_new;
+    __nv_bfloat16* kc_w;
+    __nv_bfloat16* vc_w;
+    const float* inv_freq;
+    int rotary_dim, pairing;
 };
 
 __device__ __forceinline__ void dm_cp_async16(void* dst, const void* src, bool valid) {
@@ -65,7 +76,7 @@ template <int HD> __device__ __forceinline__ int dm_swz(int row, int chunk) {
 
 template <int HD>
 __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmParams p) {
-    constexpr int CH = HD / 8, KS = HD / 16, OT = HD / 8;
+    constexpr int CH = HD / 8, KS = HD / 16, OT = HD / 8, HALF = HD / 2;
     constexpr int PAGE_ELEMS = GB_PAGE * HD;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                  // [16][HD]
@@ -99,6 +110,7 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
     const int pg_begin = first_page + int((long long)split * n_pages / p.splits);
     const int pg_end = first_page + int((long long)(split + 1) * n_pages / p.splits);
     const int* trow = p.table + size_t(b) * p.table_width;
+    const bool own_kv = p.rotate && p.k_new != nullptr;
 
     auto load_page = [&](int pg, int stage) {
         const int phys = trow[pg % p.ring_pages];
@@ -107,21 +119,68 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
         __nv_bfloat16* vd = vs + stage * PAGE_ELEMS;
         for (int i = tid; i < GB_PAGE * CH; i += DM_THREADS) {
             int r = i / CH, c = i - r * CH;
-            bool ok = pg * GB_PAGE + r <= pos;             // rows beyond the sequence are read as zeros
+            const int key = pg * GB_PAGE + r;              // rows beyond the sequence are read as zeros, and so
+            bool ok = key < pos || (key == pos && !own_kv);   // is the token's own row when this kernel makes it
             dm_cp_async16(kd + dm_swz<HD>(r, c), p.kc + off + size_t(r) * HD + c * 8, ok);
             dm_cp_async16(vd + dm_swz<HD>(r, c), p.vc + off + size_t(r) * HD + c * 8, ok);
         }
     };
 
-    // the group's queries (rows beyond the group are zeros) and the first pages
-    for (int i = tid; i < DM_ROWS * CH; i += DM_THREADS) {
-        int r = i / CH, c = i - r * CH;
-        dm_cp_async16(qs + dm_swz<HD>(r, c), p.q + size_t(t) * p.ldq + size_t(h0 + min(r, heads - 1)) * HD + c * 8, r < heads);
+    // the group's queries (rows beyond the group are zeros; with the first page's copies if they need no
+    // rotation, else through registers below) and the first pages
+    if (!p.rotate) {
+        for (int i = tid; i < DM_ROWS * CH; i += DM_THREADS) {
+            int r = i / CH, c = i - r * CH;
+            dm_cp_async16(qs + dm_swz<HD>(r, c), p.q + size_t(t) * p.ldq + size_t(h0 + min(r, heads - 1)) * HD + c * 8, r < heads);
+        }
     }
 #pragma unroll
     for (int s = 0; s < DM_STAGES - 1; ++s) {
         if (pg_begin + s < pg_end) load_page(pg_begin + s, s);
         dm_commit();
+    }
+    float sn = 0.f, cs = 1.f;
+    int d0 = 0, d1 = 0;
+    float own0 = 0.f, own1 = 0.f;                     // this thread's two elements of the token's own key or value
+    const bool has_own = own_kv && pg_begin < pg_end && pg_end - 1 == (pos >> GB_PAGE_SHIFT);
+    if (p.rotate) {
+        // pair `pi` of every row: (pi, pi + half) or (2 pi, 2 pi + 1) inside the rotation, unchanged beyond it
+        const int pi = tid % HALF, half = p.inv_freq ? p.rotary_dim / 2 : 0;
+        const float freq = pi < half ? p.inv_freq[pi] : 0.f;
+        d0 = pi < half ? (p.pairing ? 2 * pi : pi) : 2 * pi;
+        d1 = pi < half ? (p.pairing ? 2 * pi + 1 : pi + half) : 2 * pi + 1;
+        constexpr int RPT = DM_ROWS * HALF / DM_THREADS;         // rows per thread
+        float x0[RPT], x1[RPT];
+#pragma unroll
+        for (int j = 0; j < RPT; ++j) {
+            const int r = tid / HALF + j * (DM_THREADS / HALF);
+            x0[j] = x1[j] = 0.f;
+            if (r < heads) {
+                const __nv_bfloat16* src = p.q + size_t(t) * p.ldq + size_t(h0 + r) * HD;
+                x0[j] = __bfloat162float(src[d0]);
+                x1[j] = __bfloat162float(src[d1]);
+            }
+        }
+        if (has_own) {
+            const size_t src = size_t(t) * p.ldq + size_t(g) * HD;
+            if (tid < HALF) {
+                own0 = __bfloat162float(p.k_new[src + d0]);
+                own1 = __bfloat162float(p.k_new[src + d1]);
+            } else if (tid < 2 * HALF) {
+                const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(p.v_new + src + 2 * (tid - HALF));
+                own0 = __low2float(x);
+                own1 = __high2float(x);
+            }
+        }
+        if (pi < half) sincosf(float(pos) * freq, &sn, &cs);
+#pragma unroll
+        for (int j = 0; j < RPT; ++j) {
+            const int r = tid / HALF + j * (DM_THREADS / HALF);
+            float y0, y1;
+            gb_rotate(x0[j], x1[j], cs, sn, y0, y1);
+            qs[dm_swz<HD>(r, d0 >> 3) + (d0 & 7)] = __float2bfloat16_rn(y0);
+            qs[dm_swz<HD>(r, d1 >> 3) + (d1 & 7)] = __float2bfloat16_rn(y1);
+        }
     }
 
     float o[OT][4];
@@ -137,6 +196,29 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
         dm_commit();
         dm_wait<DM_STAGES - 1>();
         __syncthreads();
+        if (has_own && pg == pg_end - 1) {
+            // the token's own key (rotated) and value: into the page in shared memory, and by the first head
+            // tile of the KV head into the cache
+            const int r = pos & (GB_PAGE - 1);
+            const bool writes = (blockIdx.y % gtiles) == 0;
+            const size_t dst = (size_t(trow[pg % p.ring_pages]) * p.nkv + g) * size_t(PAGE_ELEMS) + size_t(r) * HD;
+            if (tid < HALF) {
+                float r0, r1;
+                gb_rotate(own0, own1, cs, sn, r0, r1);
+                const __nv_bfloat16 y0 = __float2bfloat16_rn(r0), y1 = __float2bfloat16_rn(r1);
+                __nv_bfloat16* kt_w = ks + stage * PAGE_ELEMS;
+                kt_w[dm_swz<HD>(r, d0 >> 3) + (d0 & 7)] = y0;
+                kt_w[dm_swz<HD>(r, d1 >> 3) + (d1 & 7)] = y1;
+                if (writes) { p.kc_w[dst + d0] = y0; p.kc_w[dst + d1] = y1; }
+            } else if (tid < 2 * HALF) {
+                const int e = 2 * (tid - HALF);
+                const __nv_bfloat162 x = __floats2bfloat162_rn(own0, own1);
+                __nv_bfloat16* vt_w = vs + stage * PAGE_ELEMS;
+                *reinterpret_cast<__nv_bfloat162*>(vt_w + dm_swz<HD>(r, e >> 3) + (e & 7)) = x;
+                if (writes) *reinterpret_cast<__nv_bfloat162*>(p.vc_w + dst + e) = x;
+            }
+            __syncthreads();
+        }
         if (it == 0) {
 #pragma unroll
             for (int k = 0; k < KS; ++k)
@@ -312,11 +394,15 @@ GB_API int gb_attention_decode_mma_splits(int T, int nh, int nkv, int sms, int m
 }
 
 // Same contract as gb_attention_decode; counters: T * nkv * ceil(G/16) zeroed ints when splits > 1;
-// scratch: T * nh * splits * (hd + 2) floats.
-GB_API int gb_attention_decode_mma(const void* q, long long ldq, void* out, long long ldo, int T, int nh, int nkv, int hd,
-                                   const int* seq_of, const int* pos, const int* table, int table_width,
-                                   int ring_pages, const void* kcache, const void* vcache, int window, float scale,
-                                   int splits, float* scratch, int* counters, int n_counters, cudaStream_t stream) {
+// scratch: T * nh * splits * (hd + 2) floats.  With rotate != 0 the kernel also does what gb_rope_kv_write does
+// for these tokens: q, k_new, v_new (rows ldq apart, as the projection left them; k_new and v_new null for a
+// mixer that reads another run's cache) are rotated by pos * inv_freq (inv_freq null: no rotation) and the
+// token's key and value are written at its position of the cache.  q itself stays as it was.
+static int decode_mma(const void* q, long long ldq, void* out, long long ldo, int T, int nh, int nkv, int hd,
+                      const int* seq_of, const int* pos, const int* table, int table_width, int ring_pages,
+                      void* kcache, void* vcache, int window, float scale, int splits, float* scratch,
+                      int* counters, int n_counters, int rotate, const void* k_new, const void* v_new,
+                      const float* inv_freq, int rotary_dim, int pairing, cudaStream_t stream) {
     GB_REQUIRE(gb_attention_decode_mma_supported(hd, GB_BF16, GB_BF16), "gb_attention_decode_mma: head_dim %d is not 64 or 128", hd);
     GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "gb_attention_decode_mma: %d heads are not a multiple of %d KV heads", nh, nkv);
     GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0 && splits >= 1, "gb_attention_decode_mma: bad cache geometry");
@@ -332,6 +418,33 @@ GB_API int gb_attention_decode_mma(const void* q, long long ldq, void* out, long
     p.vc = (const __nv_bfloat16*)vcache; p.seq_of = seq_of; p.pos = pos; p.table = table; p.scratch = scratch;
     p.counters = counters; p.ldq = ldq; p.ldo = ldo; p.nh = nh; p.nkv = nkv; p.table_width = table_width;
     p.ring_pages = ring_pages; p.window = window; p.splits = splits; p.scale_log2 = scale * 1.4426950408889634f;
+    p.rotate = rotate; p.k_new = (const __nv_bfloat16*)k_new; p.v_new = (const __nv_bfloat16*)v_new;
+    p.kc_w = (__nv_bfloat16*)kcache; p.vc_w = (__nv_bfloat16*)vcache; p.inv_freq = inv_freq;
+    p.rotary_dim = rotary_dim; p.pairing = pairing;
     dim3 grid(T, nkv * gtiles, splits);
     return hd == 64 ? launch_dm<64>(p, grid, stream) : launch_dm<128>(p, grid, stream);
+}
+
+GB_API int gb_attention_decode_mma(const void* q, long long ldq, void* out, long long ldo, int T, int nh, int nkv, int hd,
+                                   const int* seq_of, const int* pos, const int* table, int table_width,
+                                   int ring_pages, const void* kcache, const void* vcache, int window, float scale,
+                                   int splits, float* scratch, int* counters, int n_counters, cudaStream_t stream) {
+    return decode_mma(q, ldq, out, ldo, T, nh, nkv, hd, seq_of, pos, table, table_width, ring_pages, (void*)kcache,
+                      (void*)vcache, window, scale, splits, scratch, counters, n_counters, 0, nullptr, nullptr, nullptr,
+                      0, 0, stream);
+}
+
+GB_API int gb_attention_decode_mma_rope(const void* q, const void* k_new, const void* v_new, long long ldq, void* out,
+                                        long long ldo, int T, int nh, int nkv, int hd, int rotary_dim, int pairing,
+                                        const float* inv_freq, const int* seq_of, const int* pos, const int* table,
+                                        int table_width, int ring_pages, void* kcache, void* vcache, int window,
+                                        float scale, int splits, float* scratch, int* counters, int n_counters,
+                                        cudaStream_t stream) {
+    GB_REQUIRE(rotary_dim >= 0 && rotary_dim <= hd && rotary_dim % 2 == 0,
+               "gb_attention_decode_mma_rope: rotary_dim %d must be even and at most head_dim %d", rotary_dim, hd);
+    GB_REQUIRE((k_new == nullptr) == (v_new == nullptr), "gb_attention_decode_mma_rope: k and v must both be given or both be null");
+    GB_REQUIRE(!v_new || (reinterpret_cast<uintptr_t>(v_new) & 3) == 0, "gb_attention_decode_mma_rope: misaligned v");
+    return decode_mma(q, ldq, out, ldo, T, nh, nkv, hd, seq_of, pos, table, table_width, ring_pages, kcache, vcache,
+                      window, scale, splits, scratch, counters, n_counters, 1, k_new, v_new, inv_freq, rotary_dim,
+                      pairing, stream);
 }

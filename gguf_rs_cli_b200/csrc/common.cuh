@@ -83,6 +83,13 @@ __device__ __forceinline__ size_t gb_kv_offset(const int* row, int ring_pages, i
     return ((size_t(page) * nkv + g) * GB_PAGE + (pos & (GB_PAGE - 1))) * size_t(hd);
 }
 
+// Rotation of one pair by the angle whose sine and cosine are given.  Products and sums are rounded one by
+// one (no fused multiply-add), so that every kernel that rotates gives the same bits.
+__device__ __forceinline__ void gb_rotate(float x0, float x1, float cs, float sn, float& y0, float& y1) {
+    y0 = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+    y1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
+}
+
 __device__ __forceinline__ float gb_warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -242,15 +242,19 @@ __global__ void rope_kv_write_kernel(void* __restrict__ q, const void* __restric
             if (!q || i >= half) continue;             // q's unrotated dimensions stay as they are
             const size_t o = row + size_t(head) * hd;
             const float x0 = gb_load(q, dtype, o + d0), x1 = gb_load(q, dtype, o + d1);
-            gb_store(q, dtype, o + d0, x0 * cs - x1 * sn);
-            gb_store(q, dtype, o + d1, x0 * sn + x1 * cs);
+            float y0, y1;
+            gb_rotate(x0, x1, cs, sn, y0, y1);
+            gb_store(q, dtype, o + d0, y0);
+            gb_store(q, dtype, o + d1, y1);
         } else if (head < nh + nkv) {
             const int g = head - nh;
             const size_t o = row + size_t(g) * hd;
             const size_t c = gb_kv_offset(trow, ring_pages, p, g, nkv, hd);
             const float x0 = gb_load(k, dtype, o + d0), x1 = gb_load(k, dtype, o + d1);
-            gb_store(kcache, cache_dtype, c + d0, x0 * cs - x1 * sn);     // beyond the rotation: cs = 1, sn = 0
-            gb_store(kcache, cache_dtype, c + d1, x0 * sn + x1 * cs);
+            float y0, y1;
+            gb_rotate(x0, x1, cs, sn, y0, y1);                            // beyond the rotation: cs = 1, sn = 0
+            gb_store(kcache, cache_dtype, c + d0, y0);
+            gb_store(kcache, cache_dtype, c + d1, y1);
         } else {
             const int g = head - nh - nkv;
             const size_t o = row + size_t(g) * hd;

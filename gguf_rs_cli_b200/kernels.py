@@ -230,10 +230,14 @@ def attention_decode_mma_supported(q: torch.Tensor, kcache: torch.Tensor, head_d
 def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                      seq_of: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, ring_pages: int,
                      kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float,
-                     splits: Optional[int] = None, mma: Optional[bool] = None, max_kv: Optional[int] = None) -> torch.Tensor:
+                     splits: Optional[int] = None, mma: Optional[bool] = None, max_kv: Optional[int] = None,
+                     rope: Optional[tuple] = None) -> torch.Tensor:
     """One token per sequence over the bf16 cache; all heads of a group share one pass over
     the keys and values.  mma: the tensor-core kernel (head sizes 64 and 128; the default
-    where it fits) or the CUDA-core one (any head size that is a multiple of 16)."""
+    where it fits) or the CUDA-core one (any head size that is a multiple of 16).
+    rope = (k, v, inv_freq, rotary_dim, pairing), tensor-core kernel only: q, k and v are the
+    unrotated projections; the kernel rotates q and k and writes k and v into the cache itself
+    (k and v None: it reads another run's cache and only rotates q)."""
     _cuda(q, out, seq_of, pos, table, kcache, vcache)
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, n_heads * head_dim)
@@ -252,6 +256,15 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_head
         scratch, counters = sc.floats, sc.counters
         if T * n_heads > sc.COUNTERS:
             splits, scratch, counters = 1, None, None
+    if rope is not None:
+        k, v, inv_freq, rotary_dim, pairing = rope
+        _cuda(k, v, inv_freq)
+        assert mma and (k is None or (k.stride(0) == q.stride(0) and v.stride(0) == q.stride(0) and k.dtype == q.dtype))
+        call("gb_attention_decode_mma_rope", ptr(q), ptr(k), ptr(v), q.stride(0), ptr(out), out.stride(0), T, n_heads,
+             n_kv_heads, head_dim, rotary_dim, pairing, ptr(inv_freq), ptr(seq_of), ptr(pos), ptr(table), table.shape[1],
+             ring_pages, ptr(kcache), ptr(vcache), int(window or 0), float(scale), splits, ptr(scratch), ptr(counters),
+             0 if counters is None else counters.numel(), stream_ptr())
+        return out
     call(entry, ptr(q), q.stride(0), ptr(out), out.stride(0), T, n_heads, n_kv_heads, head_dim,
          ptr(seq_of), ptr(pos), ptr(table), table.shape[1], ring_pages, ptr(kcache), ptr(vcache), int(window or 0),
          float(scale), splits, ptr(scratch), ptr(counters), 0 if counters is None else counters.numel(), stream_ptr())
@@ -332,12 +345,24 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: to
     return gemm_generic(x, w, bias, out)
 
 
+def decode_rotates(ctx, q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> bool:
+    """Whether this step's attention kernel rotates q and k and writes the cache itself (a step of single
+    tokens on the tensor-core decode kernel), so that no separate rotation kernel runs before it."""
+    return bool(ctx.decode) and attention_decode_supported(q, kcache, head_dim) and \
+        attention_decode_mma_supported(q, kcache, head_dim)
+
+
 def attention(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, ctx, table: torch.Tensor,
-              ring_pages: int, kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float) -> torch.Tensor:
-    """Attention of one step over the cache; picks the kernel for the step's shape."""
+              ring_pages: int, kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float,
+              rope: Optional[tuple] = None) -> torch.Tensor:
+    """Attention of one step over the cache; picks the kernel for the step's shape.  rope: see
+    attention_decode; allowed where decode_rotates() says so (q, k and v then come unrotated)."""
+    if rope is not None:
+        assert decode_rotates(ctx, q, kcache, head_dim)
     if ctx.decode and attention_decode_supported(q, kcache, head_dim):
         return attention_decode(q, out, n_heads, n_kv_heads, head_dim, ctx.seq_of, ctx.pos, table, ring_pages, kcache,
-                                vcache, window, scale, max_kv=min(ctx.max_kv, window) if window else ctx.max_kv)
+                                vcache, window, scale, max_kv=min(ctx.max_kv, window) if window else ctx.max_kv,
+                                mma=True if rope is not None else None, rope=rope)
     if not ctx.decode and ctx.tiles is not None and attention_prefill_supported(q, kcache, head_dim):
         return attention_prefill(q, out, n_heads, n_kv_heads, head_dim, ctx.tiles, ctx.cu, ctx.starts, ctx.qlens, table,
                                  ring_pages, kcache, vcache, window, scale)

@@ -91,10 +91,15 @@ class Attention(Part):
             k, v = qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
         table = ctx.tables[run.group]
         pos = self.position
-        kernels.rope_kv_write(q, k, v, nh, nkv, hd, None if pos is None else pos.inv_freq,
-                              0 if pos is None else pos.rotary_dim, 0 if pos is None else pos.pairing,
-                              ctx.seq_of, ctx.pos, table, run.ring_pages, run.k if k is not None else None,
-                              run.v if k is not None else None)
+        inv_freq = None if pos is None else pos.inv_freq
+        rotary_dim, pairing = (0, 0) if pos is None else (pos.rotary_dim, pos.pairing)
+        rope = None
+        if kernels.decode_rotates(ctx, q, run.k, hd):
+            rope = (k, v, inv_freq, rotary_dim, pairing)         # single tokens: the attention kernel rotates and writes
+        else:
+            kernels.rope_kv_write(q, k, v, nh, nkv, hd, inv_freq, rotary_dim, pairing, ctx.seq_of, ctx.pos, table,
+                                  run.ring_pages, run.k if k is not None else None, run.v if k is not None else None)
         out = ctx.ws.get("attn.out", (h.shape[0], nh * hd), ctx.dtype)
-        kernels.attention(q, out, nh, nkv, hd, ctx, table, run.ring_pages, run.k, run.v, self.window or 0, self.scale)
+        kernels.attention(q, out, nh, nkv, hd, ctx, table, run.ring_pages, run.k, run.v, self.window or 0, self.scale,
+                          rope=rope)
         return self.o(out, ctx, residual=residual)

@@ -415,6 +415,54 @@ def test_attention_decode_far_key_and_window(window, mma):
     assert rel_err(want_w, want) > 0.05
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 128), (40, 2, 64), (7, 7, 128), (16, 1, 64)])
+@pytest.mark.parametrize("pairing,rot", [(0, 1.0), (1, 1.0), (0, 0.5), (0, 0.0)])
+@pytest.mark.parametrize("own_kv", [True, False])
+def test_attention_decode_rotating(nh, nkv, hd, pairing, rot, own_kv):
+    """The decode kernel that rotates q and k and writes the cache itself gives, bit for bit, the output and
+    the cache of the rotation kernel followed by the plain decode kernel: whole and split pages, a window,
+    groups of more than 16 heads (two CTAs share the token's own key), padding tokens, a position that opens
+    a page (64) and one that ends it (191)."""
+    k = K()
+    lens = [200, 1, 65, 130, 64, 513, 192]
+    _, seq_of, pos, table, kc, vc, _ = attention_case(nh, nkv, hd, lens, [1] * len(lens), BF, seed=3 * hd + nh)
+    T = len(lens) + 1
+    rows = [0, 1, 2, 4, 5, 6, 7]
+    sp = torch.full((T,), -1, dtype=torch.int32, device=DEV)
+    pp = torch.zeros(T, dtype=torch.int32, device=DEV)
+    sp[rows], pp[rows] = seq_of, pos
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=torch.Generator().manual_seed(nh + hd + pairing)).to(DEV).to(BF)
+    rotary_dim = int(hd * rot)
+    inv_freq = None
+    if rotary_dim:
+        inv_freq = (10000.0 ** (-torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim)).to(DEV)
+    scale = 1 / math.sqrt(hd)
+    for window, splits in ((0, None), (0, 1), (0, 3), (100, None), (70, 2)):
+        got = []
+        for fused in (False, True):
+            x, kc2, vc2 = qkv.clone(), kc.clone(), vc.clone()
+            q, kn, vn = x[:, :nh * hd], x[:, nh * hd:(nh + nkv) * hd], x[:, (nh + nkv) * hd:]
+            if not own_kv:
+                kn = vn = None
+            out = torch.full((T, nh * hd), float("nan"), dtype=BF, device=DEV)
+            if fused:
+                k.attention_decode(q, out, nh, nkv, hd, sp, pp, table, 1 << 20, kc2, vc2, window, scale, splits=splits,
+                                   mma=True, rope=(kn, vn, inv_freq, rotary_dim, pairing))
+                assert torch.equal(x, qkv)                       # the projections are left as they were
+            else:
+                k.rope_kv_write(q, kn, vn, nh, nkv, hd, inv_freq, rotary_dim, pairing, sp, pp, table if own_kv else None,
+                                1 << 20, kc2 if own_kv else None, vc2 if own_kv else None)
+                k.attention_decode(q, out, nh, nkv, hd, sp, pp, table, 1 << 20, kc2, vc2, window, scale, splits=splits, mma=True)
+            got.append((out, kc2, vc2))
+        (a, ka, va), (b, kb, vb) = got
+        assert torch.equal(a, b), f"window {window} splits {splits}: outputs differ by {(a.float() - b.float()).abs().max()}"
+        bits = lambda x: x.view(torch.int16)                     # unused rows of the cache hold NaNs
+        for name, u, w in (("k", ka, kb), ("v", va, vb)):
+            diff = (bits(u) != bits(w)).nonzero()
+            assert diff.numel() == 0, f"window {window} splits {splits}: {name} caches differ at {diff[:8].tolist()} of {tuple(u.shape)}"
+        assert own_kv == (not torch.equal(bits(ka), bits(kc)))
+
+
 # ---------------------------------------------------------- prefill attention
 def prefill_meta(lens, qlens):
     k = K()
