@@ -1,0 +1,186 @@
+// What the tensor-core product kernels share: tile sizes, the parameter block, the numbering of the units
+// of work, and the last steps of an output tile (the deferred norm's scale per token, bias, the gated
+// activation, the residual update).  gemm_tc.cu: one CTA per tile; gemm_tc_pair.cu: two CTAs (two SMs) per tile.
+#pragma once
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace {
+
+constexpr int BM = 128;       // output features per tile (MMA M)
+constexpr int BK = 64;        // K per stage: one 128-byte swizzled row of bf16
+constexpr int UMMA_K = 16;
+constexpr int TC_THREADS = 192;
+constexpr int A_BYTES = BM * BK * 2;
+
+template <int BN> struct TileCfg {
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    // small token tiles keep the ring near 100 KB so that two CTAs share an SM (more tiles in flight,
+    // no idle half wave when there are between one and two tiles per SM)
+    static constexpr int STAGES = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 4 : BN >= 32 ? 5 : 6;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;     // + slack to align the ring to 1024 bytes
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators
+};
+
+struct TcParams {
+    void* out;
+    const void* bias;
+    float* scratch;       // [tiles][splits][BN][128] partial sums, used when splits > 1
+    int* counters;        // [tiles], zero between launches
+    int* status;          // set non-zero when a bounded wait gave up
+    long long ldo;
+    int out_dtype, bias_dtype;
+    int T, N, K, splits;
+    int swiglu, N_out;    // swiglu: W's rows alternate gate, up; out has N_out features
+    int sms;
+    // deferred RMS norm of the input: X holds the un-normalised rows (the norm's weight is folded into W), and
+    // the result is scaled per token by 1 / sqrt(sum_i row_ssq[i][t] / norm_size + eps)
+    const float* row_ssq;
+    int ssq_parts, norm_size;
+    float eps;
+    // residual epilogue: x[t,n] += result (32-bit, in place), xb = bf16(x), and the sum over this tile's 128
+    // features of x^2 goes to ssq_out[feature tile][t] for the norm that comes next
+    float* resid_x;
+    __nv_bfloat16* resid_xb;
+    float* ssq_out;
+    long long ld_x;
+};
+
+// One unit of work: a tile of 128 features x BN tokens over one split of K.  Units are numbered
+// unit = tile * splits + split, and CTA c takes units c, c + grid, ...  Tiles are numbered so that the CTAs
+// running at one time share operands in L2: token tiles in groups of TILE_GROUP, inside a group feature tile
+// by feature tile with the group's token tiles innermost (many tokens: the group's activations stay in L2
+// while the weights stream; few tokens: one group, feature-major as the weights lie in memory).
+constexpr int TILE_GROUP = 16;
+struct Unit {
+    int tile, split, n0, t0, kb_begin, kb_end;
+};
+__device__ __forceinline__ Unit unit_of(int u, const TcParams& p, int BN, int token_tiles, int kb_total) {
+    Unit w;
+    w.tile = u / p.splits;
+    w.split = u - w.tile * p.splits;
+    const int feature_tiles = (p.N + BM - 1) / BM;
+    const int per_group = TILE_GROUP * feature_tiles;
+    const int group = w.tile / per_group, r = w.tile - group * per_group;
+    const int group_start = group * TILE_GROUP;
+    const int group_size = min(TILE_GROUP, token_tiles - group_start);
+    const int ft = r / group_size;
+    w.n0 = ft * BM;
+    w.t0 = (group_start + (r - ft * group_size)) * BN;
+    w.kb_begin = int((long long)w.split * kb_total / p.splits);
+    w.kb_end = int((long long)(w.split + 1) * kb_total / p.splits);
+    return w;
+}
+
+// The scale of each token of a tile under a deferred norm (the splits of one tile all compute the same
+// numbers): the 128 epilogue threads share the loads, GROUPS threads per token each summing every GROUPS-th
+// part with several loads in flight, then one of them adds the groups' sums in order.  rstd_s[c] is valid for
+// c < cols afterwards.
+template <int BN>
+__device__ __forceinline__ void tc_token_scales(const TcParams& p, int t0, int cols, int row, float* rstd_s, float* part_s) {
+    constexpr int SLOTS = BN < 128 ? BN : 128, GROUPS = 128 / SLOTS;
+    const int slot = row % SLOTS, grp = row / SLOTS;
+    for (int c0 = 0; c0 < BN; c0 += SLOTS) {
+        const int c = c0 + slot;
+        float ss = 0.f;
+        if (c < cols) {
+            const float* src = p.row_ssq + t0 + c;
+            for (int i = grp; i < p.ssq_parts; i += 4 * GROUPS) {
+                float ld[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    ld[e] = i + e * GROUPS < p.ssq_parts ? __ldcg(src + size_t(i + e * GROUPS) * p.T) : 0.f;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ss += ld[e];
+            }
+        }
+        part_s[grp * SLOTS + slot] = ss;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (grp == 0 && c < cols) {
+            float tot = 0.f;
+#pragma unroll
+            for (int gi = 0; gi < GROUPS; ++gi) tot += part_s[gi * SLOTS + slot];
+            rstd_s[c] = 1.f / sqrtf(tot / float(p.norm_size) + p.eps);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+}
+
+// The last steps for 16 columns (tokens c0 .. c0+15 of the tile, those below c_end being valid) of this
+// thread's feature row n = n0 + row: v[jj] holds the finished sum of column c0 + jj.
+template <int BN>
+__device__ __forceinline__ void tc_finish_chunk(const TcParams& p, int n0, int t0, int n, int row, int lane, int quarter,
+                                                float bias, bool waited, int c0, int c_end, float (&v)[16],
+                                                const float* rstd_s, float (*ssq_s)[BN]) {
+    if (p.row_ssq) {
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) v[jj] *= rstd_s[min(c0 + jj, BN - 1)];
+    }
+    if (p.resid_x) {
+        // x += result; the bf16 copy and the tile's share of sum(x^2) per token for the next norm.
+        // All of x is read before anything is written, so that the loads are in flight together.
+        float xv[16];
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj)
+            xv[jj] = (n < p.N && c0 + jj < c_end) ? __ldcg(p.resid_x + size_t(t0 + c0 + jj) * p.ld_x + n) : 0.f;
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+            float sq = 0.f;
+            if (n < p.N && c0 + jj < c_end) {
+                const size_t at = size_t(t0 + c0 + jj) * p.ld_x + n;
+                const float xn = xv[jj] + v[jj] + bias;
+                p.resid_x[at] = xn;
+                p.resid_xb[at] = __float2bfloat16_rn(xn);
+                sq = xn * xn;
+            }
+            v[jj] = sq;
+        }
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+            const float sq = gb_warp_sum(v[jj]);
+            if (lane == 0 && c0 + jj < c_end) ssq_s[quarter][c0 + jj] = sq;
+        }
+    } else if (!p.swiglu) {
+        if (n < p.N && waited) {
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj)
+                if (c0 + jj < c_end)
+                    gb_store(p.out, p.out_dtype, size_t(t0 + c0 + jj) * p.ldo + n, v[jj] + bias);
+        }
+    } else {
+        // even rows of the tile are gate features, odd rows the matching up features: the two
+        // lanes of a pair swap halves of their 16 columns, the even lane finishes columns
+        // 0..7 and the odd lane columns 8..15 of silu(gate) * up
+        const bool odd = lane & 1;
+        float other[8];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) other[jj] = __shfl_xor_sync(0xffffffffu, odd ? v[jj] : v[8 + jj], 1);
+        const int f = (n0 >> 1) + (row >> 1);          // output feature
+        if (f < p.N_out && waited) {
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+                const float gte = odd ? other[jj] : v[jj], up = odd ? v[8 + jj] : other[jj];
+                const int c = c0 + (odd ? 8 : 0) + jj;
+                if (c < c_end)
+                    gb_store(p.out, p.out_dtype, size_t(t0 + c) * p.ldo + f, gte / (1.f + expf(-gte)) * up);
+            }
+        }
+    }
+}
+
+// After tc_finish_chunk over the columns [c_begin, c_end) with a residual epilogue: the tile's sums of
+// squares per token, for the norm that comes next.
+template <int BN>
+__device__ __forceinline__ void tc_write_ssq(const TcParams& p, int n0, int t0, int row, int c_begin, int c_end,
+                                             float (*ssq_s)[BN]) {
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    for (int c = c_begin + row; c < c_end; c += 128)
+        p.ssq_out[size_t(n0 / BM) * p.T + t0 + c] = ssq_s[0][c] + ssq_s[1][c] + ssq_s[2][c] + ssq_s[3][c];
+    asm volatile("bar.sync 1, 128;" ::: "memory");     // ssq_s is written again by the next unit
+}
+
+}  // namespace
+
+// Two CTAs on two SMs per 256 x 256 tile (gemm_tc_pair.cu); taken for steps of many tokens.
+int gemm_tc_pair_launch(const CUtensorMap& mw, const CUtensorMap& mx, const void* params, cudaStream_t stream);

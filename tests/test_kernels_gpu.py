@@ -551,6 +551,52 @@ def test_gemm_tensor_core_gated(T, F, Kd):
     assert rel_err(out32, want) < 1e-5
 
 
+# ------------------------------------------ many tokens: two SMs per 256 x 256 tile
+@pytest.mark.parametrize("T,N,Kd", [(1024, 2560, 512), (1000, 2500, 328), (257, 19000, 64), (3000, 1290, 1032)])
+def test_gemm_tensor_core_two_sms_per_tile(T, N, Kd):
+    """Steps of many tokens take the kernel whose tiles are worked by a pair of CTAs; it must agree with the plain
+    product, and with the one-CTA kernel to the bit (same order of the sum over K), with ragged edges in
+    tokens, features and K, with a bias, and twice in a row."""
+    from gguf_rs_cli_b200 import native
+    k = K()
+    g = torch.Generator().manual_seed(T + N + Kd)
+    x = torch.randn(T, Kd, generator=g).to(BF).to(DEV)
+    w = (torch.randn(N, Kd, generator=g) * 0.1).to(BF).to(DEV)
+    b = torch.randn(N, generator=g).to(DEV)
+    want = P.linear(x.double().cpu(), w.double().cpu(), b.double().cpu())
+    outs = []
+    try:
+        for pair in (1, 0):
+            native.call("gb_gemm_tc_set_pair", pair)
+            out = torch.full((T, N), float("nan"), dtype=F32, device=DEV)
+            k.gemm_tc(x, w, b, out)
+            again = torch.full((T, N), float("nan"), dtype=BF, device=DEV)
+            k.gemm_tc(x, w, b, again)
+            torch.cuda.synchronize()
+            k.check_tc_status()
+            assert rel_err(out, want) < 1e-5 and rel_err(again, want) < 5e-3
+            outs.append(out)
+    finally:
+        native.call("gb_gemm_tc_set_pair", 1)
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_gemm_tensor_core_two_sms_per_tile_gated():
+    k = K()
+    T, F, Kd = 1500, 2000, 264
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(T, Kd, generator=g).to(BF).to(DEV)
+    wg = (torch.randn(F, Kd, generator=g) * 0.1).to(BF).to(DEV)
+    wu = (torch.randn(F, Kd, generator=g) * 0.1).to(BF).to(DEV)
+    w = k.interleave_gate_up(wg, wu)
+    want = P.silu(P.linear(x.double().cpu(), wg.double().cpu())) * P.linear(x.double().cpu(), wu.double().cpu())
+    out = torch.full((T, F), float("nan"), dtype=BF, device=DEV)
+    k.gemm_tc(x, w, None, out, swiglu_features=F)
+    torch.cuda.synchronize()
+    k.check_tc_status()
+    assert rel_err(out, want) < 5e-3
+
+
 # --------------------------- deferred norm and residual epilogue of the product
 @pytest.mark.parametrize("T,N,Kd", [(1, 256, 512), (8, 520, 320), (16, 4096, 4096), (70, 384, 1024), (300, 640, 328),
                                     (2100, 512, 256)])
