@@ -253,16 +253,6 @@ int group_tile(int G) { return G >= 8 ? 8 : G > 2 ? 4 : G; }
 
 }  // namespace
 
-// Splits of each token's pages for a launch of T tokens (fixed per launch, not per sequence).
-GB_API int gb_attention_decode_splits(int T, int nh, int nkv, int sms, int max_pages) {
-    int G = nh / nkv, gt = group_tile(G);
-    long long ctas = (long long)T * nkv * ((G + gt - 1) / gt);
-    int s = int((2LL * sms + ctas - 1) / ctas);
-    if (s > max_pages) s = max_pages;
-    if (s > 32) s = 32;
-    return s < 1 ? 1 : s;
-}
-
 GB_API long long gb_attention_decode_scratch_floats(int T, int nh, int hd, int splits) {
     return splits <= 1 ? 0 : (long long)T * nh * splits * (hd + 2);
 }
@@ -271,8 +261,7 @@ GB_API int gb_attention_decode_supported(int hd, int cache_dtype, int q_dtype) {
     return cache_dtype == GB_BF16 && q_dtype == GB_BF16 && hd >= 16 && hd <= 256 && hd % 16 == 0;
 }
 
-// One token per sequence: q [T, nh*hd] bf16 (rotated), cache bf16.  splits from
-// gb_attention_decode_splits; scratch and counters (T * nkv * group tiles ints, zeroed) are
+// One token per sequence: q [T, nh*hd] bf16 (rotated), cache bf16.  splits chosen by the caller; scratch and counters (T * nkv * group tiles ints, zeroed) are
 // needed when splits > 1.
 GB_API int gb_attention_decode(const void* q, long long ldq, void* out, long long ldo, int T, int nh, int nkv, int hd,
                                const int* seq_of, const int* pos, const int* table, int table_width, int ring_pages,

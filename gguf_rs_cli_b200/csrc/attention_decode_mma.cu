@@ -383,16 +383,6 @@ GB_API int gb_attention_decode_mma_supported(int hd, int cache_dtype, int q_dtyp
     return cache_dtype == GB_BF16 && q_dtype == GB_BF16 && (hd == 64 || hd == 128);
 }
 
-// Splits of each token's pages for a launch of T tokens (fixed per launch, not per sequence).
-GB_API int gb_attention_decode_mma_splits(int T, int nh, int nkv, int sms, int max_pages) {
-    int G = nh / nkv, gtiles = (G + DM_ROWS - 1) / DM_ROWS;
-    long long ctas = (long long)T * nkv * gtiles;
-    int s = int((2LL * sms + ctas - 1) / ctas);
-    if (s > max_pages) s = max_pages;
-    if (s > 32) s = 32;
-    return s < 1 ? 1 : s;
-}
-
 // Same contract as gb_attention_decode; counters: T * nkv * ceil(G/16) zeroed ints when splits > 1;
 // scratch: T * nh * splits * (hd + 2) floats.  With rotate != 0 the kernel also does what gb_rope_kv_write does
 // for these tokens: q, k_new, v_new (rows ldq apart, as the projection left them; k_new and v_new null for a

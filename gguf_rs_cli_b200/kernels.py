@@ -207,20 +207,24 @@ def attention_decode_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim: 
     return bool(native.library().gb_attention_decode_supported(head_dim, dtype_code(kcache), dtype_code(q)))
 
 
+SPLIT_CLASSES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32)
+
+
 def decode_split_class(max_kv: int) -> int:
-    """Sequences up to max_kv positions long want this many splits of their pages, if the
-    batch is too small to fill the device without (a captured graph is made per class)."""
-    return max(1, min(32, ((max_kv + 63) // 64) // 16))
+    """Sequences up to max_kv positions long want at most this many splits of their pages: 8 pages or more
+    per split (merging the splits costs more than it saves below that), rounded down to one of a few
+    values (a captured graph is made per class)."""
+    want = ((max_kv + 63) // 64) // 8
+    return max(c for c in SPLIT_CLASSES if c <= max(want, 1))
 
 
 def decode_splits(T: int, n_heads: int, n_kv_heads: int, max_kv: int, sms: int, mma: bool) -> int:
-    """Splits of each sequence's pages for a decode step: at least 16 pages per split (merging
-    the splits costs more than it saves below that), and no more than it takes to give every SM
-    two CTAs."""
+    """Splits of each sequence's pages for a decode step: the class of its longest sequence, but no more than
+    fit the device at once with two CTAs per SM (a second round of CTAs costs more than the splits save)."""
     group = n_heads // n_kv_heads
     tile = 16 if mma else (8 if group >= 8 else 4 if group > 2 else group)
     ctas = T * n_kv_heads * ((group + tile - 1) // tile)
-    return max(1, min(decode_split_class(max_kv), (2 * sms + ctas - 1) // ctas))
+    return max(1, min(decode_split_class(max_kv), (2 * sms) // ctas))
 
 
 def attention_decode_mma_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> bool:

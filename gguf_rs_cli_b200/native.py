@@ -142,11 +142,9 @@ _SIGNATURES = {
     "gb_gemm_tc_scratch_floats": [_I, _I, _I, _I],
     "gb_gemm_tc_supported": [_P, _L, _P, _L, _I],
     "gb_attention_decode": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P],
-    "gb_attention_decode_splits": [_I, _I, _I, _I, _I],
     "gb_attention_decode_mma": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P],
     "gb_attention_decode_mma_rope": [_P, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I,
                                      _P, _P, _I, _P],
-    "gb_attention_decode_mma_splits": [_I, _I, _I, _I, _I],
     "gb_attention_decode_mma_supported": [_I, _I, _I],
     "gb_attention_decode_scratch_floats": [_I, _I, _I, _I],
     "gb_attention_decode_supported": [_I, _I, _I],
