@@ -3,13 +3,15 @@
 // with both products of flash attention issued as tcgen05.mma and their results in TMEM.
 //
 // A CTA owns 128 consecutive queries of one sequence and one head and walks the keys in
-// blocks of 128 (two cache pages).  6 warps:
+// blocks of 128 (two cache pages).  10 warps:
 //   warp 0  TMA: Q once, then K and V pages into two-stage rings (128-byte swizzle);
 //   warp 1  one thread issues S = Q K^T (M128 N128 K128) into one of two TMEM buffers and,
-//           when the probabilities are ready, O += P V (V is read N-contiguous, as the cache
-//           stores it) into the output accumulator, which stays in TMEM for the whole tile;
-//   warps 2-5  one query row per thread (its TMEM lane): read S, mask, maximum and sum in
-//           32-bit, write P as bf16 into shared memory in the operand's swizzled layout.
+//           when the probabilities are ready, O += P V (P is read from TMEM, V from shared memory
+//           N-contiguous, as the cache stores it) into the output accumulator, which stays in TMEM
+//           for the whole tile;
+//   warps 2-9  two threads per query row (its TMEM lane), each with 64 of a block's 128 keys: read S,
+//           mask, maximum (agreed between the two through shared memory) and sum in 32-bit, write P as
+//           bf16 into one of two TMEM buffers (the A operand of the second product).
 //           Probabilities are taken relative to a reference maximum that is only raised when
 //           the row's maximum has grown by more than 2^8; only then is the row of O in TMEM
 //           (and the running sum) rescaled, so most blocks touch O through the MMA alone.
@@ -26,12 +28,12 @@ using namespace sm100;
 namespace {
 
 constexpr int AT_BM = 128, AT_BN = 128, AT_HD = 128;
-constexpr int AT_THREADS = 192;
+constexpr int AT_THREADS = 320;          // TMA, MMA and eight softmax warps
 constexpr int AT_CHUNK = 128 * 128;            // bytes of a [128 rows x 64 columns] bf16 tile
 constexpr int AT_TILE = 2 * AT_CHUNK;          // 32 KB: 128 x 128 bf16
 constexpr int AT_PAGE_CHUNK = 64 * 128;        // bytes of a [64 rows x 64 columns] piece of a page
-constexpr int AT_SMEM = 6 * AT_TILE + 1024;    // Q, K x2, V x2, P (+ alignment slack)
-constexpr int AT_TMEM_COLS = 512;              // S x2 (128 each) + PV (128), rounded up to a power of two
+constexpr int AT_SMEM = 5 * AT_TILE + 1024;    // Q, K x2, V x2 (+ alignment slack)
+constexpr int AT_TMEM_COLS = 512;              // S x2 (128 each), O (128), P x2 (64 each: 128 bf16 a row)
 
 struct AtParams {
     __nv_bfloat16* out;
@@ -66,10 +68,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
     uint8_t* q_s = base;
     uint8_t* k_s = base + AT_TILE;               // 2 stages
     uint8_t* v_s = base + 3 * AT_TILE;           // 2 stages
-    uint8_t* p_s = base + 5 * AT_TILE;
-    __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, p_empty;
+    __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], p_empty[2];
     __shared__ uint32_t tmem_base;
     __shared__ volatile int abort_flag;
+    __shared__ float mx_s[2][2][AT_BM], l_s[2][AT_BM];      // exchanged between the two threads of a query row
 
     gb_grid_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -90,9 +92,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
         for (int i = 0; i < 2; ++i) {
             mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 8);
         }
-        mbar_init(&p_full, 4); mbar_init(&p_empty, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&p_full[i], 8); mbar_init(&p_empty[i], 1); }
         abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_q);
@@ -107,7 +109,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
     __syncthreads();
     tc_fence_after();
     gb_grid_wait();                                // q and the cache come from the kernels before
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * AT_BN;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * AT_BN, tmem_p = tmem_base + 3 * AT_BN;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -159,51 +161,74 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
                 if (j + 1 < n_blocks) issue_qk(j + 1);            // runs under the softmax of block j
                 if (!ok) break;
                 const int s = j & 1;
-                if (!mbar_wait(&v_full[s], (j >> 1) & 1) || !mbar_wait(&p_full, j & 1)) {
+                if (!mbar_wait(&v_full[s], (j >> 1) & 1) || !mbar_wait(&p_full[s], (j >> 1) & 1)) {
                     atomicExch(p.status, 15); abort_flag = 1; break;
                 }
                 tc_fence_after();
-                const uint32_t pa = smem_u32(p_s), va = smem_u32(v_s + s * AT_TILE);
+                const uint32_t va = smem_u32(v_s + s * AT_TILE);
 #pragma unroll
                 for (int k = 0; k < AT_BN / 16; ++k)
-                    mma_f16(tmem_o, smem_desc_sw128(pa + (k >> 2) * AT_CHUNK + (k & 3) * 32),
-                            smem_desc_sw128_mn(va + k * 2048, AT_CHUNK), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                mma_commit(&p_empty);                 // P may be rewritten, and O holds this block's contribution
+                    mma_f16_a_tmem(tmem_o, tmem_p + s * 64 + k * 8, smem_desc_sw128_mn(va + k * 2048, AT_CHUNK), idesc_pv,
+                                   (j > 0 || k > 0) ? 1u : 0u);
+                mma_commit(&p_empty[s]);              // this P buffer may be rewritten, and O holds this block's contribution
                 mma_commit(&v_empty[s]);
             }
         }
     } else {
+        // two warps per quarter of the rows: warps 2..5 take the first 64 keys of every block, warps 6..9 the
+        // other 64; the two threads of a row agree on the row's maximum through shared memory
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;                       // query row = TMEM lane
         const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
         const int pq = r < rows ? pos_lo + r : -1;
         const int lo = p.window > 0 ? pq - p.window + 1 : 0;
         const float raise = 8.f / p.scale_log2;                  // the reference maximum follows only jumps beyond 2^8
+        constexpr int HB = AT_BN / 2;                            // keys per thread and block
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_blocks && ok; ++j) {
+        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
+        for (int j = 0; j < n_blocks; ++j) {
+            // after a wait has given up this warp only keeps its appointments with its partner (a named barrier
+            // does not time out)
+            if (!ok) { pair_sync(); continue; }
             const int s = j & 1;
-            const int key0 = (pg_begin + 2 * j) * GB_PAGE;
-            if (!mbar_wait(&s_full[s], (j >> 1) & 1)) { if (lane == 0) atomicExch(p.status, 16); abort_flag = 1; break; }
+            const int key0 = (pg_begin + 2 * j) * GB_PAGE + half * HB;
+            if (!mbar_wait(&s_full[s], (j >> 1) & 1)) {
+                if (lane == 0) atomicExch(p.status, 16);
+                abort_flag = 1;
+                ok = false;
+                pair_sync();
+                continue;
+            }
             tc_fence_after();
-            const uint32_t s_addr = tmem_s + s * AT_BN + lane_addr;
-            const bool need_mask = key0 + AT_BN - 1 > pos_lo || p.window > 0 || r >= rows;
-            float v[AT_BN];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, v + 32 * c);
+            const uint32_t s_addr = tmem_s + s * AT_BN + half * HB + lane_addr;
+            const bool need_mask = key0 + HB - 1 > pos_lo || p.window > 0 || r >= rows;
+            float v[HB];
+            tmem_ld64(s_addr, v);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[s]);               // S may be overwritten by the block after next
             float mx = -INFINITY;
             if (need_mask) {
 #pragma unroll
-                for (int i = 0; i < AT_BN; ++i) {
+                for (int i = 0; i < HB; ++i) {
                     const int ka = key0 + i;
                     if (ka > pq || ka < lo) v[i] = -INFINITY;
                 }
             }
+            {
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one long one
 #pragma unroll
-            for (int i = 0; i < AT_BN; ++i) mx = fmaxf(mx, v[i]);
+                for (int i = 0; i < HB; i += 4) {
+                    m4[0] = fmaxf(m4[0], v[i]); m4[1] = fmaxf(m4[1], v[i + 1]);
+                    m4[2] = fmaxf(m4[2], v[i + 2]); m4[3] = fmaxf(m4[3], v[i + 3]);
+                }
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            }
+            mx_s[s][half][r] = mx;
+            pair_sync();
+            mx = fmaxf(mx, mx_s[s][half ^ 1][r]);
             // raise the reference when the maximum has run away from it (or there was none yet)
             float factor = 1.f;
             if (mx > -INFINITY && (m_ref == -INFINITY || mx > m_ref + raise)) {
@@ -211,65 +236,85 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
                 m_ref = mx;
             }
             const float ms = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
-            float add = 0.f;
+            // two elements per instruction for the scaling and the sum; masked entries are -inf: 2^-inf is 0
+            float add;
+            {
+                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ms2 = make_float2(-ms, -ms);
+                float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int i = 0; i < AT_BN; ++i) {
-                v[i] = exp2f(fmaf(v[i], p.scale_log2, -ms));        // masked entries are -inf: exp2 gives 0
-                add += v[i];
+                for (int i = 0; i < HB; i += 2) {
+                    float2 t = __ffma2_rn(make_float2(v[i], v[i + 1]), sc2, ms2);
+                    t.x = ex2_approx(t.x);
+                    t.y = ex2_approx(t.y);
+                    v[i] = t.x;
+                    v[i + 1] = t.y;
+                    acc[(i >> 1) & 3] = __fadd2_rn(acc[(i >> 1) & 3], t);
+                }
+                const float2 a01 = __fadd2_rn(acc[0], acc[1]), a23 = __fadd2_rn(acc[2], acc[3]);
+                add = (a01.x + a01.y) + (a23.x + a23.y);
             }
-            // P(j-1) has been consumed and O holds every block before this one
-            if (!mbar_wait(&p_empty, (j & 1) ^ 1)) { if (lane == 0) atomicExch(p.status, 17); abort_flag = 1; break; }
             if (j > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+                // O must hold every block before this one before its rows are rescaled
+                if (!mbar_wait(&p_empty[s ^ 1], ((j - 1) >> 1) & 1)) { if (lane == 0) atomicExch(p.status, 17); abort_flag = 1; ok = false; continue; }
                 tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < 2; ++c) {                       // this thread's half of the row of O
                     float o[32];
-                    tmem_ld32(tmem_o + lane_addr + 32 * c, o);
+                    tmem_ld32(tmem_o + lane_addr + half * 64 + 32 * c, o);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] *= factor;
-                    tmem_st32(tmem_o + lane_addr + 32 * c, o);
+                    tmem_st32(tmem_o + lane_addr + half * 64 + 32 * c, o);
                 }
                 tc_fence_before();
             }
             l = l * factor + add;
-            // P as bf16 in the operand layout: 16-byte pieces of a row are XOR-swizzled with the row number, as
-            // TMA would have stored them
+            // P as bf16 into this block's TMEM buffer, once the product of the block before last has read it
+            if (!mbar_wait(&p_empty[s], ((j >> 1) & 1) ^ 1)) { if (lane == 0) atomicExch(p.status, 17); abort_flag = 1; ok = false; continue; }
+            {
+                uint32_t w[HB / 2];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint8_t* row = p_s + c * AT_CHUNK + r * 128;
-#pragma unroll
-                for (int piece = 0; piece < 8; ++piece)
-                    *reinterpret_cast<uint4*>(row + ((piece ^ (r & 7)) << 4)) = pack8(v + 64 * c + 8 * piece);
+                for (int i = 0; i < HB / 2; ++i) {
+                    __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                    w[i] = *reinterpret_cast<uint32_t*>(&t);
+                }
+                tmem_st32_words(tmem_p + s * 64 + half * 32 + lane_addr, w);
+                tc_fence_before();
             }
-            if (key0 + AT_BN - 1 > valid_end) {
+            if ((pg_begin + 2 * j) * GB_PAGE + AT_BN - 1 > valid_end) {
                 // key row r of this block holds nothing meaningful if it lies beyond the sequence's end (never
                 // written) or in a page this tile did not load: zero its values before they are multiplied
+                // (each of the row's two threads zeroes one half of the head's dimensions)
                 if (mbar_wait(&v_full[s], (j >> 1) & 1)) {
-                    if (key0 + r > valid_end) {
+                    if ((pg_begin + 2 * j) * GB_PAGE + r > valid_end) {
                         uint4 z = make_uint4(0, 0, 0, 0);
-                        for (int c = 0; c < 2; ++c)
-                            for (int piece = 0; piece < 8; ++piece)
-                                *reinterpret_cast<uint4*>(v_s + s * AT_TILE + c * AT_CHUNK + r * 128 + piece * 16) = z;
+                        for (int piece = 0; piece < 8; ++piece)
+                            *reinterpret_cast<uint4*>(v_s + s * AT_TILE + half * AT_CHUNK + r * 128 + piece * 16) = z;
                     }
+                    fence_proxy_async();                           // the patch is visible to the tensor core
                 } else {
                     if (lane == 0) atomicExch(p.status, 18);
                     abort_flag = 1;
                     ok = false;
                 }
             }
-            fence_proxy_async();                                   // P (and the patch) are visible to the tensor core
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full);
+            if (lane == 0) mbar_arrive(&p_full[s]);
         }
-        // the last block's product has been added to O when P could be written once more
-        if (ok && n_blocks > 0 && !mbar_wait(&p_empty, (n_blocks & 1) ^ 1)) { if (lane == 0) atomicExch(p.status, 19); ok = false; }
+        // the last block's product has been added to O when its P buffer is free again
+        if (ok && n_blocks > 0 && !mbar_wait(&p_empty[(n_blocks - 1) & 1], ((n_blocks - 1) >> 1) & 1)) {
+            if (lane == 0) atomicExch(p.status, 19);
+            ok = false;
+        }
         tc_fence_after();
+        l_s[half][r] = l;
+        pair_sync();
+        l += l_s[half ^ 1][r];
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* dst = p.out + size_t(tok0 + r) * p.ldo + size_t(h) * AT_HD;
+        __nv_bfloat16* dst = p.out + size_t(tok0 + r) * p.ldo + size_t(h) * AT_HD + half * 64;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
             float o[32];
-            tmem_ld32(tmem_o + lane_addr + 32 * c, o);              // every lane takes part; rows beyond the tile are not stored
+            tmem_ld32(tmem_o + lane_addr + half * 64 + 32 * c, o);  // every lane takes part; rows beyond the tile are not stored
             if (r < rows && ok && n_blocks > 0) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
