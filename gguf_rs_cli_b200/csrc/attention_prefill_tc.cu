@@ -2,16 +2,17 @@
 // arithmetic as attention_prefill.cu and the generic kernel (src/model/llama.rs:374-394),
 // with both products of flash attention issued as tcgen05.mma and their results in TMEM.
 //
-// A CTA owns 128 consecutive queries of one sequence and one head and walks the keys in
-// blocks of 128 (two cache pages).  10 warps:
-//   warp 0  TMA: Q once, then K and V pages into two-stage rings (128-byte swizzle);
-//   warp 1  one thread issues S = Q K^T (M128 N128 K128) into one of two TMEM buffers and,
-//           when the probabilities are ready, O += P V (P is read from TMEM, V from shared memory
-//           N-contiguous, as the cache stores it) into the output accumulator, which stays in TMEM
-//           for the whole tile;
-//   warps 2-9  two threads per query row (its TMEM lane), each with 64 of a block's 128 keys: read S,
-//           mask, maximum (agreed between the two through shared memory) and sum in 32-bit, write P as
-//           bf16 into one of two TMEM buffers (the A operand of the second product).
+// A CTA owns 256 consecutive queries of one sequence and one head as two tiles of 128 and walks
+// the keys in blocks of 128 (two cache pages) that both tiles share.  10 warps:
+//   warp 0  TMA: both Q tiles once, then K and V pages into two-stage rings (128-byte swizzle);
+//   warp 1  one thread issues, tile by tile, S = Q K^T (M128 N128 K128) into the tile's TMEM
+//           buffer and, when the tile's probabilities are ready, O += P V (P read from TMEM,
+//           V from shared memory N-contiguous, as the cache stores it) into the tile's
+//           output accumulator, which stays in TMEM for the whole tile.  While one tile's
+//           warps work on their softmax the tensor core serves the other tile;
+//   warps 2-5 and 6-9  one tile each, one query row per thread (its TMEM lane): a first
+//           pass over S for the row's maximum, a second for the probabilities, in 32-bit;
+//           P goes back as bf16 into the first half of the columns S came from.
 //           Probabilities are taken relative to a reference maximum that is only raised when
 //           the row's maximum has grown by more than 2^8; only then is the row of O in TMEM
 //           (and the running sum) rescaled, so most blocks touch O through the MMA alone.
@@ -28,12 +29,13 @@ using namespace sm100;
 namespace {
 
 constexpr int AT_BM = 128, AT_BN = 128, AT_HD = 128;
-constexpr int AT_THREADS = 320;          // TMA, MMA and eight softmax warps
+constexpr int AT_PAIR = 2 * AT_BM;             // queries per CTA
+constexpr int AT_THREADS = 320;                // TMA, MMA and two tiles of four softmax warps
 constexpr int AT_CHUNK = 128 * 128;            // bytes of a [128 rows x 64 columns] bf16 tile
 constexpr int AT_TILE = 2 * AT_CHUNK;          // 32 KB: 128 x 128 bf16
 constexpr int AT_PAGE_CHUNK = 64 * 128;        // bytes of a [64 rows x 64 columns] piece of a page
-constexpr int AT_SMEM = 5 * AT_TILE + 1024;    // Q, K x2, V x2 (+ alignment slack)
-constexpr int AT_TMEM_COLS = 512;              // S x2 (128 each), O (128), P x2 (64 each: 128 bf16 a row)
+constexpr int AT_SMEM = 6 * AT_TILE + 1024;    // Q x2, K x2, V x2 (+ alignment slack)
+constexpr int AT_TMEM_COLS = 512;              // per tile: S (128; P in its first 64) and O (128)
 
 struct AtParams {
     __nv_bfloat16* out;
@@ -65,25 +67,37 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
                                                                              AtParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* q_s = base;
-    uint8_t* k_s = base + AT_TILE;               // 2 stages
-    uint8_t* v_s = base + 3 * AT_TILE;           // 2 stages
-    __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], p_empty[2];
+    uint8_t* q_s = base;                         // 2 tiles
+    uint8_t* k_s = base + 2 * AT_TILE;           // 2 stages
+    uint8_t* v_s = base + 4 * AT_TILE;           // 2 stages
+    __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2];
     __shared__ uint32_t tmem_base;
     __shared__ volatile int abort_flag;
-    __shared__ float mx_s[2][2][AT_BM], l_s[2][AT_BM];      // exchanged between the two threads of a query row
 
     gb_grid_launch_dependents();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the list holds tiles of 128 queries; this kernel takes them two at a time, from the even ones
     const int b = p.tiles[2 * blockIdx.y], q0 = p.tiles[2 * blockIdx.y + 1];
+    if (q0 % AT_PAIR != 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, g = h / (p.nh / p.nkv);
     const int start = p.starts[b], qlen = p.qlens[b], tok0 = p.cu[b] + q0;
-    const int rows = min(AT_BM, qlen - q0);
     const int last_pos = start + qlen - 1;
-    const int pos_lo = start + q0, pos_hi = pos_lo + rows - 1;
-    const int pg_begin = p.window > 0 ? max(0, pos_lo - p.window + 1) >> GB_PAGE_SHIFT : 0;
+    // per tile: its rows, the positions of its first and last query, and its blocks [first, end) in the grid
+    // of 128-key blocks that starts at the page of the earliest key the first tile may see
+    int rows[2], pos_lo[2], blk_first[2], blk_end[2];
+    const int lo0 = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
+    const int pg_base = lo0 >> GB_PAGE_SHIFT;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        rows[t] = max(0, min(AT_BM, qlen - q0 - t * AT_BM));
+        pos_lo[t] = start + q0 + t * AT_BM;
+        const int lo = p.window > 0 ? max(0, pos_lo[t] - p.window + 1) : 0;
+        blk_first[t] = rows[t] > 0 ? ((lo >> GB_PAGE_SHIFT) - pg_base) / 2 : 0;
+        blk_end[t] = rows[t] > 0 ? (((pos_lo[t] + rows[t] - 1) >> GB_PAGE_SHIFT) - pg_base) / 2 + 1 : 0;
+    }
+    const int n_blocks = max(blk_end[0], blk_end[1]);
+    const int pos_hi = start + q0 + rows[0] + rows[1] - 1;                 // the CTA's last query
     const int pg_end = (pos_hi >> GB_PAGE_SHIFT) + 1;
-    const int n_blocks = (pg_end - pg_begin + 1) / 2;
     const int valid_end = min(last_pos, pg_end * GB_PAGE - 1);   // last key position that was both written and loaded
     const int* trow = p.table + size_t(b) * p.table_width;
 
@@ -92,9 +106,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
         for (int i = 0; i < 2; ++i) {
             mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 8);
+            mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&pv_done[i], 1);
         }
-        for (int i = 0; i < 2; ++i) { mbar_init(&p_full[i], 8); mbar_init(&p_empty[i], 1); }
         abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_q);
@@ -109,28 +122,29 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
     __syncthreads();
     tc_fence_after();
     gb_grid_wait();                                // q and the cache come from the kernels before
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * AT_BN, tmem_p = tmem_base + 3 * AT_BN;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * AT_BN;     // + tile * 128 each
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_expect_tx(&q_full, AT_TILE);
-            tma_load_2d(q_s, &map_q, h * AT_HD, tok0, &q_full);
-            tma_load_2d(q_s + AT_CHUNK, &map_q, h * AT_HD + 64, tok0, &q_full);
+            mbar_expect_tx(&q_full, 2 * AT_TILE);
+            for (int t = 0; t < 2; ++t)
+                for (int c = 0; c < 2; ++c)
+                    tma_load_2d(q_s + t * AT_TILE + c * AT_CHUNK, &map_q, h * AT_HD + 64 * c, tok0 + t * AT_BM, &q_full);
             for (int j = 0; j < n_blocks && !abort_flag; ++j) {
                 const int s = j & 1;
                 const uint32_t par = ((j >> 1) & 1) ^ 1;
-                const int pages = min(2, pg_end - (pg_begin + 2 * j));          // the last block may hold one page
+                const int pages = min(2, pg_end - (pg_base + 2 * j));          // the last block may hold one page
                 if (!mbar_wait(&k_empty[s], par)) { atomicExch(p.status, 11); abort_flag = 1; break; }
                 mbar_expect_tx(&k_full[s], pages * 2 * AT_PAGE_CHUNK);
                 for (int pg = 0; pg < pages; ++pg) {
-                    const int y = (trow[(pg_begin + 2 * j + pg) % p.ring_pages] * p.nkv + g) * GB_PAGE;
+                    const int y = (trow[(pg_base + 2 * j + pg) % p.ring_pages] * p.nkv + g) * GB_PAGE;
                     for (int c = 0; c < 2; ++c)
                         tma_load_2d(k_s + s * AT_TILE + c * AT_CHUNK + pg * AT_PAGE_CHUNK, &map_k, 64 * c, y, &k_full[s]);
                 }
                 if (!mbar_wait(&v_empty[s], par)) { atomicExch(p.status, 12); abort_flag = 1; break; }
                 mbar_expect_tx(&v_full[s], pages * 2 * AT_PAGE_CHUNK);
                 for (int pg = 0; pg < pages; ++pg) {
-                    const int y = (trow[(pg_begin + 2 * j + pg) % p.ring_pages] * p.nkv + g) * GB_PAGE;
+                    const int y = (trow[(pg_base + 2 * j + pg) % p.ring_pages] * p.nkv + g) * GB_PAGE;
                     for (int c = 0; c < 2; ++c)
                         tma_load_2d(v_s + s * AT_TILE + c * AT_CHUNK + pg * AT_PAGE_CHUNK, &map_v, 64 * c, y, &v_full[s]);
                 }
@@ -142,93 +156,87 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
             constexpr uint32_t idesc_pv = instr_desc_bf16_b_mn(AT_BM, AT_HD);
             bool ok = mbar_wait(&q_full, 0);
             if (!ok) { atomicExch(p.status, 13); abort_flag = 1; }
-            auto issue_qk = [&](int j) {
+            auto active = [&](int t, int j) { return j >= blk_first[t] && j < blk_end[t]; };
+            // S of tile t for block j; it overwrites the tile's S and P of the block before, whose product was
+            // issued earlier by this thread
+            auto issue_qk = [&](int t, int j) {
                 const int s = j & 1;
-                const uint32_t par = (j >> 1) & 1;
-                if (!mbar_wait(&k_full[s], par) || !mbar_wait(&s_empty[s], par ^ 1)) { atomicExch(p.status, 14); abort_flag = 1; ok = false; return; }
+                if (!mbar_wait(&k_full[s], (j >> 1) & 1)) { atomicExch(p.status, 14); abort_flag = 1; ok = false; return; }
                 tc_fence_after();
-                const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + s * AT_TILE);
+                const uint32_t qa = smem_u32(q_s + t * AT_TILE), ka = smem_u32(k_s + s * AT_TILE);
 #pragma unroll
                 for (int k = 0; k < AT_HD / 16; ++k) {
                     const uint32_t off = (k >> 2) * AT_CHUNK + (k & 3) * 32;
-                    mma_f16(tmem_s + s * AT_BN, smem_desc_sw128(qa + off), smem_desc_sw128(ka + off), idesc_qk, k > 0 ? 1u : 0u);
+                    mma_f16(tmem_s + t * AT_BN, smem_desc_sw128(qa + off), smem_desc_sw128(ka + off), idesc_qk, k > 0 ? 1u : 0u);
                 }
-                mma_commit(&s_full[s]);
-                mma_commit(&k_empty[s]);
+                mma_commit(&s_full[t]);
             };
-            if (ok && n_blocks > 0) issue_qk(0);
+            int done[2] = {0, 0};                              // blocks multiplied into O per tile
+            for (int t = 0; t < 2 && ok; ++t)
+                if (active(t, 0)) issue_qk(t, 0);
+            if (ok && n_blocks > 0) mma_commit(&k_empty[0]);
             for (int j = 0; j < n_blocks && ok && !abort_flag; ++j) {
-                if (j + 1 < n_blocks) issue_qk(j + 1);            // runs under the softmax of block j
-                if (!ok) break;
                 const int s = j & 1;
-                if (!mbar_wait(&v_full[s], (j >> 1) & 1) || !mbar_wait(&p_full[s], (j >> 1) & 1)) {
-                    atomicExch(p.status, 15); abort_flag = 1; break;
-                }
-                tc_fence_after();
-                const uint32_t va = smem_u32(v_s + s * AT_TILE);
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (active(t, j)) {
+                        if (!mbar_wait(&v_full[s], (j >> 1) & 1) || !mbar_wait(&p_full[t], done[t] & 1)) {
+                            atomicExch(p.status, 15); abort_flag = 1; ok = false; break;
+                        }
+                        tc_fence_after();
+                        const uint32_t va = smem_u32(v_s + s * AT_TILE);
 #pragma unroll
-                for (int k = 0; k < AT_BN / 16; ++k)
-                    mma_f16_a_tmem(tmem_o, tmem_p + s * 64 + k * 8, smem_desc_sw128_mn(va + k * 2048, AT_CHUNK), idesc_pv,
-                                   (j > 0 || k > 0) ? 1u : 0u);
-                mma_commit(&p_empty[s]);              // this P buffer may be rewritten, and O holds this block's contribution
+                        for (int k = 0; k < AT_BN / 16; ++k)
+                            mma_f16_a_tmem(tmem_o + t * AT_HD, tmem_s + t * AT_BN + k * 8, smem_desc_sw128_mn(va + k * 2048, AT_CHUNK),
+                                           idesc_pv, (done[t] > 0 || k > 0) ? 1u : 0u);
+                        mma_commit(&pv_done[t]);              // O of the tile holds this block
+                        ++done[t];
+                    }
+                    if (j + 1 < n_blocks && active(t, j + 1)) issue_qk(t, j + 1);     // runs under the other tile's softmax
+                }
+                if (!ok) break;
                 mma_commit(&v_empty[s]);
+                if (j + 1 < n_blocks) mma_commit(&k_empty[(j + 1) & 1]);
             }
         }
     } else {
-        // two warps per quarter of the rows: warps 2..5 take the first 64 keys of every block, warps 6..9 the
-        // other 64; the two threads of a row agree on the row's maximum through shared memory
+        const int t = (warp - 2) >> 2;                           // the tile of this warp
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
-        const int r = quarter * 32 + lane;                       // query row = TMEM lane
+        const int r = quarter * 32 + lane;                       // query row of the tile = TMEM lane
         const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
-        const int pq = r < rows ? pos_lo + r : -1;
+        const uint32_t s_addr = tmem_s + t * AT_BN + lane_addr, o_addr = tmem_o + t * AT_HD + lane_addr;
+        const int pq = r < rows[t] ? pos_lo[t] + r : -1;
         const int lo = p.window > 0 ? pq - p.window + 1 : 0;
         const float raise = 8.f / p.scale_log2;                  // the reference maximum follows only jumps beyond 2^8
-        constexpr int HB = AT_BN / 2;                            // keys per thread and block
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
-        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
-        for (int j = 0; j < n_blocks; ++j) {
-            // after a wait has given up this warp only keeps its appointments with its partner (a named barrier
-            // does not time out)
-            if (!ok) { pair_sync(); continue; }
+        int c = 0;                                               // blocks done by this tile
+        for (int j = blk_first[t]; j < blk_end[t] && ok; ++j, ++c) {
             const int s = j & 1;
-            const int key0 = (pg_begin + 2 * j) * GB_PAGE + half * HB;
-            if (!mbar_wait(&s_full[s], (j >> 1) & 1)) {
-                if (lane == 0) atomicExch(p.status, 16);
-                abort_flag = 1;
-                ok = false;
-                pair_sync();
-                continue;
-            }
+            const int key0 = (pg_base + 2 * j) * GB_PAGE;
+            if (!mbar_wait(&s_full[t], c & 1)) { if (lane == 0) atomicExch(p.status, 16); abort_flag = 1; ok = false; break; }
             tc_fence_after();
-            const uint32_t s_addr = tmem_s + s * AT_BN + half * HB + lane_addr;
-            const bool need_mask = key0 + HB - 1 > pos_lo || p.window > 0 || r >= rows;
-            float v[HB];
-            tmem_ld64(s_addr, v);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[s]);               // S may be overwritten by the block after next
+            const bool need_mask = key0 + AT_BN - 1 > pos_lo[t] || p.window > 0 || r >= rows[t];
+            float v[64];
+            // first pass: the row's maximum over the block
             float mx = -INFINITY;
-            if (need_mask) {
 #pragma unroll
-                for (int i = 0; i < HB; ++i) {
-                    const int ka = key0 + i;
-                    if (ka > pq || ka < lo) v[i] = -INFINITY;
+            for (int hh = 0; hh < 2; ++hh) {
+                tmem_ld64(s_addr + 64 * hh, v);
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int ka = key0 + 64 * hh + i;
+                        if (ka > pq || ka < lo) v[i] = -INFINITY;
+                    }
                 }
-            }
-            {
                 float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one long one
 #pragma unroll
-                for (int i = 0; i < HB; i += 4) {
+                for (int i = 0; i < 64; i += 4) {
                     m4[0] = fmaxf(m4[0], v[i]); m4[1] = fmaxf(m4[1], v[i + 1]);
                     m4[2] = fmaxf(m4[2], v[i + 2]); m4[3] = fmaxf(m4[3], v[i + 3]);
                 }
-                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
             }
-            mx_s[s][half][r] = mx;
-            pair_sync();
-            mx = fmaxf(mx, mx_s[s][half ^ 1][r]);
             // raise the reference when the maximum has run away from it (or there was none yet)
             float factor = 1.f;
             if (mx > -INFINITY && (m_ref == -INFINITY || mx > m_ref + raise)) {
@@ -236,59 +244,62 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
                 m_ref = mx;
             }
             const float ms = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
-            // two elements per instruction for the scaling and the sum; masked entries are -inf: 2^-inf is 0
-            float add;
-            {
-                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ms2 = make_float2(-ms, -ms);
-                float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-                for (int i = 0; i < HB; i += 2) {
-                    float2 t = __ffma2_rn(make_float2(v[i], v[i + 1]), sc2, ms2);
-                    t.x = ex2_approx(t.x);
-                    t.y = ex2_approx(t.y);
-                    v[i] = t.x;
-                    v[i + 1] = t.y;
-                    acc[(i >> 1) & 3] = __fadd2_rn(acc[(i >> 1) & 3], t);
-                }
-                const float2 a01 = __fadd2_rn(acc[0], acc[1]), a23 = __fadd2_rn(acc[2], acc[3]);
-                add = (a01.x + a01.y) + (a23.x + a23.y);
-            }
-            if (j > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+            if (c > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
                 // O must hold every block before this one before its rows are rescaled
-                if (!mbar_wait(&p_empty[s ^ 1], ((j - 1) >> 1) & 1)) { if (lane == 0) atomicExch(p.status, 17); abort_flag = 1; ok = false; continue; }
+                if (!mbar_wait(&pv_done[t], (c - 1) & 1)) { if (lane == 0) atomicExch(p.status, 17); abort_flag = 1; ok = false; break; }
                 tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < 2; ++c) {                       // this thread's half of the row of O
+                for (int cc = 0; cc < 4; ++cc) {
                     float o[32];
-                    tmem_ld32(tmem_o + lane_addr + half * 64 + 32 * c, o);
+                    tmem_ld32(o_addr + 32 * cc, o);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] *= factor;
-                    tmem_st32(tmem_o + lane_addr + half * 64 + 32 * c, o);
+                    tmem_st32(o_addr + 32 * cc, o);
                 }
                 tc_fence_before();
+            }
+            // second pass: probabilities (two elements per instruction for the scaling and the sum; masked
+            // entries are -inf: 2^-inf is 0), written as bf16 over the first half of the columns S came from:
+            // keys 0..63 into columns 0..31 once columns 0..63 are in registers, keys 64..127 into columns 32..63
+            float add = 0.f;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                tmem_ld64(s_addr + 64 * hh, v);
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int ka = key0 + 64 * hh + i;
+                        if (ka > pq || ka < lo) v[i] = -INFINITY;
+                    }
+                }
+                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ms2 = make_float2(-ms, -ms);
+                float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+                uint32_t w[32];
+#pragma unroll
+                for (int i = 0; i < 64; i += 2) {
+                    float2 e = __ffma2_rn(make_float2(v[i], v[i + 1]), sc2, ms2);
+                    e.x = ex2_approx(e.x);
+                    e.y = ex2_approx(e.y);
+                    acc[(i >> 1) & 3] = __fadd2_rn(acc[(i >> 1) & 3], e);
+                    __nv_bfloat162 pk = __floats2bfloat162_rn(e.x, e.y);
+                    w[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+                }
+                const float2 a01 = __fadd2_rn(acc[0], acc[1]), a23 = __fadd2_rn(acc[2], acc[3]);
+                add += (a01.x + a01.y) + (a23.x + a23.y);
+                tmem_st32_words(s_addr + 32 * hh, w);
             }
             l = l * factor + add;
-            // P as bf16 into this block's TMEM buffer, once the product of the block before last has read it
-            if (!mbar_wait(&p_empty[s], ((j >> 1) & 1) ^ 1)) { if (lane == 0) atomicExch(p.status, 17); abort_flag = 1; ok = false; continue; }
-            {
-                uint32_t w[HB / 2];
-#pragma unroll
-                for (int i = 0; i < HB / 2; ++i) {
-                    __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                    w[i] = *reinterpret_cast<uint32_t*>(&t);
-                }
-                tmem_st32_words(tmem_p + s * 64 + half * 32 + lane_addr, w);
-                tc_fence_before();
-            }
-            if ((pg_begin + 2 * j) * GB_PAGE + AT_BN - 1 > valid_end) {
+            tc_fence_before();
+            if (key0 + AT_BN - 1 > valid_end) {
                 // key row r of this block holds nothing meaningful if it lies beyond the sequence's end (never
-                // written) or in a page this tile did not load: zero its values before they are multiplied
-                // (each of the row's two threads zeroes one half of the head's dimensions)
+                // written) or in a page this CTA did not load: zero its values before they are multiplied (both
+                // tiles do so before their own product of this block)
                 if (mbar_wait(&v_full[s], (j >> 1) & 1)) {
-                    if ((pg_begin + 2 * j) * GB_PAGE + r > valid_end) {
+                    if (key0 + r > valid_end) {
                         uint4 z = make_uint4(0, 0, 0, 0);
-                        for (int piece = 0; piece < 8; ++piece)
-                            *reinterpret_cast<uint4*>(v_s + s * AT_TILE + half * AT_CHUNK + r * 128 + piece * 16) = z;
+                        for (int cc = 0; cc < 2; ++cc)
+                            for (int piece = 0; piece < 8; ++piece)
+                                *reinterpret_cast<uint4*>(v_s + s * AT_TILE + cc * AT_CHUNK + r * 128 + piece * 16) = z;
                     }
                     fence_proxy_async();                           // the patch is visible to the tensor core
                 } else {
@@ -298,30 +309,26 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[s]);
+            if (lane == 0) mbar_arrive(&p_full[t]);
         }
-        // the last block's product has been added to O when its P buffer is free again
-        if (ok && n_blocks > 0 && !mbar_wait(&p_empty[(n_blocks - 1) & 1], ((n_blocks - 1) >> 1) & 1)) {
-            if (lane == 0) atomicExch(p.status, 19);
-            ok = false;
-        }
+        // the tile's last product has been added to O
+        if (ok && c > 0 && !mbar_wait(&pv_done[t], (c - 1) & 1)) { if (lane == 0) atomicExch(p.status, 19); ok = false; }
         tc_fence_after();
-        l_s[half][r] = l;
-        pair_sync();
-        l += l_s[half ^ 1][r];
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* dst = p.out + size_t(tok0 + r) * p.ldo + size_t(h) * AT_HD + half * 64;
+        __nv_bfloat16* dst = p.out + size_t(tok0 + t * AT_BM + r) * p.ldo + size_t(h) * AT_HD;
+        if (c > 0) {
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-            float o[32];
-            tmem_ld32(tmem_o + lane_addr + half * 64 + 32 * c, o);  // every lane takes part; rows beyond the tile are not stored
-            if (r < rows && ok && n_blocks > 0) {
+            for (int cc = 0; cc < 4; ++cc) {
+                float o[32];
+                tmem_ld32(o_addr + 32 * cc, o);                    // every lane takes part; rows beyond the tile are not stored
+                if (r < rows[t] && ok) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    float t[8];
+                    for (int i = 0; i < 32; i += 8) {
+                        float tt[8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) t[e] = o[i + e] * inv;
-                    *reinterpret_cast<uint4*>(dst + 32 * c + i) = pack8(t);
+                        for (int e = 0; e < 8; ++e) tt[e] = o[i + e] * inv;
+                        *reinterpret_cast<uint4*>(dst + 32 * cc + i) = pack8(tt);
+                    }
                 }
             }
         }
