@@ -238,24 +238,26 @@ EncodeTiledFn encode_fn() {
 struct MapKey {
     const void* ptr;
     long long rows, cols, ld;
-    int box_rows;
+    int box_rows, box_cols;
     bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && box_cols == o.box_cols;
     }
 };
 struct MapKeyHash {
     size_t operator()(const MapKey& k) const {
         size_t h = std::hash<const void*>()(k.ptr);
-        for (long long v : {k.rows, k.cols, k.ld, (long long)k.box_rows}) h = h * 1000003u ^ std::hash<long long>()(v);
+        for (long long v : {k.rows, k.cols, k.ld, (long long)k.box_rows, (long long)k.box_cols}) h = h * 1000003u ^ std::hash<long long>()(v);
         return h;
     }
 };
 
-// Tensor map of a row-major bf16 matrix [rows, cols] with pitch ld, box [box_rows x 64], 128-byte swizzle.
-int tensor_map_2d(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+// Tensor map of a row-major bf16 matrix [rows, cols] with pitch ld: box [box_rows x 64] with the 128-byte swizzle
+// (operands), or, with box_cols given, [box_rows x box_cols] without a swizzle (tiles stored from shared memory).
+int tensor_map_2d(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out,
+                  int box_cols = 0) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     static std::mutex mu;
-    MapKey key{ptr, rows, cols, ld, box_rows};
+    MapKey key{ptr, rows, cols, ld, box_rows, box_cols};
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) { *out = it->second; return 0; }
@@ -263,11 +265,11 @@ int tensor_map_2d(const void* ptr, long long rows, long long cols, long long ld,
     if (!fn) return gb_fail("gb_gemm_tc: the driver gives no cuTensorMapEncodeTiled");
     cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
     cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
-    cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(box_rows)};
+    cuuint32_t box[2] = {cuuint32_t(box_cols ? box_cols : BK), cuuint32_t(box_rows)};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return gb_fail("gb_gemm_tc: cuTensorMapEncodeTiled failed with code %d", int(r));
     if (cache.size() > 8192) cache.clear();
     cache.emplace(key, *out);
@@ -426,9 +428,13 @@ static int gemm_tc_impl(const void* X, long long ldx, const void* W, long long l
     CUtensorMap mw, mx;
     if (tensor_map_2d(W, N, K, ldw, BM, &mw)) return 1;
     if (bn == 256 && g_pair && p.splits == 1) {
-        // many tokens: two SMs per 256 x 256 tile, each loading 128 tokens of X per stage
+        // many tokens: two SMs per 256 x 256 tile, each loading 128 tokens of X per stage; bf16 results leave
+        // through shared memory and TMA stores of [16 tokens x 128 features] (64 features after SwiGLU)
         if (tensor_map_2d(X, T, K, ldx, 128, &mx)) return 1;
-        return gemm_tc_pair_launch(mw, mx, &p, stream);
+        CUtensorMap mo;
+        const bool staged = !resid_x && out_dtype == GB_BF16 && ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+        if (staged && tensor_map_2d(out, T, swiglu_features ? swiglu_features : N, ldo, 16, &mo, swiglu_features ? 64 : 128)) return 1;
+        return gemm_tc_pair_launch(mw, mx, staged ? &mo : nullptr, &p, stream);
     }
     if (tensor_map_2d(X, T, K, ldx, bn, &mx)) return 1;
     switch (bn) {

@@ -183,4 +183,7 @@ __device__ __forceinline__ void tc_write_ssq(const TcParams& p, int n0, int t0, 
 }  // namespace
 
 // Two CTAs on two SMs per 256 x 256 tile (gemm_tc_pair.cu); taken for steps of many tokens.
-int gemm_tc_pair_launch(const CUtensorMap& mw, const CUtensorMap& mx, const void* params, cudaStream_t stream);
+// mo: map of the bf16 output for stores from shared memory (boxes of 16 tokens x 128 features, or x 64 after
+// SwiGLU), or null: results are then stored from registers.
+int gemm_tc_pair_launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap* mo, const void* params,
+                        cudaStream_t stream);

@@ -19,7 +19,9 @@ constexpr int PBN = 256;                    // tokens per tile
 constexpr int PHALF = PBN / 2;              // tokens a CTA loads
 constexpr int PSTAGES = 6;
 constexpr int PSTAGE_BYTES = A_BYTES + PHALF * BK * 2;         // per CTA
-constexpr int PSMEM = PSTAGES * PSTAGE_BYTES + 1024;
+constexpr int POUT_CHUNK = 16 * BM * 2;      // a staged piece of the result: 16 tokens x 128 features of bf16
+constexpr int POUT_RING = 4;                // pieces in flight to global memory
+constexpr int PSMEM = PSTAGES * PSTAGE_BYTES + POUT_RING * POUT_CHUNK + 1024;
 constexpr int PTMEM_COLS = 2 * PBN;         // two accumulators
 
 struct PairUnit {
@@ -39,10 +41,13 @@ __device__ __forceinline__ PairUnit pair_unit_of(int u, int feature_tiles, int t
     return w;
 }
 
+template <bool STAGED>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w,
-                                                                     const __grid_constant__ CUtensorMap map_x, TcParams p) {
+                                                                     const __grid_constant__ CUtensorMap map_x,
+                                                                     const __grid_constant__ CUtensorMap map_o, TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* out_ring = ring + PSTAGES * PSTAGE_BYTES;
     __shared__ uint64_t full_bar[PSTAGES], empty_bar[PSTAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base;
     __shared__ float rstd_s[PBN];
@@ -127,7 +132,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         gb_grid_wait();
-        int j = 0;
+        int j = 0, piece = 0;
         for (int u = pair; u < n_units; u += n_pairs, ++j) {
             const PairUnit w = pair_unit_of(u, feature_tiles, token_tiles);
             const int buf = j & 1;
@@ -144,16 +149,53 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
             const uint32_t taddr = tmem_d + (uint32_t(quarter * 32) << 16) + buf * PBN;
             float bias = 0.f;
             if (p.bias && n < p.N) bias = gb_load(p.bias, p.bias_dtype, n);
-            for (int c0 = 0; c0 < cols; c0 += 16) {
-                float v[16];
-                tmem_ld16(taddr + c0, v);
-                tc_finish_chunk<PBN>(p, n0, w.t0, n, row, lane, quarter, bias, waited, c0, cols, v, rstd_s, ssq_s);
+            if constexpr (STAGED) {
+                // bf16 results: 16 tokens at a time into a ring of shared-memory pieces [token][feature], each
+                // sent on its way by one TMA store (the scattered 2-byte stores from registers would take as
+                // long as the tile's multiplications)
+                for (int c0 = 0; c0 < cols; c0 += 16, ++piece) {
+                    float v[16];
+                    tmem_ld16(taddr + c0, v);
+                    if (p.row_ssq) {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) v[jj] *= rstd_s[min(c0 + jj, PBN - 1)];
+                    }
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out_ring + (piece % POUT_RING) * POUT_CHUNK);
+                    if (threadIdx.x == 64) tma_store_source_free<POUT_RING - 1>();      // the piece's last store has read it
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (!p.swiglu) {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) dst[jj * BM + row] = __float2bfloat16_rn(v[jj] + bias);
+                    } else {
+                        // even rows are gate features, odd rows the matching up features (see tc_finish_chunk)
+                        const bool odd = lane & 1;
+                        float other[8];
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) other[jj] = __shfl_xor_sync(0xffffffffu, odd ? v[jj] : v[8 + jj], 1);
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) {
+                            const float gte = odd ? other[jj] : v[jj], up = odd ? v[8 + jj] : other[jj];
+                            dst[((odd ? 8 : 0) + jj) * (BM / 2) + (row >> 1)] = __float2bfloat16_rn(gte / (1.f + expf(-gte)) * up);
+                        }
+                    }
+                    fence_proxy_async();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (threadIdx.x == 64 && waited)
+                        tma_store_2d(&map_o, p.swiglu ? (n0 >> 1) : n0, w.t0 + c0, dst);
+                }
+            } else {
+                for (int c0 = 0; c0 < cols; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(taddr + c0, v);
+                    tc_finish_chunk<PBN>(p, n0, w.t0, n, row, lane, quarter, bias, waited, c0, cols, v, rstd_s, ssq_s);
+                }
+                if (p.resid_x) tc_write_ssq<PBN>(p, n0, w.t0, row, 0, cols, ssq_s);
             }
-            if (p.resid_x) tc_write_ssq<PBN>(p, n0, w.t0, row, 0, cols, ssq_s);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(&acc_empty[buf], 0);      // the leader may overwrite this accumulator
         }
+        if (STAGED && threadIdx.x == 64) tma_store_done();
     }
     // nobody leaves while its partner may still read its shared memory or arrive on its barriers
     tc_fence_before();
@@ -163,11 +205,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
 
 }  // namespace
 
-int gemm_tc_pair_launch(const CUtensorMap& mw, const CUtensorMap& mx, const void* params, cudaStream_t stream) {
+int gemm_tc_pair_launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap* mo, const void* params,
+                        cudaStream_t stream) {
     const TcParams& p = *static_cast<const TcParams*>(params);
     static int state = 0;                          // 1: ready, -1: refused
     if (state == 0) {
-        state = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PSMEM) == cudaSuccess ? 1 : -1;
+        state = cudaFuncSetAttribute(gemm_tc_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PSMEM) == cudaSuccess &&
+                        cudaFuncSetAttribute(gemm_tc_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PSMEM) == cudaSuccess
+                    ? 1 : -1;
         if (state < 0) cudaGetLastError();
     }
     if (state < 0) return gb_fail("gb_gemm_tc: cannot get %d bytes of shared memory", PSMEM);
@@ -189,7 +234,10 @@ int gemm_tc_pair_launch(const CUtensorMap& mw, const CUtensorMap& mx, const void
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = gb_pdl_enabled() ? 2 : 1;
-    cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, p);
+    if (mo)
+        cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<true>, mw, mx, *mo, p);
+    else
+        cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<false>, mw, mx, mx, p);
     GB_LAUNCH_OK("gb_gemm_tc (pair)");
     return 0;
 }
