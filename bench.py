@@ -246,6 +246,10 @@ def main():
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": step_bytes},
     }
     if not args.no_points:
+        # the end-to-end figure right after the device-timed one (the same state of the device), then the rest
+        e_tok_s, h2d, d2h = measure_e2e(llm, cfg, args.batch, args.steps, warmup)
+        line["e2e"] = {"value": round(e_tok_s, 2), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+                       "d2h_bytes_per_step": int(d2h)}
         pms = measure_prefill(llm, cfg, args.layers)
         flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
         line["prefill"] = {"value": round(PREFILL_TOKENS * 1000.0 / pms, 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
@@ -256,9 +260,6 @@ def main():
             points[f"decode_b{b}"] = round(p_tok_s, 2)
             points[f"decode_b{b}_ms"] = round(p_ms, 4)
         line["points"] = points
-        e_tok_s, h2d, d2h = measure_e2e(llm, cfg, args.batch, args.steps, warmup)
-        line["e2e"] = {"value": round(e_tok_s, 2), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
-                       "d2h_bytes_per_step": int(d2h)}
     sampler.stop()
     print(json.dumps(line))
     return 0

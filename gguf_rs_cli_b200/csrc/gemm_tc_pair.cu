@@ -205,6 +205,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_pair_kernel(const __gri
 
 }  // namespace
 
+// How many pairs of CTAs of this kernel the device holds at once (0 if it cannot be asked).
+static int pair_slots() {
+    static int slots = -1;
+    if (slots < 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2);
+        cfg.blockDim = dim3(TC_THREADS);
+        cfg.dynamicSmemBytes = PSMEM;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<true>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+        slots = n;
+    }
+    return slots;
+}
+GB_API int gb_gemm_tc_pair_slots() { return pair_slots(); }
+
 int gemm_tc_pair_launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap* mo, const void* params,
                         cudaStream_t stream) {
     const TcParams& p = *static_cast<const TcParams*>(params);
