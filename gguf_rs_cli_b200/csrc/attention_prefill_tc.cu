@@ -216,9 +216,14 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
             if (!mbar_wait(&s_full[t], c & 1)) { if (lane == 0) atomicExch(p.status, 16); abort_flag = 1; ok = false; break; }
             tc_fence_after();
             const bool need_mask = key0 + AT_BN - 1 > pos_lo[t] || p.window > 0 || r >= rows[t];
+            // The block in two halves of 64 keys, each loaded from TMEM once: its maximum decides whether the
+            // reference is raised (rarely; then what the row has gathered so far is rescaled: O, the sums, and
+            // the first half's probabilities if they are written already), then its probabilities (two
+            // elements per instruction for the scaling and the sum; masked entries are -inf: 2^-inf is 0) go
+            // back as bf16 over the first half of the columns S came from: keys 0..63 into columns 0..31 once
+            // columns 0..63 are in registers, keys 64..127 into columns 32..63.
             float v[64];
-            // first pass: the row's maximum over the block
-            float mx = -INFINITY;
+            float add = 0.f;
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 tmem_ld64(s_addr + 64 * hh, v);
@@ -235,43 +240,44 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
                     m4[0] = fmaxf(m4[0], v[i]); m4[1] = fmaxf(m4[1], v[i + 1]);
                     m4[2] = fmaxf(m4[2], v[i + 2]); m4[3] = fmaxf(m4[3], v[i + 3]);
                 }
-                mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
-            }
-            // raise the reference when the maximum has run away from it (or there was none yet)
-            float factor = 1.f;
-            if (mx > -INFINITY && (m_ref == -INFINITY || mx > m_ref + raise)) {
-                factor = m_ref == -INFINITY ? 0.f : exp2f((m_ref - mx) * p.scale_log2);
-                m_ref = mx;
-            }
-            const float ms = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
-            if (c > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
-                // O must hold every block before this one before its rows are rescaled
-                if (!mbar_wait(&pv_done[t], (c - 1) & 1)) { if (lane == 0) atomicExch(p.status, 17); abort_flag = 1; ok = false; break; }
-                tc_fence_after();
+                const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                // raise the reference when the maximum has run away from it (or there was none yet)
+                float factor = 1.f;
+                if (mx > -INFINITY && (m_ref == -INFINITY || mx > m_ref + raise)) {
+                    factor = m_ref == -INFINITY ? 0.f : exp2f((m_ref - mx) * p.scale_log2);
+                    m_ref = mx;
+                }
+                if (__any_sync(0xffffffffu, factor != 1.f)) {
+                    if (c > 0) {
+                        // O must hold every block before this one before its rows are rescaled
+                        if (!mbar_wait(&pv_done[t], (c - 1) & 1)) { if (lane == 0) atomicExch(p.status, 17); abort_flag = 1; ok = false; }
+                        tc_fence_after();
 #pragma unroll 1
-                for (int cc = 0; cc < 4; ++cc) {
-                    float o[32];
-                    tmem_ld32(o_addr + 32 * cc, o);
+                        for (int cc = 0; cc < 4; ++cc) {
+                            float o[32];
+                            tmem_ld32(o_addr + 32 * cc, o);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] *= factor;
-                    tmem_st32(o_addr + 32 * cc, o);
-                }
-                tc_fence_before();
-            }
-            // second pass: probabilities (two elements per instruction for the scaling and the sum; masked
-            // entries are -inf: 2^-inf is 0), written as bf16 over the first half of the columns S came from:
-            // keys 0..63 into columns 0..31 once columns 0..63 are in registers, keys 64..127 into columns 32..63
-            float add = 0.f;
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                tmem_ld64(s_addr + 64 * hh, v);
-                if (need_mask) {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const int ka = key0 + 64 * hh + i;
-                        if (ka > pq || ka < lo) v[i] = -INFINITY;
+                            for (int i = 0; i < 32; ++i) o[i] *= factor;
+                            tmem_st32(o_addr + 32 * cc, o);
+                        }
                     }
+                    if (hh == 1) {
+                        // the first half's probabilities, already in place, relative to the new reference
+                        uint32_t w0[32];
+                        tmem_ld32_words(s_addr, w0);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            __nv_bfloat162 pk = *reinterpret_cast<__nv_bfloat162*>(&w0[i]);
+                            pk = __floats2bfloat162_rn(__low2float(pk) * factor, __high2float(pk) * factor);
+                            w0[i] = *reinterpret_cast<uint32_t*>(&pk);
+                        }
+                        tmem_st32_words(s_addr, w0);
+                    }
+                    tc_fence_before();
+                    l *= factor;
+                    add *= factor;
                 }
+                const float ms = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
                 const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ms2 = make_float2(-ms, -ms);
                 float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
                 uint32_t w[32];
@@ -288,7 +294,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
                 add += (a01.x + a01.y) + (a23.x + a23.y);
                 tmem_st32_words(s_addr + 32 * hh, w);
             }
-            l = l * factor + add;
+            if (!ok) break;
+            l += add;
             tc_fence_before();
             if (key0 + AT_BN - 1 > valid_end) {
                 // key row r of this block holds nothing meaningful if it lies beyond the sequence's end (never

@@ -512,6 +512,28 @@ def test_attention_prefill_far_key_and_window(window, hd, tc):
     assert rel_err(want_w, want) > 0.05
 
 
+@pytest.mark.parametrize("key", [3, 70, 200, 449, 650])
+@pytest.mark.parametrize("tc", [False, True])
+def test_attention_prefill_score_that_stands_out_anywhere_in_a_block(key, tc):
+    """One key whose score with the last query towers over the rest, placed in the first or second half of the
+    first or a later block of 128 keys: the running maximum then jumps in the middle of a block, after sums,
+    outputs and probabilities have been gathered relative to the old one."""
+    k = K()
+    nh, nkv, hd = 8, 2, 128
+    lens, qlens = [700, 300], [700, 150]
+    q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, qlens, BF, 9, boost=(0, key, 5))
+    tiles, cu, starts, ql = prefill_meta(lens, qlens)
+    out = torch.empty(q.shape[0], nh * hd, dtype=BF, device=DEV)
+    k.attention_prefill(q, out, nh, nkv, hd, tiles, cu, starts, ql, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd), tc=tc)
+    torch.cuda.synchronize()
+    k.check_tc_status()
+    assert rel_err(out, want) < 1e-2
+    # the last query's head 5 is (nearly) that key's value
+    v_key = read_cache(vc, table[0], 700)[key, 5 // (nh // nkv)]
+    got = out[699, 5 * hd:6 * hd].float().cpu()
+    assert float((got - v_key).abs().max()) < 0.05 * float(v_key.abs().max())
+
+
 @pytest.mark.parametrize("tc", [False, True])
 def test_attention_prefill_ignores_unwritten_cache_rows(tc):
     """Rows of a page beyond the sequence's end hold NaN here; they must not reach the output."""
