@@ -226,7 +226,6 @@ static int pair_slots() {
     }
     return slots;
 }
-GB_API int gb_gemm_tc_pair_slots() { return pair_slots(); }
 
 int gemm_tc_pair_launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap* mo, const void* params,
                         cudaStream_t stream) {
@@ -240,7 +239,7 @@ int gemm_tc_pair_launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUte
     }
     if (state < 0) return gb_fail("gb_gemm_tc: cannot get %d bytes of shared memory", PSMEM);
     long long units = (long long)((p.N + 2 * BM - 1) / (2 * BM)) * ((p.T + PBN - 1) / PBN);
-    long long slots = p.sms / 2;                                       // pairs that can be resident at once
+    long long slots = pair_slots() > 0 ? pair_slots() : p.sms / 2;     // pairs that can be resident at once
     long long rounds = (units + slots - 1) / slots;
     long long pairs = (units + rounds - 1) / rounds;
     cudaLaunchConfig_t cfg = {};

@@ -137,7 +137,6 @@ _SIGNATURES = {
     "gb_gemm_tc_tile": [_I],
     "gb_gemm_tc_set_splits": [_I],
     "gb_gemm_tc_set_pair": [_I],
-    "gb_gemm_tc_pair_slots": [],
     "gb_gemm_tc_set_tile": [_I],
     "gb_gemm_tc_splits": [_I, _I, _I, _I],
     "gb_gemm_tc_scratch_floats": [_I, _I, _I, _I],
