@@ -86,8 +86,14 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
     __shared__ float m_s[DM_WARPS][DM_ROWS], l_s[DM_WARPS][DM_ROWS];
     __shared__ int last_flag;
 
+    // What the kernel in front writes is q (and k_new, v_new).  The index arrays were in place before the step
+    // began, and when this kernel writes the token's own key and value itself (rotate with k_new) every row of
+    // the cache it reads was written in an earlier step: then the first pages are asked for before waiting for
+    // that kernel.  Otherwise the rotation kernel in front wrote the token's row, or (a cache shared with another
+    // run) a kernel further back did: wait first.
     gb_grid_launch_dependents();
-    gb_grid_wait();
+    const bool early = p.rotate && p.k_new != nullptr;
+    if (!early) gb_grid_wait();
     const int t = blockIdx.x;
     const int G = p.nh / p.nkv;
     const int gtiles = (G + DM_ROWS - 1) / DM_ROWS;
@@ -99,6 +105,7 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     if (b < 0) {
+        if (early) gb_grid_wait();                         // `out` may still be read by a kernel further back
         if (split == 0)
             for (int i = tid; i < heads * HD; i += DM_THREADS)
                 p.out[size_t(t) * p.ldo + size_t(h0) * HD + i] = __float2bfloat16_rn(0.f);
@@ -139,6 +146,7 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
         if (pg_begin + s < pg_end) load_page(pg_begin + s, s);
         dm_commit();
     }
+    if (early) gb_grid_wait();
     float sn = 0.f, cs = 1.f;
     int d0 = 0, d1 = 0;
     float own0 = 0.f, own1 = 0.f;                     // this thread's two elements of the token's own key or value
@@ -364,6 +372,254 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
     if (tid == 0) p.counters[t * gridDim.y + blockIdx.y] = 0;
 }
 
+// The same attention for steps with so few (token, KV head) pairs that the device is mostly idle and a CTA's
+// time is the latency of its pages one after the other: twelve warps, each taking half pages of 32 keys (warp w:
+// half pages w, w + 12, ...) into a slot of shared memory of its own, so that six pages are on their way at
+// once, twelve warps work on them and nobody waits for a block-wide barrier per page.  One CTA per SM (twelve
+// slots of 32 keys and values); no splits.
+constexpr int PW_WARPS = 12;
+constexpr int PW_THREADS = PW_WARPS * 32;
+constexpr int PW_KEYS = 32;                 // keys per slot
+
+template <int HD>
+__global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmParams p) {
+    constexpr int CH = HD / 8, KS = HD / 16, OT = HD / 8, HALF = HD / 2;
+    constexpr int PAGE_ELEMS = GB_PAGE * HD, SLOT_ELEMS = PW_KEYS * HD;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                  // [16][HD]
+    __nv_bfloat16* ks = qs + DM_ROWS * HD;                                            // [warps][32][HD]
+    __nv_bfloat16* vs = ks + PW_WARPS * SLOT_ELEMS;                                   // [warps][32][HD]
+    float* merge_o = reinterpret_cast<float*>(ks);                                    // reused after the loop: [warps][16][HD]
+    __shared__ float m_s[PW_WARPS][DM_ROWS], l_s[PW_WARPS][DM_ROWS];
+    __shared__ float cs_s[HALF], sn_s[HALF];
+
+    gb_grid_launch_dependents();
+    const bool early = p.rotate && p.k_new != nullptr;       // see the other kernel: pages before the wait
+    if (!early) gb_grid_wait();
+    const int t = blockIdx.x;
+    const int G = p.nh / p.nkv;
+    const int gtiles = (G + DM_ROWS - 1) / DM_ROWS;
+    const int g = blockIdx.y / gtiles;
+    const int h0 = g * G + (blockIdx.y % gtiles) * DM_ROWS;
+    const int heads = min(DM_ROWS, g * G + G - h0);
+    const int b = p.seq_of[t];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (b < 0) {
+        if (early) gb_grid_wait();
+        for (int i = tid; i < heads * HD; i += PW_THREADS)
+            p.out[size_t(t) * p.ldo + size_t(h0) * HD + i] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int pos = p.pos[t];
+    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int pg_begin = lo >> GB_PAGE_SHIFT, pg_end = (pos >> GB_PAGE_SHIFT) + 1;
+    const int* trow = p.table + size_t(b) * p.table_width;
+    const bool own_kv = p.rotate && p.k_new != nullptr;
+    __nv_bfloat16* kt = ks + warp * SLOT_ELEMS;
+    __nv_bfloat16* vt = vs + warp * SLOT_ELEMS;
+    const int u_end = 2 * (pg_end - pg_begin);               // half pages, counted from the first page
+
+    auto load_half = [&](int u) {
+        const int pg = pg_begin + (u >> 1), row0 = (u & 1) * PW_KEYS;
+        const int phys = trow[pg % p.ring_pages];
+        const size_t off = (size_t(phys) * p.nkv + g) * size_t(PAGE_ELEMS) + size_t(row0) * HD;
+        for (int i = lane; i < PW_KEYS * CH; i += 32) {
+            int r = i / CH, c = i - r * CH;
+            const int key = pg * GB_PAGE + row0 + r;       // rows beyond the sequence are read as zeros, and so
+            bool ok = key < pos || (key == pos && !own_kv);   // is the token's own row when this kernel makes it
+            dm_cp_async16(kt + dm_swz<HD>(r, c), p.kc + off + size_t(r) * HD + c * 8, ok);
+            dm_cp_async16(vt + dm_swz<HD>(r, c), p.vc + off + size_t(r) * HD + c * 8, ok);
+        }
+        dm_commit();
+    };
+    // every warp's first half page is asked for at once
+    int u = warp;
+    if (u < u_end) load_half(u);
+    if (early) gb_grid_wait();
+
+    // the rotation's cosines and sines, one pair index per thread, and the queries
+    if (p.rotate) {
+        const int half = p.inv_freq ? p.rotary_dim / 2 : 0;
+        if (tid < HALF) {
+            float sn = 0.f, cs = 1.f;
+            if (tid < half) sincosf(float(pos) * p.inv_freq[tid], &sn, &cs);
+            cs_s[tid] = cs;
+            sn_s[tid] = sn;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < DM_ROWS * HALF; idx += PW_THREADS) {
+            const int r = idx / HALF, pi = idx - r * HALF;
+            const int d0 = pi < half ? (p.pairing ? 2 * pi : pi) : 2 * pi;
+            const int d1 = pi < half ? (p.pairing ? 2 * pi + 1 : pi + half) : 2 * pi + 1;
+            float x0 = 0.f, x1 = 0.f;
+            if (r < heads) {
+                const __nv_bfloat16* src = p.q + size_t(t) * p.ldq + size_t(h0 + r) * HD;
+                x0 = __bfloat162float(src[d0]);
+                x1 = __bfloat162float(src[d1]);
+            }
+            float y0, y1;
+            gb_rotate(x0, x1, cs_s[pi], sn_s[pi], y0, y1);
+            qs[dm_swz<HD>(r, d0 >> 3) + (d0 & 7)] = __float2bfloat16_rn(y0);
+            qs[dm_swz<HD>(r, d1 >> 3) + (d1 & 7)] = __float2bfloat16_rn(y1);
+        }
+    } else {
+        for (int i = tid; i < DM_ROWS * CH; i += PW_THREADS) {
+            int r = i / CH, c = i - r * CH;
+            dm_cp_async16(qs + dm_swz<HD>(r, c), p.q + size_t(t) * p.ldq + size_t(h0 + min(r, heads - 1)) * HD + c * 8, r < heads);
+        }
+        dm_commit();
+        dm_wait<0>();
+    }
+    __syncthreads();                                         // the queries are in place
+
+    float o[OT][4];
+#pragma unroll
+    for (int i = 0; i < OT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    unsigned qf[KS][4];
+#pragma unroll
+    for (int k = 0; k < KS; ++k)
+        dm_ldmatrix_x4(qf[k][0], qf[k][1], qf[k][2], qf[k][3], qs + dm_swz<HD>(lane & 15, 2 * k + (lane >> 4)));
+
+    for (; u < u_end; u += PW_WARPS) {
+        const int pg = pg_begin + (u >> 1), row0 = (u & 1) * PW_KEYS;
+        dm_wait<0>();
+        __syncwarp();
+        if (own_kv && pg * GB_PAGE + row0 <= pos && pos < pg * GB_PAGE + row0 + PW_KEYS) {
+            // the token's own key (rotated) and value: into the half page in shared memory, and by the first
+            // head tile of the KV head into the cache
+            const int r = pos & (PW_KEYS - 1);
+            const int half = p.inv_freq ? p.rotary_dim / 2 : 0;
+            const bool writes = (blockIdx.y % gtiles) == 0;
+            const size_t src = size_t(t) * p.ldq + size_t(g) * HD;
+            const size_t dst = (size_t(trow[pg % p.ring_pages]) * p.nkv + g) * size_t(PAGE_ELEMS) + size_t(row0 + r) * HD;
+            for (int pi = lane; pi < HALF; pi += 32) {
+                const int d0 = pi < half ? (p.pairing ? 2 * pi : pi) : 2 * pi;
+                const int d1 = pi < half ? (p.pairing ? 2 * pi + 1 : pi + half) : 2 * pi + 1;
+                float r0, r1;
+                gb_rotate(__bfloat162float(p.k_new[src + d0]), __bfloat162float(p.k_new[src + d1]), cs_s[pi], sn_s[pi], r0, r1);
+                const __nv_bfloat16 y0 = __float2bfloat16_rn(r0), y1 = __float2bfloat16_rn(r1);
+                kt[dm_swz<HD>(r, d0 >> 3) + (d0 & 7)] = y0;
+                kt[dm_swz<HD>(r, d1 >> 3) + (d1 & 7)] = y1;
+                const int e = 2 * pi;
+                const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(p.v_new + src + e);
+                *reinterpret_cast<__nv_bfloat162*>(vt + dm_swz<HD>(r, e >> 3) + (e & 7)) = x;
+                if (writes) {
+                    p.kc_w[dst + d0] = y0;
+                    p.kc_w[dst + d1] = y1;
+                    *reinterpret_cast<__nv_bfloat162*>(p.vc_w + dst + e) = x;
+                }
+            }
+            __syncwarp();
+        }
+        // the slot's 32 keys in two groups of 16, each as the other kernel treats a warp's 16 keys of a page
+#pragma unroll 1
+        for (int grp = 0; grp < PW_KEYS / 16; ++grp) {
+            const int key_base = grp * 16;
+            float s[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+            for (int k = 0; k < KS; ++k) {
+                unsigned b0, b1, b2, b3;
+                dm_ldmatrix_x4(b0, b1, b2, b3, kt + dm_swz<HD>(key_base + (lane & 7) + ((lane >> 4) << 3), 2 * k + ((lane >> 3) & 1)));
+                dm_mma(s[0], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b0, b1);
+                dm_mma(s[1], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b2, b3);
+            }
+            const int key0 = pg * GB_PAGE + row0 + key_base + 2 * (lane & 3);
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                int ka = key0 + 8 * j, kb = ka + 1;
+                if (ka > pos || ka < lo) s[j][0] = s[j][2] = -INFINITY;
+                if (kb > pos || kb < lo) s[j][1] = s[j][3] = -INFINITY;
+                mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            const float a0 = mn0 == -INFINITY ? 1.f : exp2f((m0 - mn0) * p.scale_log2);
+            const float a1 = mn1 == -INFINITY ? 1.f : exp2f((m1 - mn1) * p.scale_log2);
+            const float ms0 = mn0 == -INFINITY ? 0.f : mn0 * p.scale_log2, ms1 = mn1 == -INFINITY ? 0.f : mn1 * p.scale_log2;
+            float p00 = exp2f(s[0][0] * p.scale_log2 - ms0), p01 = exp2f(s[0][1] * p.scale_log2 - ms0);
+            float p02 = exp2f(s[0][2] * p.scale_log2 - ms1), p03 = exp2f(s[0][3] * p.scale_log2 - ms1);
+            float p10 = exp2f(s[1][0] * p.scale_log2 - ms0), p11 = exp2f(s[1][1] * p.scale_log2 - ms0);
+            float p12 = exp2f(s[1][2] * p.scale_log2 - ms1), p13 = exp2f(s[1][3] * p.scale_log2 - ms1);
+            l0 = l0 * a0 + (p00 + p01 + p10 + p11);
+            l1 = l1 * a1 + (p02 + p03 + p12 + p13);
+            m0 = mn0;
+            m1 = mn1;
+            const unsigned pa0 = dm_pack(p00, p01), pa1 = dm_pack(p02, p03), pa2 = dm_pack(p10, p11), pa3 = dm_pack(p12, p13);
+#pragma unroll
+            for (int i2 = 0; i2 < OT / 2; ++i2) {
+                unsigned b0, b1, b2, b3;
+                dm_ldmatrix_x4_trans(b0, b1, b2, b3, vt + dm_swz<HD>(key_base + (lane & 15), 2 * i2 + (lane >> 4)));
+                o[2 * i2][0] *= a0; o[2 * i2][1] *= a0; o[2 * i2][2] *= a1; o[2 * i2][3] *= a1;
+                o[2 * i2 + 1][0] *= a0; o[2 * i2 + 1][1] *= a0; o[2 * i2 + 1][2] *= a1; o[2 * i2 + 1][3] *= a1;
+                dm_mma(o[2 * i2], pa0, pa1, pa2, pa3, b0, b1);
+                dm_mma(o[2 * i2 + 1], pa0, pa1, pa2, pa3, b2, b3);
+            }
+        }
+        __syncwarp();                                        // the slot may be loaded again
+        if (u + PW_WARPS < u_end) load_half(u + PW_WARPS);
+    }
+    dm_wait<0>();
+    __syncthreads();
+
+    // ---- merge the warps (each saw some of the pages) in warp order
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    {
+        const int ra = lane >> 2, rb = ra + 8, col = 2 * (lane & 3);
+        float* mo = merge_o + size_t(warp) * DM_ROWS * HD;
+#pragma unroll
+        for (int i = 0; i < OT; ++i) {
+            mo[ra * HD + 8 * i + col] = o[i][0];
+            mo[ra * HD + 8 * i + col + 1] = o[i][1];
+            mo[rb * HD + 8 * i + col] = o[i][2];
+            mo[rb * HD + 8 * i + col + 1] = o[i][3];
+        }
+        if ((lane & 3) == 0) {
+            m_s[warp][ra] = m0; l_s[warp][ra] = l0;
+            m_s[warp][rb] = m1; l_s[warp][rb] = l1;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < heads * HD; i += PW_THREADS) {
+        const int r = i / HD, d = i - r * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < PW_WARPS; ++w) M = fmaxf(M, m_s[w][r]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < PW_WARPS; ++w) {
+            float wgt = m_s[w][r] == -INFINITY ? 0.f : exp2f((m_s[w][r] - M) * p.scale_log2);
+            L += l_s[w][r] * wgt;
+            acc += merge_o[(size_t(w) * DM_ROWS + r) * HD + d] * wgt;
+        }
+        p.out[size_t(t) * p.ldo + size_t(h0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
+    }
+}
+
+template <int HD> int launch_pw(const DmParams& p, dim3 grid, cudaStream_t stream) {
+    constexpr int SMEM = (DM_ROWS + 2 * PW_WARPS * PW_KEYS) * HD * 2;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_decode_pages_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+            return gb_fail("gb_attention_decode_mma: cannot get %d bytes of shared memory", SMEM);
+        configured = true;
+    }
+    gb_launch(attention_decode_pages_kernel<HD>, grid, dim3(PW_THREADS), SMEM, stream, p);
+    GB_LAUNCH_OK("gb_attention_decode_mma");
+    return 0;
+}
+
 template <int HD> int launch_dm(const DmParams& p, dim3 grid, cudaStream_t stream) {
     constexpr int SMEM = (DM_ROWS + 2 * DM_STAGES * GB_PAGE) * HD * 2;
     static bool configured = false;
@@ -378,6 +634,9 @@ template <int HD> int launch_dm(const DmParams& p, dim3 grid, cudaStream_t strea
 }
 
 }  // namespace
+
+static int g_pages_kernel = 1;        // 0: never the kernel whose warps take whole pages (tuning aid)
+GB_API int gb_attention_decode_set_pages_kernel(int on) { g_pages_kernel = on; return 0; }
 
 GB_API int gb_attention_decode_mma_supported(int hd, int cache_dtype, int q_dtype) {
     return cache_dtype == GB_BF16 && q_dtype == GB_BF16 && (hd == 64 || hd == 128);
@@ -412,6 +671,11 @@ static int decode_mma(const void* q, long long ldq, void* out, long long ldo, in
     p.kc_w = (__nv_bfloat16*)kcache; p.vc_w = (__nv_bfloat16*)vcache; p.inv_freq = inv_freq;
     p.rotary_dim = rotary_dim; p.pairing = pairing;
     dim3 grid(T, nkv * gtiles, splits);
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (splits == 1 && g_pages_kernel && (long long)T * nkv * gtiles <= sms)       // few CTAs: a CTA's latency is the step's
+        return hd == 64 ? launch_pw<64>(p, grid, stream) : launch_pw<128>(p, grid, stream);
     return hd == 64 ? launch_dm<64>(p, grid, stream) : launch_dm<128>(p, grid, stream);
 }
 
