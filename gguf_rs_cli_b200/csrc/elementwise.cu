@@ -265,6 +265,64 @@ __global__ void rope_kv_write_kernel(void* __restrict__ q, const void* __restric
     }
 }
 
+// The same for the common case (bf16 rows and cache, the whole head rotated, pairs (i, i + hd/2), 16-byte
+// aligned rows): 16 bytes per load and store.  A thread owns 8 consecutive pair indices (its 8 angles are
+// computed once) and walks the q and k heads; then the threads copy v.
+constexpr int ROPE_VEC_THREADS = 128;
+
+__global__ void __launch_bounds__(ROPE_VEC_THREADS) rope_kv_write_vec_kernel(
+        __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v, long long ld,
+        int nh, int nkv, int hd, const float* __restrict__ inv_freq, const int* __restrict__ seq_of,
+        const int* __restrict__ pos, const int* __restrict__ table, int table_width, int ring_pages,
+        __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache) {
+    gb_grid_launch_dependents();
+    gb_grid_wait();
+    const int t = blockIdx.x;
+    const int b = seq_of[t];
+    if (b < 0) return;
+    const int p = pos[t];
+    const int half = hd / 2, chunks = hd / 16;             // chunks of 8 pairs per head
+    const size_t row = size_t(t) * size_t(ld);
+    const int pc = threadIdx.x % chunks, lanes = ROPE_VEC_THREADS / chunks;
+    const int* trow = k ? table + size_t(b) * table_width : nullptr;
+    if (threadIdx.x < lanes * chunks) {
+        float cs[8], sn[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sincosf(float(p) * inv_freq[8 * pc + i], &sn[i], &cs[i]);
+        const int total = k ? nh + nkv : nh;
+        for (int head = threadIdx.x / chunks; head < total; head += lanes) {
+            const bool is_q = head < nh;
+            const __nv_bfloat16* src = is_q ? q + row + size_t(head) * hd : k + row + size_t(head - nh) * hd;
+            __nv_bfloat16* dst = is_q ? q + row + size_t(head) * hd
+                                      : kcache + gb_kv_offset(trow, ring_pages, p, head - nh, nkv, hd);
+            const uint4 lo4 = *reinterpret_cast<const uint4*>(src + 8 * pc);
+            const uint4 hi4 = *reinterpret_cast<const uint4*>(src + half + 8 * pc);
+            const __nv_bfloat16* lo = reinterpret_cast<const __nv_bfloat16*>(&lo4);
+            const __nv_bfloat16* hi = reinterpret_cast<const __nv_bfloat16*>(&hi4);
+            uint4 olo4, ohi4;
+            __nv_bfloat16* olo = reinterpret_cast<__nv_bfloat16*>(&olo4);
+            __nv_bfloat16* ohi = reinterpret_cast<__nv_bfloat16*>(&ohi4);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float y0, y1;
+                gb_rotate(__bfloat162float(lo[i]), __bfloat162float(hi[i]), cs[i], sn[i], y0, y1);
+                olo[i] = __float2bfloat16_rn(y0);
+                ohi[i] = __float2bfloat16_rn(y1);
+            }
+            *reinterpret_cast<uint4*>(dst + 8 * pc) = olo4;
+            *reinterpret_cast<uint4*>(dst + half + 8 * pc) = ohi4;
+        }
+    }
+    if (k) {
+        const int per_head = hd / 8;
+        for (int idx = threadIdx.x; idx < nkv * per_head; idx += ROPE_VEC_THREADS) {
+            const int g = idx / per_head, c = idx - g * per_head;
+            *reinterpret_cast<uint4*>(vcache + gb_kv_offset(trow, ring_pages, p, g, nkv, hd) + 8 * c) =
+                *reinterpret_cast<const uint4*>(v + row + size_t(g) * hd + 8 * c);
+        }
+    }
+}
+
 // q, k, v: first elements of the q, k and v parts of token 0's row; rows are `ld` elements
 // apart.  k and v may be null (a mixer that reads another run's cache writes none);
 // inv_freq may be null (no rotation).
@@ -280,6 +338,16 @@ GB_API int gb_rope_kv_write(void* q, const void* k, const void* v, int dtype, lo
     GB_REQUIRE(!k || (table && kcache && vcache && ring_pages > 0 && table_width >= 1), "gb_rope_kv_write: cache missing");
     GB_REQUIRE(nh + 2 * nkv <= 65535, "gb_rope_kv_write: too many heads");
     if (T == 0) return 0;
+    auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+    if (dtype == GB_BF16 && (!k || cache_dtype == GB_BF16) && inv_freq && rotary_dim == hd && pairing == 0 && hd % 16 == 0 &&
+        hd / 16 <= ROPE_VEC_THREADS && ld % 8 == 0 && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(kcache) &&
+        aligned16(vcache) && T >= 64) {
+        gb_launch(rope_kv_write_vec_kernel, dim3(T), dim3(ROPE_VEC_THREADS), 0, stream, (__nv_bfloat16*)q,
+                  (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, ld, nh, nkv, hd, inv_freq, seq_of, pos, table, table_width,
+                  ring_pages, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache);
+        GB_LAUNCH_OK("gb_rope_kv_write");
+        return 0;
+    }
     int threads = ((hd / 2 + 31) / 32) * 32;
     int total = k ? nh + 2 * nkv : nh;
     int heads_per_block = T >= 512 ? 8 : 1;
