@@ -1,6 +1,8 @@
 """Each part of a layer alone against the plain implementation, and the generality of
 the composition: a toy mixer with state of its own (defined here, registered from
-here), windowed and cache-sharing layers, a layer that runs twice."""
+here), windowed and cache-sharing layers, a layer that runs twice; a toy feed-forward
+that routes tokens to experts and a position encoding of its own in a second toy
+architecture."""
 import math
 from dataclasses import dataclass
 
@@ -300,3 +302,174 @@ def test_schedule_errors_are_found_when_the_model_is_built():
     bad = ModelSpec(**{**spec.__dict__, "schedule": [Run(0), Run(1), Run(2), Run(3, cache_of=0)]})  # window != all keys
     with pytest.raises(ValueError, match="does not match"):
         Decoder(bad, torch.float32, "meta")
+
+
+# ------------------------------- a routed feed-forward and another position encoding
+def register_more_toys():
+    """Two more kinds registered from here: a feed-forward that routes every token to one of a few small experts
+    (router logits in 32-bit, top-1, the winner's gated MLP scaled by its softmax weight), and a position
+    encoding of its own (interleaved pairs over half of each head, frequencies that fall off linearly).  An
+    architecture uses them in alternate layers beside the library's own parts."""
+    from gguf_rs_cli_b200.config import register_architecture
+    from gguf_rs_cli_b200.config.llama import LlamaConfig, build_llama_spec
+    from gguf_rs_cli_b200.config.specs import LayerSpec, ModelSpec, PartSpec, Run
+    from gguf_rs_cli_b200.parts import FEED_FORWARDS, Part, register_feed_forward, register_position
+    from gguf_rs_cli_b200.weights import TensorRequest
+    if "top1_experts" in FEED_FORWARDS.kinds():
+        return
+
+    @register_feed_forward("top1_experts")
+    class Top1Experts(Part):
+        def tensor_requests(self):
+            E, F, n, t = self.p["hidden_size"], self.p["expert_size"], self.p["experts"], self.spec.tensors
+            return [TensorRequest(t["router"], (n, E)), TensorRequest(t["gate"], (n, F, E)), TensorRequest(t["up"], (n, F, E)),
+                    TensorRequest(t["down"], (n, E, F))]
+
+        def load(self, store):
+            self.router, self.gate, self.up, self.down = (store.get(r).float() for r in self.tensor_requests())
+
+        def forward(self, h, ctx):
+            x = h.float()
+            weight = torch.softmax(x @ self.router.t(), dim=-1)                 # [T, experts], 32-bit
+            best = weight.argmax(-1)
+            out = torch.zeros_like(x)
+            for e in range(self.p["experts"]):
+                rows = (best == e).nonzero().flatten()
+                if rows.numel():
+                    xe = x[rows]
+                    a = torch.nn.functional.silu(xe @ self.gate[e].t()) * (xe @ self.up[e].t())
+                    out[rows] = (a @ self.down[e].t()) * weight[rows, e:e + 1]
+            return out.to(ctx.dtype)
+
+    @register_position("linear_interleaved")
+    class LinearInterleaved(Part):
+        def __init__(self, spec, dtype, device):
+            super().__init__(spec, dtype, device)
+            self.rotary_dim = self.p["head_dim"] // 2
+            self.pairing = 1
+            n = self.rotary_dim // 2
+            self.inv_freq = torch.tensor([self.p["top"] * (1.0 - i / n) for i in range(n)], dtype=torch.float32, device=device)
+
+    @dataclass(frozen=True)
+    class Toy2Config:
+        llama: LlamaConfig
+        experts: int
+        expert_size: int
+        top: float
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(LlamaConfig.from_dict(raw), int(raw["toy_experts"]), int(raw["toy_expert_size"]), float(raw["toy_top_frequency"]))
+
+    def build_toy2_spec(cfg: Toy2Config) -> ModelSpec:
+        """Odd layers: routed experts instead of the dense feed-forward.  Even layers: the new position encoding."""
+        base = build_llama_spec(cfg.llama)
+        E, hd = cfg.llama.hidden_size, cfg.llama.head_dim
+        layers = []
+        for i, ls in enumerate(base.layers):
+            ff, position = ls.feed_forward, ls.position
+            if i % 2 == 1:
+                p = f"model.layers.{i}.experts."
+                ff = PartSpec("top1_experts", {"hidden_size": E, "experts": cfg.experts, "expert_size": cfg.expert_size},
+                              {"router": p + "router.weight", "gate": p + "gate.weight", "up": p + "up.weight", "down": p + "down.weight"})
+            else:
+                position = PartSpec("linear_interleaved", {"head_dim": hd, "top": cfg.top}, {})
+            layers.append(LayerSpec(ls.block, ls.mixer, ff, ls.norms, position))
+        return ModelSpec(**{**base.__dict__, "architecture": "Toy2ForCausalLM", "layers": layers})
+
+    register_architecture("Toy2ForCausalLM", Toy2Config, build_toy2_spec)
+
+
+TOY2 = {**config("B"), "architectures": ["Toy2ForCausalLM"], "model_type": "toy2", "num_hidden_layers": 4, "toy_experts": 3,
+        "toy_expert_size": 40, "toy_top_frequency": 0.7}
+
+
+def toy2_weights(seed=0):
+    cfg = {**TOY2, "architectures": ["LlamaForCausalLM"]}
+    w = P.random_weights(cfg, seed, std=0.05, norm_noise=0.1)
+    E, n, F = cfg["hidden_size"], TOY2["toy_experts"], TOY2["toy_expert_size"]
+    g = torch.Generator().manual_seed(seed + 7)
+    for i in (1, 3):
+        for name in ("gate_proj", "up_proj", "down_proj"):
+            del w[f"model.layers.{i}.mlp.{name}.weight"]
+        p = f"model.layers.{i}.experts."
+        w[p + "router.weight"] = torch.randn(n, E, generator=g) * 0.5
+        w[p + "gate.weight"] = torch.randn(n, F, E, generator=g) * 0.05
+        w[p + "up.weight"] = torch.randn(n, F, E, generator=g) * 0.05
+        w[p + "down.weight"] = torch.randn(n, E, F, generator=g) * 0.05
+    return {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+
+
+def toy2_plain_forward(w, tokens):
+    cfg = TOY2
+    nh, nkv, hd, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    T = len(tokens)
+    pos = torch.arange(T)
+    x = P.embedding(w["model.embed_tokens.weight"], tokens)
+
+    def rotate(t, layer):
+        if layer % 2 == 1:
+            return P.rope(t, pos, P.inv_freq_table(cfg))
+        rd = hd // 2
+        f = torch.tensor([cfg["toy_top_frequency"] * (1.0 - i / (rd // 2)) for i in range(rd // 2)])
+        ang = pos[:, None].float() * f[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        out = t.clone()
+        a, b = t[..., 0:rd:2], t[..., 1:rd:2]                       # pairs (2i, 2i+1) of the first half of the head
+        out[..., 0:rd:2], out[..., 1:rd:2] = a * c - b * s, a * s + b * c
+        return out
+
+    for l in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{l}."
+        xn = P.rmsnorm(x, w[p + "input_layernorm.weight"], eps)
+        proj = lambda n: P.linear(xn, w[p + f"self_attn.{n}_proj.weight"], w.get(p + f"self_attn.{n}_proj.bias"))
+        q = rotate(proj("q").reshape(T, nh, hd), l)
+        k = rotate(proj("k").reshape(T, nkv, hd), l)
+        v = proj("v").reshape(T, nkv, hd)
+        x = x + P.linear(P.attention(q, k, v), w[p + "self_attn.o_proj.weight"])
+        xn = P.rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps)
+        if l % 2 == 1:
+            e = p + "experts."
+            weight = P.softmax(P.linear(xn, w[e + "router.weight"]))
+            best = weight.argmax(-1)
+            term = torch.zeros_like(x)
+            for t in range(T):
+                i = int(best[t])
+                term[t] = P.feed_forward(xn[t:t + 1], w[e + "gate.weight"][i], w[e + "up.weight"][i], w[e + "down.weight"][i])[0] * weight[t, i]
+            x = x + term
+        else:
+            x = x + P.feed_forward(xn, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    x = P.rmsnorm(x, w["model.norm.weight"], eps)
+    return P.linear(x, w.get("lm_head.weight", w["model.embed_tokens.weight"]))
+
+
+def test_toy_architecture_with_routed_experts_and_a_position_encoding_of_its_own():
+    """Registered, built and stepped without a change to the package: whole prompts, then token by token with
+    unequal lengths, against the plain formulas.  32-bit (the winner of a near-tied router would differ between
+    roundings in bfloat16)."""
+    from gguf_rs_cli_b200.api import _build
+    from gguf_rs_cli_b200.engine.step import Engine, Entry
+    from gguf_rs_cli_b200.weights import TensorSource
+    register_more_toys()
+    w = toy2_weights()
+    model = _build(dict(TOY2), TensorSource(tensors={k: v.to(torch.bfloat16) for k, v in w.items()}, where="toy2"),
+                   "float32", DEV).model
+    kinds = [(type(l.feed_forward).__name__, type(l.mixer.position).__name__) for l in model.layers]
+    assert kinds == [("GatedMLP", "LinearInterleaved"), ("Top1Experts", "Rotary")] * 2
+    eng = Engine(model, n_tokens=64 * 8, n_slots=2, max_len=256)
+    g = torch.Generator().manual_seed(4)
+    seqs = [torch.randint(0, TOY2["vocab_size"], (n,), generator=g).tolist() for n in (90, 37)]
+    want = [toy2_plain_forward(w, s) for s in seqs]
+    slots = [eng.open() for _ in seqs]
+    cut = [70, 20]
+    logits = eng.step([Entry(s, q[:c], range(c)) for s, q, c in zip(slots, seqs, cut)])
+    assert_close(logits[:70], want[0][:70], "float32", "prompt 0")
+    assert_close(logits[70:], want[1][:20], "float32", "prompt 1")
+    for step in range(20):
+        live = [i for i in range(2) if cut[i] + step < len(seqs[i])]
+        logits = eng.step([Entry(slots[i], [seqs[i][cut[i] + step]], [0]) for i in live])
+        for row, i in enumerate(live):
+            assert_close(logits[row:row + 1], want[i][cut[i] + step:cut[i] + step + 1], "float32", f"seq {i} token {cut[i] + step}")
+    for s in slots:
+        eng.close(s)
+    eng.cache.check()
