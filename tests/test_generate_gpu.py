@@ -141,3 +141,30 @@ def test_decode_steps_updated_in_place_cross_pages(name):
         for g, w in zip(got, want):
             assert g == (w[:w.index(stop)] if stop in w else w)        # the stop token itself is not given out
         assert eng.cache.slots.held_count == 0
+
+
+def test_decode_past_a_thousand_positions_splits_pages_and_changes_graphs():
+    """Two sequences of the wide tiny model decode across position 960, where the decode attention goes from one
+    split of a sequence's pages to two (another captured graph from there on): the captured steps give the
+    tokens of the eager ones, and the logits on both sides of the change are the plain implementation's."""
+    from gguf_rs_cli_b200.engine.backend import EngineBackend
+    from gguf_rs_cli_b200.engine.generate import generate_ids
+    from gguf_rs_cli_b200.engine.step import Entry
+    from gguf_rs_cli_b200.sampling import SamplingParams
+    assert config("C")["max_position_embeddings"] >= 1024
+    prompts = [tokens_of("C", n, 500 + n) for n in (945, 930)]
+    outs = []
+    for graphs in (False, True):
+        eng = new_engine("C", "bfloat16", n_tokens=64 * 34, n_slots=2)
+        outs.append(generate_ids(EngineBackend(eng, use_graphs=graphs), prompts, 40, SamplingParams(temperature=0.0), []))
+        assert eng.cache.slots.held_count == 0
+    assert outs[0] == outs[1]
+    # logits of single-token steps at positions 940..985 of one long sequence against the plain ones
+    n = 986
+    toks, ref = tokens_of("C", n, 77), plain_logits("C", n, 77)
+    eng = new_engine("C", "bfloat16", n_tokens=64 * 34, n_slots=2)
+    a, b = eng.open(), eng.open()
+    eng.step([Entry(a, toks[:940], []), Entry(b, toks[:100], [])])
+    for i in range(940, n):
+        got = eng.step([Entry(a, [toks[i]], [0]), Entry(b, [toks[100 + i - 940]], [])])
+        assert_close(got[0], ref[i], "bfloat16", f"decoded position {i}")
