@@ -1,6 +1,7 @@
 """A small, whole library for the Llama dense decoder on one NVIDIA B200: from a model
 folder (config.json + safetensors) or random weights to generated token ids, on
-hand-written sm_100a kernels.  See DESIGN.md at the repository root."""
+hand-written sm_100a kernels.  config/, weights/, parts/, cache/, engine/ and sampling/ hold the
+library, csrc/ the kernels, api.py and cli.py the two ways in."""
 from .config import ConfigError, LlamaConfig, load_config, register_architecture, registered_architectures
 from .sampling.params import SamplingParams
 
