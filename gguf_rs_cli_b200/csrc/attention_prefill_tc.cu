@@ -3,16 +3,16 @@
 // with both products of flash attention issued as tcgen05.mma and their results in TMEM.
 //
 // A CTA owns 256 consecutive queries of one sequence and one head as two tiles of 128 and walks
-// the keys in blocks of 128 (two cache pages) that both tiles share.  10 warps:
+// the keys in blocks of 128 (two cache pages) that both tiles share.  18 warps:
 //   warp 0  TMA: both Q tiles once, then K and V pages into two-stage rings (128-byte swizzle);
 //   warp 1  one thread issues, tile by tile, S = Q K^T (M128 N128 K128) into the tile's TMEM
 //           buffer and, when the tile's probabilities are ready, O += P V (P read from TMEM,
 //           V from shared memory N-contiguous, as the cache stores it) into the tile's
 //           output accumulator, which stays in TMEM for the whole tile.  While one tile's
 //           warps work on their softmax the tensor core serves the other tile;
-//   warps 2-5 and 6-9  one tile each, one query row per thread (its TMEM lane): a first
-//           pass over S for the row's maximum, a second for the probabilities, in 32-bit;
-//           P goes back as bf16 into the first half of the columns S came from.
+//   warps 2-9 and 10-17  one tile each, two threads per query row (its TMEM lane), each with 64
+//           of a block's 128 keys: maximum (agreed between the two through shared memory), sum and
+//           probabilities in 32-bit; P goes back as bf16 into the first half of the columns S came from.
 //           Probabilities are taken relative to a reference maximum that is only raised when
 //           the row's maximum has grown by more than 2^8; only then is the row of O in TMEM
 //           (and the running sum) rescaled, so most blocks touch O through the MMA alone.
@@ -30,7 +30,7 @@ namespace {
 
 constexpr int AT_BM = 128, AT_BN = 128, AT_HD = 128;
 constexpr int AT_PAIR = 2 * AT_BM;             // queries per CTA
-constexpr int AT_THREADS = 320;                // TMA, MMA and two tiles of four softmax warps
+constexpr int AT_THREADS = 576;                // TMA, MMA and two tiles of eight softmax warps
 constexpr int AT_CHUNK = 128 * 128;            // bytes of a [128 rows x 64 columns] bf16 tile
 constexpr int AT_TILE = 2 * AT_CHUNK;          // 32 KB: 128 x 128 bf16
 constexpr int AT_PAGE_CHUNK = 64 * 128;        // bytes of a [64 rows x 64 columns] piece of a page
@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
     __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done[2];
     __shared__ uint32_t tmem_base;
     __shared__ volatile int abort_flag;
+    __shared__ float mx_s[2][2][2][AT_BM], l_s[2][2][AT_BM];      // exchanged between the two threads of a query row
 
     gb_grid_launch_dependents();
     // the list holds tiles of 128 queries; this kernel takes them two at a time, from the even ones
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
         for (int i = 0; i < 2; ++i) {
             mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-            mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&pv_done[i], 1);
+            mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 8); mbar_init(&pv_done[i], 1);
         }
         abort_flag = 0;
         fence_barrier_init();
@@ -199,114 +200,104 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
             }
         }
     } else {
-        const int t = (warp - 2) >> 2;                           // the tile of this warp
+        // eight warps per tile: two threads per query row, each with 64 of a block's 128 keys (warps 2..5 and
+        // 10..13: the first 64; 6..9 and 14..17: the other 64); the two agree on the row's maximum through
+        // shared memory.  A thread that has given up on a wait keeps its appointments with its partner (a named
+        // barrier does not time out).
+        const int t = (warp - 2) >> 3;                           // the tile of this warp
+        const int half = ((warp - 2) >> 2) & 1;
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;                       // query row of the tile = TMEM lane
         const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
-        const uint32_t s_addr = tmem_s + t * AT_BN + lane_addr, o_addr = tmem_o + t * AT_HD + lane_addr;
+        const uint32_t s_addr = tmem_s + t * AT_BN + lane_addr, o_addr = tmem_o + t * AT_HD + half * 64 + lane_addr;
         const int pq = r < rows[t] ? pos_lo[t] + r : -1;
         const int lo = p.window > 0 ? pq - p.window + 1 : 0;
         const float raise = 8.f / p.scale_log2;                  // the reference maximum follows only jumps beyond 2^8
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + t * 4 + quarter) : "memory"); };
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         int c = 0;                                               // blocks done by this tile
-        for (int j = blk_first[t]; j < blk_end[t] && ok; ++j, ++c) {
+        for (int j = blk_first[t]; j < blk_end[t]; ++j, ++c) {
+            if (!ok) { pair_sync(); continue; }
             const int s = j & 1;
-            const int key0 = (pg_base + 2 * j) * GB_PAGE;
-            if (!mbar_wait(&s_full[t], c & 1)) { if (lane == 0) atomicExch(p.status, 16); abort_flag = 1; ok = false; break; }
-            tc_fence_after();
-            const bool need_mask = key0 + AT_BN - 1 > pos_lo[t] || p.window > 0 || r >= rows[t];
-            // The block in two halves of 64 keys, each loaded from TMEM once: its maximum decides whether the
-            // reference is raised (rarely; then what the row has gathered so far is rescaled: O, the sums, and
-            // the first half's probabilities if they are written already), then its probabilities (two
-            // elements per instruction for the scaling and the sum; masked entries are -inf: 2^-inf is 0) go
-            // back as bf16 over the first half of the columns S came from: keys 0..63 into columns 0..31 once
-            // columns 0..63 are in registers, keys 64..127 into columns 32..63.
-            float v[64];
-            float add = 0.f;
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                tmem_ld64(s_addr + 64 * hh, v);
-                if (need_mask) {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const int ka = key0 + 64 * hh + i;
-                        if (ka > pq || ka < lo) v[i] = -INFINITY;
-                    }
-                }
-                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one long one
-#pragma unroll
-                for (int i = 0; i < 64; i += 4) {
-                    m4[0] = fmaxf(m4[0], v[i]); m4[1] = fmaxf(m4[1], v[i + 1]);
-                    m4[2] = fmaxf(m4[2], v[i + 2]); m4[3] = fmaxf(m4[3], v[i + 3]);
-                }
-                const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-                // raise the reference when the maximum has run away from it (or there was none yet)
-                float factor = 1.f;
-                if (mx > -INFINITY && (m_ref == -INFINITY || mx > m_ref + raise)) {
-                    factor = m_ref == -INFINITY ? 0.f : exp2f((m_ref - mx) * p.scale_log2);
-                    m_ref = mx;
-                }
-                if (__any_sync(0xffffffffu, factor != 1.f)) {
-                    if (c > 0) {
-                        // O must hold every block before this one before its rows are rescaled
-                        if (!mbar_wait(&pv_done[t], (c - 1) & 1)) { if (lane == 0) atomicExch(p.status, 17); abort_flag = 1; ok = false; }
-                        tc_fence_after();
-#pragma unroll 1
-                        for (int cc = 0; cc < 4; ++cc) {
-                            float o[32];
-                            tmem_ld32(o_addr + 32 * cc, o);
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) o[i] *= factor;
-                            tmem_st32(o_addr + 32 * cc, o);
-                        }
-                    }
-                    if (hh == 1) {
-                        // the first half's probabilities, already in place, relative to the new reference
-                        uint32_t w0[32];
-                        tmem_ld32_words(s_addr, w0);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            __nv_bfloat162 pk = *reinterpret_cast<__nv_bfloat162*>(&w0[i]);
-                            pk = __floats2bfloat162_rn(__low2float(pk) * factor, __high2float(pk) * factor);
-                            w0[i] = *reinterpret_cast<uint32_t*>(&pk);
-                        }
-                        tmem_st32_words(s_addr, w0);
-                    }
-                    tc_fence_before();
-                    l *= factor;
-                    add *= factor;
-                }
-                const float ms = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
-                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ms2 = make_float2(-ms, -ms);
-                float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-                uint32_t w[32];
-#pragma unroll
-                for (int i = 0; i < 64; i += 2) {
-                    float2 e = __ffma2_rn(make_float2(v[i], v[i + 1]), sc2, ms2);
-                    e.x = ex2_approx(e.x);
-                    e.y = ex2_approx(e.y);
-                    acc[(i >> 1) & 3] = __fadd2_rn(acc[(i >> 1) & 3], e);
-                    __nv_bfloat162 pk = __floats2bfloat162_rn(e.x, e.y);
-                    w[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
-                }
-                const float2 a01 = __fadd2_rn(acc[0], acc[1]), a23 = __fadd2_rn(acc[2], acc[3]);
-                add += (a01.x + a01.y) + (a23.x + a23.y);
-                tmem_st32_words(s_addr + 32 * hh, w);
+            const int key0 = (pg_base + 2 * j) * GB_PAGE + half * 64;
+            if (!mbar_wait(&s_full[t], c & 1)) {
+                if (lane == 0) atomicExch(p.status, 16);
+                abort_flag = 1;
+                ok = false;
+                pair_sync();
+                continue;
             }
-            if (!ok) break;
-            l += add;
+            tc_fence_after();
+            float v[64];
+            tmem_ld64(s_addr + 64 * half, v);
+            if (key0 + 63 > pos_lo[t] || p.window > 0 || r >= rows[t]) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const int ka = key0 + i;
+                    if (ka > pq || ka < lo) v[i] = -INFINITY;
+                }
+            }
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one long one
+#pragma unroll
+            for (int i = 0; i < 64; i += 4) {
+                m4[0] = fmaxf(m4[0], v[i]); m4[1] = fmaxf(m4[1], v[i + 1]);
+                m4[2] = fmaxf(m4[2], v[i + 2]); m4[3] = fmaxf(m4[3], v[i + 3]);
+            }
+            float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            mx_s[t][c & 1][half][r] = mx;
+            pair_sync();                                         // both halves of S are in registers from here on
+            mx = fmaxf(mx, mx_s[t][c & 1][half ^ 1][r]);
+            // raise the reference when the maximum has run away from it (or there was none yet)
+            float factor = 1.f;
+            if (mx > -INFINITY && (m_ref == -INFINITY || mx > m_ref + raise)) {
+                factor = m_ref == -INFINITY ? 0.f : exp2f((m_ref - mx) * p.scale_log2);
+                m_ref = mx;
+            }
+            if (c > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+                // O must hold every block before this one before its rows are rescaled (this thread's half of them)
+                if (!mbar_wait(&pv_done[t], (c - 1) & 1)) { if (lane == 0) atomicExch(p.status, 17); abort_flag = 1; ok = false; continue; }
+                tc_fence_after();
+#pragma unroll 1
+                for (int cc = 0; cc < 2; ++cc) {
+                    float o[32];
+                    tmem_ld32(o_addr + 32 * cc, o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] *= factor;
+                    tmem_st32(o_addr + 32 * cc, o);
+                }
+                tc_fence_before();
+            }
+            // probabilities (two elements per instruction for the scaling and the sum; masked entries are -inf:
+            // 2^-inf is 0), as bf16 over the first half of the columns S came from: this thread's 64 keys into
+            // columns 32 * half .. + 31 (the partner has read them, see the barrier above)
+            const float ms = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
+            const float2 ms2 = make_float2(-ms, -ms);
+            float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            uint32_t w[32];
+#pragma unroll
+            for (int i = 0; i < 64; i += 2) {
+                float2 e = __ffma2_rn(make_float2(v[i], v[i + 1]), sc2, ms2);
+                e.x = ex2_approx(e.x);
+                e.y = ex2_approx(e.y);
+                acc[(i >> 1) & 3] = __fadd2_rn(acc[(i >> 1) & 3], e);
+                __nv_bfloat162 pk = __floats2bfloat162_rn(e.x, e.y);
+                w[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+            }
+            const float2 a01 = __fadd2_rn(acc[0], acc[1]), a23 = __fadd2_rn(acc[2], acc[3]);
+            l = l * factor + ((a01.x + a01.y) + (a23.x + a23.y));
+            tmem_st32_words(s_addr + 32 * half, w);
             tc_fence_before();
-            if (key0 + AT_BN - 1 > valid_end) {
+            if ((pg_base + 2 * j) * GB_PAGE + AT_BN - 1 > valid_end) {
                 // key row r of this block holds nothing meaningful if it lies beyond the sequence's end (never
                 // written) or in a page this CTA did not load: zero its values before they are multiplied (both
-                // tiles do so before their own product of this block)
+                // tiles do so before their own product of this block; each of a row's two threads one half)
                 if (mbar_wait(&v_full[s], (j >> 1) & 1)) {
-                    if (key0 + r > valid_end) {
+                    if ((pg_base + 2 * j) * GB_PAGE + r > valid_end) {
                         uint4 z = make_uint4(0, 0, 0, 0);
-                        for (int cc = 0; cc < 2; ++cc)
-                            for (int piece = 0; piece < 8; ++piece)
-                                *reinterpret_cast<uint4*>(v_s + s * AT_TILE + cc * AT_CHUNK + r * 128 + piece * 16) = z;
+                        for (int piece = 0; piece < 8; ++piece)
+                            *reinterpret_cast<uint4*>(v_s + s * AT_TILE + half * AT_CHUNK + r * 128 + piece * 16) = z;
                     }
                     fence_proxy_async();                           // the patch is visible to the tensor core
                 } else {
@@ -321,11 +312,14 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
         // the tile's last product has been added to O
         if (ok && c > 0 && !mbar_wait(&pv_done[t], (c - 1) & 1)) { if (lane == 0) atomicExch(p.status, 19); ok = false; }
         tc_fence_after();
+        l_s[t][half][r] = l;
+        pair_sync();
+        l += l_s[t][half ^ 1][r];
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* dst = p.out + size_t(tok0 + t * AT_BM + r) * p.ldo + size_t(h) * AT_HD;
+        __nv_bfloat16* dst = p.out + size_t(tok0 + t * AT_BM + r) * p.ldo + size_t(h) * AT_HD + half * 64;
         if (c > 0) {
 #pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
+            for (int cc = 0; cc < 2; ++cc) {
                 float o[32];
                 tmem_ld32(o_addr + 32 * cc, o);                    // every lane takes part; rows beyond the tile are not stored
                 if (r < rows[t] && ok) {
