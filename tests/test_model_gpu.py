@@ -115,3 +115,32 @@ def test_step_errors_launch_nothing():
     assert eng.cache.length(s) == 0
     eng.close(s)
     eng.cache.check()
+
+
+def test_bfloat16_path_against_the_32_bit_path_at_the_benchmark_layer_sizes():
+    """Two layers of the Llama-3.1-8B layer shape (head size 128, 32 heads in 8 groups, widths 4096 / 14336;
+    a smaller vocabulary) with random weights: prompts of unequal lengths in one step (the tensor-core
+    attention and the two-SM product run here, which the tiny models do not reach), then single tokens; the
+    bfloat16 logits against the true 32-bit path's."""
+    from gguf_rs_cli_b200.api import from_random
+    from gguf_rs_cli_b200.engine.step import Engine, Entry
+    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 2, "hidden_size": 4096,
+           "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336,
+           "vocab_size": 8192, "rope_theta": 500000.0,
+           "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 8192},
+           "rms_norm_eps": 1e-5, "max_position_embeddings": 2048, "tie_word_embeddings": False, "hidden_act": "silu"}
+    g = torch.Generator().manual_seed(1)
+    toks = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in (700, 300, 64)]
+    res = {}
+    for dtype in ("float32", "bfloat16"):
+        model = from_random(cfg, seed=0, dtype=dtype, device="cuda:0").model
+        eng = Engine(model, n_tokens=64 * 24, n_slots=4, max_len=2048)
+        slots = [eng.open() for _ in toks]
+        out = [eng.step([Entry(s, t[:-8], [len(t) - 9, 0, len(t) // 2]) for s, t in zip(slots, toks)])]
+        for i in range(8, 0, -1):
+            out.append(eng.step([Entry(s, [t[-i]], [0]) for s, t in zip(slots, toks)]))
+        res[dtype] = torch.cat(out).float().cpu()
+        del model, eng
+        torch.cuda.empty_cache()
+    assert_close(res["bfloat16"], res["float32"], "bfloat16", "8B layer shape")
