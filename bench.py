@@ -231,7 +231,7 @@ def main():
     step_bytes = wbytes + args.batch * ctx_mid * kvb
     achieved = step_bytes / (ms * 1e-3) / 1e9
     line = {
-        "metric": "Llama-3.1-8B decode tok/s @ batch 8 (512-token prompts)", "value": round(tok_s, 2), "unit": "tokens/s",
+        "metric": f"Llama-3.1-8B decode tok/s @ batch {args.batch} ({PROMPT}-token prompts)", "value": round(tok_s, 2), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights N(0,0.02)",
         "impl": "ours",
@@ -240,7 +240,7 @@ def main():
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
                    "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single-gpu",
-                   "l2": "inputs (15 GB of weights per step) exceed L2", "peaks": pk["source"]},
+                   "l2": f"inputs ({wbytes / 1e9:.1f} GB of weights per step) exceed L2", "peaks": pk["source"]},
         "clocks": clocks, "gpu_launches": launches * args.steps,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": step_bytes},

@@ -1,11 +1,11 @@
-// Attention for prompts on the 5th-generation tensor cores (head size 128): the same
+// Attention for prompts on the 5th-generation tensor cores (head sizes 64 and 128): the same
 // arithmetic as attention_prefill.cu and the generic kernel (src/model/llama.rs:374-394),
 // with both products of flash attention issued as tcgen05.mma and their results in TMEM.
 //
 // A CTA owns 256 consecutive queries of one sequence and one head as two tiles of 128 and walks
 // the keys in blocks of 128 (two cache pages) that both tiles share.  18 warps:
 //   warp 0  TMA: both Q tiles once, then K and V pages into two-stage rings (128-byte swizzle);
-//   warp 1  one thread issues, tile by tile, S = Q K^T (M128 N128 K128) into the tile's TMEM
+//   warp 1  one thread issues, tile by tile, S = Q K^T (M128 N128, K = head size) into the tile's TMEM
 //           buffer and, when the tile's probabilities are ready, O += P V (P read from TMEM,
 //           V from shared memory N-contiguous, as the cache stores it) into the tile's
 //           output accumulator, which stays in TMEM for the whole tile.  While one tile's
@@ -28,14 +28,17 @@ using namespace sm100;
 
 namespace {
 
-constexpr int AT_BM = 128, AT_BN = 128, AT_HD = 128;
+constexpr int AT_BM = 128, AT_BN = 128;
 constexpr int AT_PAIR = 2 * AT_BM;             // queries per CTA
 constexpr int AT_THREADS = 576;                // TMA, MMA and two tiles of eight softmax warps
 constexpr int AT_CHUNK = 128 * 128;            // bytes of a [128 rows x 64 columns] bf16 tile
-constexpr int AT_TILE = 2 * AT_CHUNK;          // 32 KB: 128 x 128 bf16
 constexpr int AT_PAGE_CHUNK = 64 * 128;        // bytes of a [64 rows x 64 columns] piece of a page
-constexpr int AT_SMEM = 6 * AT_TILE + 1024;    // Q x2, K x2, V x2 (+ alignment slack)
-constexpr int AT_TMEM_COLS = 512;              // per tile: S (128; P in its first 64) and O (128)
+constexpr int AT_TMEM_COLS = 512;              // per tile: S (128 columns; P in its first 64) and O (head size)
+template <int HD> struct AtCfg {
+    static constexpr int CHUNKS = HD / 64;               // [128 x 64] pieces of a [128 x HD] tile
+    static constexpr int TILE = CHUNKS * AT_CHUNK;       // 32 KB at head size 128
+    static constexpr int SMEM = 6 * TILE + 1024;         // Q x2, K x2, V x2 (+ alignment slack)
+};
 
 struct AtParams {
     __nv_bfloat16* out;
@@ -61,12 +64,14 @@ __device__ __forceinline__ uint4 pack8(const float* p) {
     return r;
 }
 
+template <int HD>
 __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                              const __grid_constant__ CUtensorMap map_k,
                                                                              const __grid_constant__ CUtensorMap map_v,
                                                                              AtParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int AT_TILE = AtCfg<HD>::TILE, CHUNKS = AtCfg<HD>::CHUNKS;
     uint8_t* q_s = base;                         // 2 tiles
     uint8_t* k_s = base + 2 * AT_TILE;           // 2 stages
     uint8_t* v_s = base + 4 * AT_TILE;           // 2 stages
@@ -129,24 +134,24 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
         if (lane == 0) {
             mbar_expect_tx(&q_full, 2 * AT_TILE);
             for (int t = 0; t < 2; ++t)
-                for (int c = 0; c < 2; ++c)
-                    tma_load_2d(q_s + t * AT_TILE + c * AT_CHUNK, &map_q, h * AT_HD + 64 * c, tok0 + t * AT_BM, &q_full);
+                for (int c = 0; c < CHUNKS; ++c)
+                    tma_load_2d(q_s + t * AT_TILE + c * AT_CHUNK, &map_q, h * HD + 64 * c, tok0 + t * AT_BM, &q_full);
             for (int j = 0; j < n_blocks && !abort_flag; ++j) {
                 const int s = j & 1;
                 const uint32_t par = ((j >> 1) & 1) ^ 1;
                 const int pages = min(2, pg_end - (pg_base + 2 * j));          // the last block may hold one page
                 if (!mbar_wait(&k_empty[s], par)) { atomicExch(p.status, 11); abort_flag = 1; break; }
-                mbar_expect_tx(&k_full[s], pages * 2 * AT_PAGE_CHUNK);
+                mbar_expect_tx(&k_full[s], pages * CHUNKS * AT_PAGE_CHUNK);
                 for (int pg = 0; pg < pages; ++pg) {
                     const int y = (trow[(pg_base + 2 * j + pg) % p.ring_pages] * p.nkv + g) * GB_PAGE;
-                    for (int c = 0; c < 2; ++c)
+                    for (int c = 0; c < CHUNKS; ++c)
                         tma_load_2d(k_s + s * AT_TILE + c * AT_CHUNK + pg * AT_PAGE_CHUNK, &map_k, 64 * c, y, &k_full[s]);
                 }
                 if (!mbar_wait(&v_empty[s], par)) { atomicExch(p.status, 12); abort_flag = 1; break; }
-                mbar_expect_tx(&v_full[s], pages * 2 * AT_PAGE_CHUNK);
+                mbar_expect_tx(&v_full[s], pages * CHUNKS * AT_PAGE_CHUNK);
                 for (int pg = 0; pg < pages; ++pg) {
                     const int y = (trow[(pg_base + 2 * j + pg) % p.ring_pages] * p.nkv + g) * GB_PAGE;
-                    for (int c = 0; c < 2; ++c)
+                    for (int c = 0; c < CHUNKS; ++c)
                         tma_load_2d(v_s + s * AT_TILE + c * AT_CHUNK + pg * AT_PAGE_CHUNK, &map_v, 64 * c, y, &v_full[s]);
                 }
             }
@@ -154,7 +159,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc_bf16(AT_BM, AT_BN);
-            constexpr uint32_t idesc_pv = instr_desc_bf16_b_mn(AT_BM, AT_HD);
+            constexpr uint32_t idesc_pv = instr_desc_bf16_b_mn(AT_BM, HD);
             bool ok = mbar_wait(&q_full, 0);
             if (!ok) { atomicExch(p.status, 13); abort_flag = 1; }
             auto active = [&](int t, int j) { return j >= blk_first[t] && j < blk_end[t]; };
@@ -166,7 +171,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
                 tc_fence_after();
                 const uint32_t qa = smem_u32(q_s + t * AT_TILE), ka = smem_u32(k_s + s * AT_TILE);
 #pragma unroll
-                for (int k = 0; k < AT_HD / 16; ++k) {
+                for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t off = (k >> 2) * AT_CHUNK + (k & 3) * 32;
                     mma_f16(tmem_s + t * AT_BN, smem_desc_sw128(qa + off), smem_desc_sw128(ka + off), idesc_qk, k > 0 ? 1u : 0u);
                 }
@@ -187,7 +192,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
                         const uint32_t va = smem_u32(v_s + s * AT_TILE);
 #pragma unroll
                         for (int k = 0; k < AT_BN / 16; ++k)
-                            mma_f16_a_tmem(tmem_o + t * AT_HD, tmem_s + t * AT_BN + k * 8, smem_desc_sw128_mn(va + k * 2048, AT_CHUNK),
+                            mma_f16_a_tmem(tmem_o + t * HD, tmem_s + t * AT_BN + k * 8, smem_desc_sw128_mn(va + k * 2048, AT_CHUNK),
                                            idesc_pv, (done[t] > 0 || k > 0) ? 1u : 0u);
                         mma_commit(&pv_done[t]);              // O of the tile holds this block
                         ++done[t];
@@ -209,7 +214,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;                       // query row of the tile = TMEM lane
         const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
-        const uint32_t s_addr = tmem_s + t * AT_BN + lane_addr, o_addr = tmem_o + t * AT_HD + half * 64 + lane_addr;
+        const uint32_t s_addr = tmem_s + t * AT_BN + lane_addr, o_addr = tmem_o + t * HD + half * (HD / 2) + lane_addr;
         const int pq = r < rows[t] ? pos_lo[t] + r : -1;
         const int lo = p.window > 0 ? pq - p.window + 1 : 0;
         const float raise = 8.f / p.scale_log2;                  // the reference maximum follows only jumps beyond 2^8
@@ -260,7 +265,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
                 if (!mbar_wait(&pv_done[t], (c - 1) & 1)) { if (lane == 0) atomicExch(p.status, 17); abort_flag = 1; ok = false; continue; }
                 tc_fence_after();
 #pragma unroll 1
-                for (int cc = 0; cc < 2; ++cc) {
+                for (int cc = 0; cc < CHUNKS; ++cc) {
                     float o[32];
                     tmem_ld32(o_addr + 32 * cc, o);
 #pragma unroll
@@ -296,8 +301,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
                 if (mbar_wait(&v_full[s], (j >> 1) & 1)) {
                     if ((pg_base + 2 * j) * GB_PAGE + r > valid_end) {
                         uint4 z = make_uint4(0, 0, 0, 0);
-                        for (int piece = 0; piece < 8; ++piece)
-                            *reinterpret_cast<uint4*>(v_s + s * AT_TILE + half * AT_CHUNK + r * 128 + piece * 16) = z;
+                        for (int i = 0; i < HD / 16; ++i) {
+                            const int piece = half * (HD / 16) + i;          // 16-byte pieces of the row, eight per chunk
+                            *reinterpret_cast<uint4*>(v_s + s * AT_TILE + (piece >> 3) * AT_CHUNK + r * 128 + (piece & 7) * 16) = z;
+                        }
                     }
                     fence_proxy_async();                           // the patch is visible to the tensor core
                 } else {
@@ -316,10 +323,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_prefill_tc_kernel(con
         pair_sync();
         l += l_s[t][half ^ 1][r];
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* dst = p.out + size_t(tok0 + t * AT_BM + r) * p.ldo + size_t(h) * AT_HD + half * 64;
+        __nv_bfloat16* dst = p.out + size_t(tok0 + t * AT_BM + r) * p.ldo + size_t(h) * HD + half * (HD / 2);
         if (c > 0) {
 #pragma unroll 1
-            for (int cc = 0; cc < 2; ++cc) {
+            for (int cc = 0; cc < CHUNKS; ++cc) {
                 float o[32];
                 tmem_ld32(o_addr + 32 * cc, o);                    // every lane takes part; rows beyond the tile are not stored
                 if (r < rows[t] && ok) {
@@ -345,18 +352,18 @@ int* g_at_status_dev = nullptr;
 }  // namespace
 
 GB_API int gb_attention_prefill_tc_supported(int hd, int cache_dtype, int q_dtype) {
-    return cache_dtype == GB_BF16 && q_dtype == GB_BF16 && hd == AT_HD;
+    return cache_dtype == GB_BF16 && q_dtype == GB_BF16 && (hd == 64 || hd == 128);
 }
 
 GB_API int gb_attention_prefill_tc_tile() { return AT_BM; }
 
-// q: bf16 [T, nh*128] (rotated) with pitch ldq; kcache, vcache: one run's pages [n_pages, nkv, 64, 128];
+// q: bf16 [T, nh*hd] (rotated) with pitch ldq; kcache, vcache: one run's pages [n_pages, nkv, 64, hd];
 // tiles: (sequence row, first query) per 128 queries.  Same contract as gb_attention_prefill.
 GB_API int gb_attention_prefill_tc(const void* q, long long ldq, void* out, long long ldo, int T, int nh, int nkv, int hd,
                                    const int* tiles, int n_tiles, const int* cu, const int* starts, const int* qlens,
                                    const int* table, int table_width, int ring_pages, const void* kcache,
                                    const void* vcache, long long n_pages, int window, float scale, cudaStream_t stream) {
-    GB_REQUIRE(gb_attention_prefill_tc_supported(hd, GB_BF16, GB_BF16), "gb_attention_prefill_tc: head_dim %d is not 128", hd);
+    GB_REQUIRE(gb_attention_prefill_tc_supported(hd, GB_BF16, GB_BF16), "gb_attention_prefill_tc: head_dim %d is neither 64 nor 128", hd);
     GB_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "gb_attention_prefill_tc: bad head counts %d / %d", nh, nkv);
     GB_REQUIRE(n_tiles <= 65535, "gb_attention_prefill_tc: %d tiles of queries are too many for one launch", n_tiles);
     GB_REQUIRE(window >= 0 && ring_pages > 0 && table_width > 0 && n_pages > 0, "gb_attention_prefill_tc: bad cache geometry");
@@ -371,8 +378,9 @@ GB_API int gb_attention_prefill_tc(const void* q, long long ldq, void* out, long
     }
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess)
-            return gb_fail("gb_attention_prefill_tc: cannot get %d bytes of shared memory", AT_SMEM);
+        if (cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, AtCfg<64>::SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AtCfg<128>::SMEM) != cudaSuccess)
+            return gb_fail("gb_attention_prefill_tc: cannot get %d bytes of shared memory", AtCfg<128>::SMEM);
         configured = true;
     }
     CUtensorMap mq, mk, mv;
@@ -383,7 +391,8 @@ GB_API int gb_attention_prefill_tc(const void* q, long long ldq, void* out, long
     p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.cu = cu; p.starts = starts; p.qlens = qlens; p.table = table;
     p.status = g_at_status_dev; p.ldo = ldo; p.nh = nh; p.nkv = nkv; p.table_width = table_width;
     p.ring_pages = ring_pages; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
-    cudaError_t e = gb_launch(attention_prefill_tc_kernel, dim3(nh, n_tiles), dim3(AT_THREADS), AT_SMEM, stream, mq, mk, mv, p);
+    cudaError_t e = hd == 64 ? gb_launch(attention_prefill_tc_kernel<64>, dim3(nh, n_tiles), dim3(AT_THREADS), AtCfg<64>::SMEM, stream, mq, mk, mv, p)
+                             : gb_launch(attention_prefill_tc_kernel<128>, dim3(nh, n_tiles), dim3(AT_THREADS), AtCfg<128>::SMEM, stream, mq, mk, mv, p);
     if (e != cudaSuccess) return gb_fail("gb_attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
     return 0;
 }

@@ -179,25 +179,26 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                     if (p.splits == 1) {
                         tmem_ld16(taddr + c0, v);
                     } else {
-                        // the splits' partial sums in ascending order; 4 columns x 4 splits of loads in flight
+                        // the splits' partial sums in ascending order; 8 columns x 8 splits of loads in flight
+                        // (every round of loads costs a trip to L2, and the kernel after this one waits for it)
 #pragma unroll
                         for (int jj = 0; jj < 16; ++jj) v[jj] = 0.f;
 #pragma unroll
-                        for (int j0 = 0; j0 < 16; j0 += 4) {
+                        for (int j0 = 0; j0 < 16; j0 += 8) {
                             if (c0 + j0 >= cols) break;
-                            for (int s0 = 0; s0 < p.splits; s0 += 4) {
-                                float ld[4][4];
+                            for (int s0 = 0; s0 < p.splits; s0 += 8) {
+                                float ld[8][8];
 #pragma unroll
-                                for (int si = 0; si < 4; ++si)
+                                for (int si = 0; si < 8; ++si)
 #pragma unroll
-                                    for (int jj = 0; jj < 4; ++jj)
+                                    for (int jj = 0; jj < 8; ++jj)
                                         ld[si][jj] = (s0 + si < p.splits && c0 + j0 + jj < cols)
                                                          ? __ldcg(partials + size_t(s0 + si) * (BN * BM) + (c0 + j0 + jj) * BM + row)
                                                          : 0.f;
 #pragma unroll
-                                for (int si = 0; si < 4; ++si)
+                                for (int si = 0; si < 8; ++si)
 #pragma unroll
-                                    for (int jj = 0; jj < 4; ++jj) v[j0 + jj] += ld[si][jj];
+                                    for (int jj = 0; jj < 8; ++jj) v[j0 + jj] += ld[si][jj];
                             }
                         }
                     }

@@ -302,8 +302,8 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_hea
                       table: torch.Tensor, ring_pages: int, kcache: torch.Tensor, vcache: torch.Tensor, window: int,
                       scale: float, tc: Optional[bool] = None) -> torch.Tensor:
     """Many tokens per sequence over the bf16 cache (which already holds their keys and
-    values), flash style.  tc: both products on tcgen05 with S and PV in TMEM (head size 128; the
-    default where it fits), else on mma.sync (head sizes 64 and 128)."""
+    values), flash style.  tc: both products on tcgen05 with S and PV in TMEM (the default where it
+    fits), else on mma.sync; both take head sizes 64 and 128."""
     _cuda(q, out, tiles, cu, starts, qlens, table, kcache, vcache)
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (q.shape[0], n_heads * head_dim)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16

@@ -478,8 +478,6 @@ def prefill_meta(lens, qlens):
 @pytest.mark.parametrize("tc", [False, True])
 def test_attention_prefill(nh, nkv, hd, tc):
     k = K()
-    if tc and hd != 128:
-        pytest.skip("the tcgen05 attention kernel takes head size 128")
     lens, qlens = [200, 1, 65, 130, 300, 513], [200, 1, 3, 40, 129, 513]   # whole prompts and further pieces
     q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, qlens, BF, seed=hd + nh)
     tiles, cu, starts, ql = prefill_meta(lens, qlens)
@@ -495,7 +493,7 @@ def test_attention_prefill(nh, nkv, hd, tc):
 
 
 @pytest.mark.parametrize("window", [1, 64, 65, 100, 300])
-@pytest.mark.parametrize("hd,tc", [(64, False), (128, False), (128, True)])
+@pytest.mark.parametrize("hd,tc", [(64, False), (128, False), (64, True), (128, True)])
 def test_attention_prefill_far_key_and_window(window, hd, tc):
     k = K()
     nh, nkv = 8, 2
@@ -513,13 +511,13 @@ def test_attention_prefill_far_key_and_window(window, hd, tc):
 
 
 @pytest.mark.parametrize("key", [3, 70, 200, 449, 650])
-@pytest.mark.parametrize("tc", [False, True])
-def test_attention_prefill_score_that_stands_out_anywhere_in_a_block(key, tc):
+@pytest.mark.parametrize("hd,tc", [(128, False), (64, True), (128, True)])
+def test_attention_prefill_score_that_stands_out_anywhere_in_a_block(key, hd, tc):
     """One key whose score with the last query towers over the rest, placed in the first or second half of the
     first or a later block of 128 keys: the running maximum then jumps in the middle of a block, after sums,
     outputs and probabilities have been gathered relative to the old one."""
     k = K()
-    nh, nkv, hd = 8, 2, 128
+    nh, nkv = 8, 2
     lens, qlens = [700, 300], [700, 150]
     q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, qlens, BF, 9, boost=(0, key, 5))
     tiles, cu, starts, ql = prefill_meta(lens, qlens)
@@ -534,11 +532,11 @@ def test_attention_prefill_score_that_stands_out_anywhere_in_a_block(key, tc):
     assert float((got - v_key).abs().max()) < 0.05 * float(v_key.abs().max())
 
 
-@pytest.mark.parametrize("tc", [False, True])
-def test_attention_prefill_ignores_unwritten_cache_rows(tc):
+@pytest.mark.parametrize("hd,tc", [(128, False), (64, True), (128, True)])
+def test_attention_prefill_ignores_unwritten_cache_rows(hd, tc):
     """Rows of a page beyond the sequence's end hold NaN here; they must not reach the output."""
     k = K()
-    nh, nkv, hd = 4, 2, 128
+    nh, nkv = 4, 2
     lens = qlens = [70]
     q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, qlens, BF, 1)
     assert torch.isnan(kc[int(table[0, 1]), :, 10:, :].float()).all()
