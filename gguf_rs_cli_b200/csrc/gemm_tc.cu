@@ -31,7 +31,7 @@ using namespace sm100;
 namespace {
 
 template <int BN>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(TC_THREADS, TileCfg<BN>::SMEM <= 112 * 1024 ? 2 : 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x, TcParams p) {
     using Cfg = TileCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -135,18 +135,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             const Unit w = unit_of(u, p, BN, token_tiles, kb_total);
             const int buf = j & 1;
             const int n = w.n0 + row;
+            const int cols = min(BN, p.T - w.t0);       // valid tokens of this tile
+            // What the kernel before left for this tile is fetched while the products still run: the sums of
+            // squares behind the tokens' scales and, in the 16-token kernel, this thread's row of the residual
+            // stream (each a trip to L2 that the kernel after this one would otherwise wait for).
+            if (first) { gb_grid_wait(); first = false; }    // also before anything is written that the kernel before may still read
+            float bias = 0.f;
+            if (p.bias && n < p.N) bias = gb_load(p.bias, p.bias_dtype, n);
+            if (p.row_ssq) tc_token_scales<BN>(p, w.t0, cols, row, rstd_s, part_s);
+            float x_early[16];
+            if (BN == 16 && p.resid_x) {
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                    x_early[c] = (n < p.N && c < cols) ? __ldcg(p.resid_x + size_t(w.t0 + c) * p.ld_x + n) : 0.f;
+            }
             const bool waited = mbar_wait(&acc_full[buf], (j >> 1) & 1);
-            if (first) { gb_grid_wait(); first = false; }    // before anything is written that the kernel before may still read
             if (!waited) {                               // the error path: give up on the remaining units too
                 if (lane == 0) atomicExch(p.status, 3);
                 break;
             }
             tc_fence_after();
             const uint32_t taddr = tmem_d + (uint32_t(quarter * 32) << 16) + buf * BN;
-            const int cols = min(BN, p.T - w.t0);       // valid tokens of this tile
-            float bias = 0.f;
-            if (p.bias && n < p.N) bias = gb_load(p.bias, p.bias_dtype, n);
-            if (p.row_ssq) tc_token_scales<BN>(p, w.t0, cols, row, rstd_s, part_s);
             const float* partials = p.scratch + size_t(w.tile) * p.splits * (BN * BM);
             bool finish = true;                          // does this CTA write the tile's result?
             if (p.splits > 1) {
@@ -202,7 +211,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                             }
                         }
                     }
-                    tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, waited, c0, cols, v, rstd_s, ssq_s);
+                    tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, waited, c0, cols, v, rstd_s, ssq_s,
+                                        BN == 16 && p.resid_x ? x_early : nullptr);
                 }
                 if (p.resid_x) tc_write_ssq<BN>(p, w.n0, w.t0, row, 0, cols, ssq_s);
                 if (p.splits > 1 && threadIdx.x == 64) p.counters[w.tile] = 0;       // ready for the next launch

@@ -108,11 +108,12 @@ __device__ __forceinline__ void tc_token_scales(const TcParams& p, int t0, int c
 }
 
 // The last steps for 16 columns (tokens c0 .. c0+15 of the tile, those below c_end being valid) of this
-// thread's feature row n = n0 + row: v[jj] holds the finished sum of column c0 + jj.
+// thread's feature row n = n0 + row: v[jj] holds the finished sum of column c0 + jj.  x_early: the 16 values of
+// the residual stream at these places if the caller has read them already, else null.
 template <int BN>
 __device__ __forceinline__ void tc_finish_chunk(const TcParams& p, int n0, int t0, int n, int row, int lane, int quarter,
                                                 float bias, bool waited, int c0, int c_end, float (&v)[16],
-                                                const float* rstd_s, float (*ssq_s)[BN]) {
+                                                const float* rstd_s, float (*ssq_s)[BN], const float* x_early = nullptr) {
     if (p.row_ssq) {
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj) v[jj] *= rstd_s[min(c0 + jj, BN - 1)];
@@ -123,7 +124,8 @@ __device__ __forceinline__ void tc_finish_chunk(const TcParams& p, int n0, int t
         float xv[16];
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj)
-            xv[jj] = (n < p.N && c0 + jj < c_end) ? __ldcg(p.resid_x + size_t(t0 + c0 + jj) * p.ld_x + n) : 0.f;
+            xv[jj] = x_early ? x_early[jj]
+                             : (n < p.N && c0 + jj < c_end) ? __ldcg(p.resid_x + size_t(t0 + c0 + jj) * p.ld_x + n) : 0.f;
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj) {
             float sq = 0.f;
