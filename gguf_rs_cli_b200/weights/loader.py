@@ -81,6 +81,18 @@ class TensorSource:
             return self._tensors[name]
         return self._index[name].tensor(name)
 
+    def dtype(self, name: str) -> torch.dtype:
+        if name in self._tensors:
+            return self._tensors[name].dtype
+        return self._index[name].dtype(name)
+
+    def to_device(self, name: str, dtype: torch.dtype, device) -> torch.Tensor:
+        """The tensor on `device` as `dtype`; tensors of a file on their way to a CUDA device are staged and
+        converted by the native reader."""
+        if name not in self._tensors and torch.device(device).type == "cuda":
+            return self._index[name].to_device(name, dtype, device)
+        return self.get(name).to(device=device, dtype=dtype).contiguous()
+
 
 def storage_dtype(stored: torch.dtype, mode: torch.dtype) -> torch.dtype:
     """The dtype a tensor is kept in on the device (see the module text)."""
@@ -132,8 +144,8 @@ class WeightStore:
         if name is None:
             return None
         if name not in self._cache:
-            t = self.source.get(name)
-            self._cache[name] = t.to(device=self.device, dtype=storage_dtype(t.dtype, self.mode)).contiguous()
+            keep = storage_dtype(self.source.dtype(name), self.mode)
+            self._cache[name] = self.source.to_device(name, keep, self.device)
         return self._cache[name]
 
     def release(self) -> None:

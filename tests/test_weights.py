@@ -51,6 +51,35 @@ def test_safetensors_rejects_broken_files(tmp_path):
         SafetensorsFile(str(p))
 
 
+def test_safetensors_header_escapes_metadata_and_unknown_keys(tmp_path):
+    """The header is JSON: names may hold escapes, entries may hold keys this reader does not know, and
+    __metadata__ is kept; a name listed twice and text after the header's end are refused."""
+    p = tmp_path / "h.safetensors"
+    data = torch.arange(6, dtype=torch.float32)
+    raw = data.numpy().tobytes()
+    hdr = ('{"__metadata__": {"format": "pt", "note": "a \\"quoted\\" \\u00e9\\ud83d\\ude00", "n": 3},'
+           ' "layer\\u002e0/w\\t": {"dtype": "F32", "extra": [1, {"x": null}, "s"], "shape": [2, 3], "data_offsets": [0, 24]},'
+           ' "empty": {"dtype": "BF16", "shape": [0, 4], "data_offsets": [24, 24]}}').encode()
+    p.write_bytes(struct.pack("<Q", len(hdr)) + hdr + raw)
+    f = SafetensorsFile(str(p))
+    assert f.metadata == {"format": "pt", "note": 'a "quoted" \u00e9\U0001F600'}
+    assert sorted(f.names()) == ["empty", "layer.0/w\t"]
+    assert torch.equal(f.tensor("layer.0/w\t"), data.reshape(2, 3)) and f.tensor("empty").shape == (0, 4)
+    view = f.tensor("layer.0/w\t")[1]
+    del f                                                    # the map stays while a tensor views it
+    assert view.tolist() == [3.0, 4.0, 5.0]
+    twice = b'{"w": {"dtype": "U8", "shape": [1], "data_offsets": [0, 1]}, "w": {"dtype": "U8", "shape": [1], "data_offsets": [0, 1]}}'
+    p.write_bytes(struct.pack("<Q", len(twice)) + twice + b"\0")
+    with pytest.raises(WeightFileError, match="listed twice"):
+        SafetensorsFile(str(p))
+    for bad in (b'{"w": {"dtype": "U8", "shape": [1], "data_offsets": [0, 1]}} x', b'{"w": {"dtype": "U8", "shape": [1.5]}}', b'["w"]'):
+        p.write_bytes(struct.pack("<Q", len(bad)) + bad + b"\0")
+        with pytest.raises(WeightFileError, match="not JSON"):
+            SafetensorsFile(str(p))
+    with pytest.raises(WeightFileError, match="cannot open"):
+        SafetensorsFile(str(tmp_path / "absent.safetensors"))
+
+
 def test_names_and_shapes_match_the_plain_reference():
     for name in "AB":
         raw = config(name)
