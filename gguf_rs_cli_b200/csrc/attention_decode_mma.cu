@@ -74,6 +74,42 @@ template <int HD> __device__ __forceinline__ int dm_swz(int row, int chunk) {
     return row * HD + (((chunk & ~7) | ((chunk ^ row) & 7)) << 3);
 }
 
+// The partial results of a (token, head tile)'s splits, merged in split order into the output: every split
+// left, per head, its unnormalised sum of values, its maximum (in units of log2) and its sum of weights.
+template <int HD>
+__device__ __forceinline__ void dm_merge_splits(const DmParams& p, int t, int h0, int heads, int tid, int threads) {
+    for (int i = tid; i < heads * HD; i += threads) {
+        const int r = i / HD, d = i - r * HD;
+        const float* rec = p.scratch + (size_t(t) * p.nh + h0 + r) * p.splits * (HD + 2);
+        float M = -INFINITY;
+        for (int s0 = 0; s0 < p.splits; s0 += 8) {
+            float mv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mv[j] = s0 + j < p.splits ? __ldcg(rec + (s0 + j) * (HD + 2) + HD) : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) M = fmaxf(M, mv[j]);
+        }
+        float L = 0.f, acc = 0.f;
+        for (int s0 = 0; s0 < p.splits; s0 += 8) {
+            float mv[8], lv[8], ov[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                bool ok = s0 + j < p.splits;
+                mv[j] = ok ? __ldcg(rec + (s0 + j) * (HD + 2) + HD) : -INFINITY;
+                lv[j] = ok ? __ldcg(rec + (s0 + j) * (HD + 2) + HD + 1) : 0.f;
+                ov[j] = ok ? __ldcg(rec + (s0 + j) * (HD + 2) + d) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float wgt = mv[j] == -INFINITY ? 0.f : exp2f(mv[j] - M);
+                L += lv[j] * wgt;
+                acc += ov[j] * wgt;
+            }
+        }
+        p.out[size_t(t) * p.ldo + size_t(h0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
+    }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmParams p) {
     constexpr int CH = HD / 8, KS = HD / 16, OT = HD / 8, HALF = HD / 2;
@@ -339,36 +375,7 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
     __syncthreads();
     if (!last_flag) return;
     __threadfence();
-    for (int i = tid; i < heads * HD; i += DM_THREADS) {
-        const int r = i / HD, d = i - r * HD;
-        const float* rec = p.scratch + (size_t(t) * p.nh + h0 + r) * p.splits * (HD + 2);
-        float M = -INFINITY;
-        for (int s0 = 0; s0 < p.splits; s0 += 8) {
-            float mv[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) mv[j] = s0 + j < p.splits ? __ldcg(rec + (s0 + j) * (HD + 2) + HD) : -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) M = fmaxf(M, mv[j]);
-        }
-        float L = 0.f, acc = 0.f;
-        for (int s0 = 0; s0 < p.splits; s0 += 8) {
-            float mv[8], lv[8], ov[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                bool ok = s0 + j < p.splits;
-                mv[j] = ok ? __ldcg(rec + (s0 + j) * (HD + 2) + HD) : -INFINITY;
-                lv[j] = ok ? __ldcg(rec + (s0 + j) * (HD + 2) + HD + 1) : 0.f;
-                ov[j] = ok ? __ldcg(rec + (s0 + j) * (HD + 2) + d) : 0.f;
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float wgt = mv[j] == -INFINITY ? 0.f : exp2f(mv[j] - M);
-                L += lv[j] * wgt;
-                acc += ov[j] * wgt;
-            }
-        }
-        p.out[size_t(t) * p.ldo + size_t(h0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
-    }
+    dm_merge_splits<HD>(p, t, h0, heads, tid, DM_THREADS);
     if (tid == 0) p.counters[t * gridDim.y + blockIdx.y] = 0;
 }
 
@@ -376,7 +383,7 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
 // time is the latency of its pages one after the other: twelve warps, each taking half pages of 32 keys (warp w:
 // half pages w, w + 12, ...) into a slot of shared memory of its own, so that six pages are on their way at
 // once, twelve warps work on them and nobody waits for a block-wide barrier per page.  One CTA per SM (twelve
-// slots of 32 keys and values); no splits.
+// slots of 32 keys and values); a sequence's pages may be split over several CTAs as in the other kernel.
 constexpr int PW_WARPS = 12;
 constexpr int PW_THREADS = PW_WARPS * 32;
 constexpr int PW_KEYS = 32;                 // keys per slot
@@ -392,6 +399,7 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
     float* merge_o = reinterpret_cast<float*>(ks);                                    // reused after the loop: [warps][16][HD]
     __shared__ float m_s[PW_WARPS][DM_ROWS], l_s[PW_WARPS][DM_ROWS];
     __shared__ float cs_s[HALF], sn_s[HALF];
+    __shared__ int last_flag;
 
     gb_grid_launch_dependents();
     const bool early = p.rotate && p.k_new != nullptr;       // see the other kernel: pages before the wait
@@ -402,23 +410,27 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
     const int g = blockIdx.y / gtiles;
     const int h0 = g * G + (blockIdx.y % gtiles) * DM_ROWS;
     const int heads = min(DM_ROWS, g * G + G - h0);
+    const int split = blockIdx.z;
     const int b = p.seq_of[t];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     if (b < 0) {
         if (early) gb_grid_wait();
-        for (int i = tid; i < heads * HD; i += PW_THREADS)
-            p.out[size_t(t) * p.ldo + size_t(h0) * HD + i] = __float2bfloat16_rn(0.f);
+        if (split == 0)
+            for (int i = tid; i < heads * HD; i += PW_THREADS)
+                p.out[size_t(t) * p.ldo + size_t(h0) * HD + i] = __float2bfloat16_rn(0.f);
         return;
     }
     const int pos = p.pos[t];
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-    const int pg_begin = lo >> GB_PAGE_SHIFT, pg_end = (pos >> GB_PAGE_SHIFT) + 1;
+    const int first_page = lo >> GB_PAGE_SHIFT, n_pages = (pos >> GB_PAGE_SHIFT) - first_page + 1;
+    const int pg_begin = first_page + int((long long)split * n_pages / p.splits);
+    const int pg_end = first_page + int((long long)(split + 1) * n_pages / p.splits);
     const int* trow = p.table + size_t(b) * p.table_width;
     const bool own_kv = p.rotate && p.k_new != nullptr;
     __nv_bfloat16* kt = ks + warp * SLOT_ELEMS;
     __nv_bfloat16* vt = vs + warp * SLOT_ELEMS;
-    const int u_end = 2 * (pg_end - pg_begin);               // half pages, counted from the first page
+    const int u_end = 2 * (pg_end - pg_begin);               // half pages, counted from this split's first page
 
     auto load_half = [&](int u) {
         const int pg = pg_begin + (u >> 1), row0 = (u & 1) * PW_KEYS;
@@ -603,8 +615,27 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
             L += l_s[w][r] * wgt;
             acc += merge_o[(size_t(w) * DM_ROWS + r) * HD + d] * wgt;
         }
-        p.out[size_t(t) * p.ldo + size_t(h0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
+        if (p.splits == 1) {
+            p.out[size_t(t) * p.ldo + size_t(h0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            float* rec = p.scratch + ((size_t(t) * p.nh + h0 + r) * p.splits + split) * (HD + 2);
+            rec[d] = acc;
+            if (d == 0) { rec[HD] = M == -INFINITY ? -INFINITY : M * p.scale_log2; rec[HD + 1] = L; }
+        }
     }
+    if (p.splits == 1) return;
+    // ---- the splits of a (token, head tile) are merged by the CTA that finishes last, in split order
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int old = atomicAdd(&p.counters[t * gridDim.y + blockIdx.y], 1);
+        last_flag = (old == p.splits - 1);
+    }
+    __syncthreads();
+    if (!last_flag) return;
+    __threadfence();
+    dm_merge_splits<HD>(p, t, h0, heads, tid, PW_THREADS);
+    if (tid == 0) p.counters[t * gridDim.y + blockIdx.y] = 0;
 }
 
 template <int HD> int launch_pw(const DmParams& p, dim3 grid, cudaStream_t stream) {
@@ -674,7 +705,7 @@ static int decode_mma(const void* q, long long ldq, void* out, long long ldo, in
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (splits == 1 && g_pages_kernel && (long long)T * nkv * gtiles <= sms)       // few CTAs: a CTA's latency is the step's
+    if (g_pages_kernel && (long long)T * nkv * gtiles * splits <= sms)       // few CTAs: a CTA's latency is the step's
         return hd == 64 ? launch_pw<64>(p, grid, stream) : launch_pw<128>(p, grid, stream);
     return hd == 64 ? launch_dm<64>(p, grid, stream) : launch_dm<128>(p, grid, stream);
 }

@@ -207,24 +207,36 @@ def attention_decode_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim: 
     return bool(native.library().gb_attention_decode_supported(head_dim, dtype_code(kcache), dtype_code(q)))
 
 
-SPLIT_CLASSES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32)
+SPLIT_CLASSES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128)
+
+
+def _split_class(n: int) -> int:
+    return max(c for c in SPLIT_CLASSES if c <= max(n, 1))
 
 
 def decode_split_class(max_kv: int) -> int:
-    """Sequences up to max_kv positions long want at most this many splits of their pages: 8 pages or more
-    per split (merging the splits costs more than it saves below that), rounded down to one of a few
-    values (a captured graph is made per class)."""
-    want = ((max_kv + 63) // 64) // 8
-    return max(c for c in SPLIT_CLASSES if c <= max(want, 1))
+    """The class of a step whose longest sequence has max_kv positions: a quarter of its pages, rounded down
+    to one of a few values.  Steps of one class split their sequences' pages in the same way (decode_splits),
+    and a captured graph is made per class."""
+    return _split_class(((max_kv + 63) // 64) // 4)
 
 
 def decode_splits(T: int, n_heads: int, n_kv_heads: int, max_kv: int, sms: int, mma: bool) -> int:
-    """Splits of each sequence's pages for a decode step: the class of its longest sequence, but no more than
-    fit the device at once with two CTAs per SM (a second round of CTAs costs more than the splits save)."""
+    """Splits of each sequence's pages for a decode step.  The rule for many CTAs: 8 pages or more per split
+    (merging the splits costs more than it saves below that) and no more CTAs than fit the device at once
+    with two per SM (a second round costs more than the splits save).  Where even four pages per split leave
+    no more CTAs than SMs (long sequences, very few of them), the tensor-core kernel runs one CTA per SM whose
+    twelve warps take half pages each, and finer splits pay: from 16 pages on, 4 pages per split."""
     group = n_heads // n_kv_heads
     tile = 16 if mma else (8 if group >= 8 else 4 if group > 2 else group)
     ctas = T * n_kv_heads * ((group + tile - 1) // tile)
-    return max(1, min(decode_split_class(max_kv), (2 * sms) // ctas))
+    pages = (max_kv + 63) // 64
+    coarse = max(1, min(_split_class(pages // 8), 32, (2 * sms) // ctas))
+    if mma and pages >= 16:
+        fine = _split_class(min(pages // 4, sms // ctas))
+        if fine >= coarse:
+            return fine
+    return coarse
 
 
 def attention_decode_mma_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> bool:

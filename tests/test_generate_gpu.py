@@ -145,7 +145,7 @@ def test_decode_steps_updated_in_place_cross_pages(name):
 
 def test_decode_past_a_thousand_positions_splits_pages_and_changes_graphs():
     """Two sequences of the wide tiny model decode across position 960, where the decode attention goes from one
-    split of a sequence's pages to two (another captured graph from there on): the captured steps give the
+    split of a sequence's pages to four (another captured graph from there on): the captured steps give the
     tokens of the eager ones, and the logits on both sides of the change are the plain implementation's."""
     from gguf_rs_cli_b200.engine.backend import EngineBackend
     from gguf_rs_cli_b200.engine.generate import generate_ids

@@ -415,6 +415,25 @@ def test_attention_decode_far_key_and_window(window, mma):
     assert rel_err(want_w, want) > 0.05
 
 
+@pytest.mark.parametrize("splits", [None, 16, 48])
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attention_decode_few_long_sequences_in_many_splits(splits, hd):
+    """Two sequences, one of them long: one CTA per SM takes a few pages each (more splits than the short
+    sequence has pages: some CTAs get none), and a key far back in the long one carries a head."""
+    k = K()
+    nh, nkv = 8, 2
+    lens = [2100, 130]
+    q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, [1, 1], BF, 11, boost=(0, 77, 3))
+    out = torch.full((2, nh * hd), float("nan"), dtype=BF, device=DEV)
+    k.attention_decode(q, out, nh, nkv, hd, seq_of, pos, table, 1 << 20, kc, vc, 0, 1 / math.sqrt(hd), splits=splits, mma=True,
+                       max_kv=max(lens))
+    assert rel_err(out, want) < 1e-2
+    v_key = read_cache(vc, table[0], lens[0])[77, 3 // (nh // nkv)]
+    got = out[0, 3 * hd:4 * hd].float().cpu()
+    assert float((got - v_key).abs().max()) < 0.05 * float(v_key.abs().max())
+    assert k.decode_splits(2, nh, nkv, max(lens), 148, True) == 8 and k.decode_splits(64, nh, nkv, max(lens), 148, True) == 2
+
+
 @pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 128), (40, 2, 64), (7, 7, 128), (16, 1, 64)])
 @pytest.mark.parametrize("pairing,rot", [(0, 1.0), (1, 1.0), (0, 0.5), (0, 0.0)])
 @pytest.mark.parametrize("own_kv", [True, False])
