@@ -332,10 +332,15 @@ GB_API int gb_gemm_tc_set_tile(int bn) { g_tile_override = bn; return 0; }
 static int tile_for(int T, int N, int sms) {
     if (g_tile_override > 0) return g_tile_override;
     int bn = gb_gemm_tc_tile(T);
-    if (bn == 256 && 2LL * ((N + BM - 1) / BM) * ((T + 255) / 256) <= sms) bn = 128;
+    const long long ft = (N + BM - 1) / BM;
+    if (bn == 256 && 2 * ft * ((T + 255) / 256) <= sms) bn = 128;
     // a few dozen tokens and fewer feature tiles than SMs: two half-size token tiles give twice the units
     // without splitting K further (measured faster at 32 and 64 tokens; the second read of W hits L2)
-    if (bn > 16 && bn <= 64 && (N + BM - 1) / BM < sms) bn /= 2;
+    if (bn > 16 && bn <= 64 && ft < sms) bn /= 2;
+    // a few hundred tokens: tiles of 64 tokens, two CTAs per SM, as long as all of them fit the device at once
+    // (a CTA with a wide tile streams its operands no faster, and merging the K splits of a wide tile takes
+    // the last CTA long; measured at 128 to 768 tokens)
+    if (bn >= 128 && (T <= 128 || ft * ((T + 63) / 64) <= 2LL * sms)) bn = 64;
     return bn;
 }
 
@@ -353,7 +358,7 @@ GB_API int gb_gemm_tc_splits(int T, int N, int K, int sms) {
     }
     long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
     int kb = (K + BK - 1) / BK;
-    int slots = bn <= 32 ? 2 * sms : sms;          // CTAs that can be resident at once
+    int slots = bn <= 64 ? 2 * sms : sms;          // CTAs that can be resident at once
     if (tiles >= sms || kb < 8) return 1;
     int s = int(slots / tiles);
     if (s > kb / 4) s = kb / 4;       // at least 4 K blocks per split
