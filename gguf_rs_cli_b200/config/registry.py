@@ -53,14 +53,32 @@ def resolve_architecture(raw: Dict[str, Any]) -> Architecture:
     raise ConfigError(f"unsupported architecture {names}; registered: {registered_architectures()}")
 
 
+def _eos_ids(value) -> list:
+    return [] if value is None else [int(v) for v in value] if isinstance(value, (list, tuple)) else [int(value)]
+
+
 def read_config_json(path: str) -> Dict[str, Any]:
-    if os.path.isdir(path):
-        path = os.path.join(path, "config.json")
+    """config.json of a model folder (or the file itself).  A generation_config.json beside it adds its
+    eos_token_id to the model's stop tokens, as the reference joins the tokenizer's end tokens with the
+    chat template's (src/chat.rs:57-72)."""
+    folder = path if os.path.isdir(path) else None
+    raw = _read_json_object(os.path.join(path, "config.json") if folder else path)
+    extra = os.path.join(folder, "generation_config.json") if folder else None
+    if extra and os.path.exists(extra):
+        more = _eos_ids(_read_json_object(extra).get("eos_token_id"))
+        have = _eos_ids(raw.get("eos_token_id"))
+        ids = have + [i for i in more if i not in have]
+        if ids:
+            raw["eos_token_id"] = ids[0] if len(ids) == 1 else ids
+    return raw
+
+
+def _read_json_object(path: str) -> Dict[str, Any]:
     try:
         with open(path, "r") as f:
             raw = json.load(f)
     except FileNotFoundError:
-        raise ConfigError(f"no config.json at {path}") from None
+        raise ConfigError(f"no {os.path.basename(path) if path.endswith('.json') else 'config.json'} at {path}") from None
     except json.JSONDecodeError as e:
         raise ConfigError(f"{path}: not valid JSON ({e})") from None
     if not isinstance(raw, dict):

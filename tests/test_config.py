@@ -70,6 +70,21 @@ def test_config_json_round_trip(tmp_path):
         load_config(str(tmp_path / "nowhere"))
 
 
+def test_generation_config_adds_stop_tokens(tmp_path):
+    raw = config("A")                                          # eos_token_id 2
+    for extra, want in ((None, [2]), ({"eos_token_id": [2, 7, 9]}, [2, 7, 9]), ({"eos_token_id": 11}, [2, 11]), ({"top_p": 0.9}, [2])):
+        d = tmp_path / f"m{want[-1]}{len(want)}{extra is None}"
+        d.mkdir()
+        (d / "config.json").write_text(json.dumps(raw))
+        if extra is not None:
+            (d / "generation_config.json").write_text(json.dumps(extra))
+        arch, cfg = load_config(str(d))
+        assert cfg.eos_token_ids == want and arch.build_spec(cfg).stop_token_ids == want
+    (d / "generation_config.json").write_text("[1]")
+    with pytest.raises(ConfigError, match="generation_config.json"):
+        load_config(str(d))
+
+
 def test_spec_is_data_layer_by_layer():
     arch, cfg = load_config(config("A"))
     spec = arch.build_spec(cfg)
