@@ -4,10 +4,16 @@
 // largest survive, softmax over them, top_p keeps the smallest set of the most
 // probable whose mass reaches it, and one uniform picks a survivor.
 //
-// Differences from the reference, on purpose: nothing is sorted.  The k-th largest
-// value and the top_p cut are found as thresholds by bisection over the ordered bit
-// patterns of the floats, ties at a threshold go to the lower indices, and the
-// cumulative walk runs over the survivors in index order (the same distribution).
+// Differences from the reference, on purpose: the vocabulary is never sorted.  The k-th
+// largest value is found as a threshold over the ordered bit patterns of the floats (four
+// passes of eight bits with a histogram each), ties at a threshold go to the lower indices,
+// and the cumulative walk runs over the survivors in index order (the same distribution).
+// With a top_k of up to 1,024 the survivors are gathered into shared memory, and what
+// follows (top_p in descending order, the walk) runs on that list.  Without top_k the walk
+// goes over the whole vocabulary, each warp with a contiguous piece of it, and the edge of the
+// nucleus is found like the k-th largest value, with masses in the histogram (in fixed point,
+// so that their sums do not depend on the order).  A top_k above 1,024 finds its thresholds
+// by bisection, one bit a pass.
 // The uniform comes from a counter-based generator per sequence:
 // top 24 bits of splitmix64(seed + (n+1) * golden), n = number of tokens sampled so
 // far for that sequence; the reference's single global LCG divides a 31-bit value by
@@ -20,7 +26,9 @@
 #include "common.cuh"
 
 constexpr int SM_THREADS = 1024;
+constexpr int SM_WARPS = SM_THREADS / 32;
 constexpr int SM_RECENT = 64;
+constexpr int SM_LIST = 1024;            // survivors of top_k that are worked on in shared memory
 
 __device__ __forceinline__ unsigned ordered_key(float z) {
     unsigned u = __float_as_uint(z);
@@ -85,6 +93,262 @@ __device__ float block_exclusive_scan_f(float v, float* scratch, float* total) {
     return base + inc - v;
 }
 
+// Thresholds by bisection over the whole vocabulary, every thread with a contiguous range of it: any
+// combination of top_k and top_p, one pass over the logits per bit.
+__device__ int sample_by_bisection(const float* __restrict__ z, int V, float temperature, int top_k, float top_p, float bv,
+                                   int bi, float u, float* fs, int* is, int* best_i) {
+    const int tid = threadIdx.x;
+    float zmax = bv / temperature;
+    // contiguous index range of this thread, for everything that depends on index order
+    int chunk = (V + SM_THREADS - 1) / SM_THREADS;
+    int c0 = min(V, tid * chunk), c1 = min(V, c0 + chunk);
+
+    // 3. top_k: threshold key tk = the k-th largest; `k_eq` of the elements equal to it survive
+    unsigned tk = 0;
+    int k_eq = 0x7fffffff;
+    bool use_k = top_k > 0 && top_k < V;
+    if (use_k) {
+        for (int bit = 31; bit >= 0; --bit) {
+            unsigned cand = tk | (1u << bit);
+            int c = 0;
+            for (int i = tid; i < V; i += SM_THREADS) c += ordered_key(z[i] / temperature) >= cand;
+            if (block_sum<int>(c, is) >= top_k) tk = cand;
+        }
+        int c = 0;
+        for (int i = tid; i < V; i += SM_THREADS) c += ordered_key(z[i] / temperature) > tk;
+        k_eq = top_k - block_sum<int>(c, is);
+    }
+    // rank, in index order, of this thread's first element among those equal to tk
+    int eqk_before = 0;
+    if (use_k) {
+        int c = 0, tot;
+        for (int i = c0; i < c1; ++i) c += ordered_key(z[i] / temperature) == tk;
+        eqk_before = block_exclusive_scan(c, is, &tot);
+    }
+    // survivors of top_k: key > tk, or key == tk with rank < k_eq
+    // 4. their mass
+    float mass = 0.f;
+    {
+        int r = eqk_before;
+        for (int i = c0; i < c1; ++i) {
+            float zi = z[i] / temperature;
+            unsigned key = ordered_key(zi);
+            bool s = !use_k || key > tk || (key == tk && r < k_eq);
+            if (use_k && key == tk) ++r;
+            if (s) mass += expf(zi - zmax);
+        }
+    }
+    float Z = block_sum<float>(mass, fs);
+
+    // 5. top_p: threshold key tp = lowest value still inside the nucleus; p_eq of the equal ones survive
+    bool use_p = top_p < 1.0f;
+    unsigned tp = 0;
+    int p_eq = 0x7fffffff;
+    if (use_p) {
+        float goal = top_p * Z;
+        for (int bit = 31; bit >= 0; --bit) {
+            unsigned cand = tp | (1u << bit);
+            float msum = 0.f;
+            int r = eqk_before;
+            for (int i = c0; i < c1; ++i) {
+                float zi = z[i] / temperature;
+                unsigned key = ordered_key(zi);
+                bool s = !use_k || key > tk || (key == tk && r < k_eq);
+                if (use_k && key == tk) ++r;
+                if (s && key >= cand) msum += expf(zi - zmax);
+            }
+            if (block_sum<float>(msum, fs) >= goal) tp = cand;
+        }
+        float mgt = 0.f, e_eq = 0.f;
+        int r = eqk_before;
+        for (int i = c0; i < c1; ++i) {
+            float zi = z[i] / temperature;
+            unsigned key = ordered_key(zi);
+            bool s = !use_k || key > tk || (key == tk && r < k_eq);
+            if (use_k && key == tk) ++r;
+            if (s && key > tp) mgt += expf(zi - zmax);
+            if (s && key == tp) e_eq = expf(zi - zmax);
+        }
+        mgt = block_sum<float>(mgt, fs);
+        // every element equal to tp has the same weight; any thread that saw one knows it
+        float e_all = e_eq;
+        for (int o = 16; o > 0; o >>= 1) e_all = fmaxf(e_all, __shfl_xor_sync(0xffffffffu, e_all, o));
+        __syncthreads();
+        if ((tid & 31) == 0) fs[tid >> 5] = e_all;
+        __syncthreads();
+        e_all = 0.f;
+        for (int w = 0; w < SM_THREADS / 32; ++w) e_all = fmaxf(e_all, fs[w]);
+        __syncthreads();
+        // the smallest count c with mgt + c * e >= goal, accumulated as the reference does
+        int c = 1;
+        float cum = mgt + e_all;
+        while (cum < goal && c < V) { cum += e_all; ++c; }
+        p_eq = c;
+    }
+    // rank among elements equal to tp (same ranks as for tk when the thresholds coincide)
+    int eqp_before = 0;
+    if (use_p) {
+        int c = 0, tot;
+        for (int i = c0; i < c1; ++i) c += ordered_key(z[i] / temperature) == tp;
+        eqp_before = block_exclusive_scan(c, is, &tot);
+    }
+
+    // 6. mass of the final survivors, in index order, and the walk
+    float mine = 0.f;
+    {
+        int rk = eqk_before, rp = eqp_before;
+        for (int i = c0; i < c1; ++i) {
+            float zi = z[i] / temperature;
+            unsigned key = ordered_key(zi);
+            bool s = !use_k || key > tk || (key == tk && rk < k_eq);
+            if (use_p) s = s && (key > tp || (key == tp && rp < p_eq));
+            if (use_k && key == tk) ++rk;
+            if (use_p && key == tp) ++rp;
+            if (s) mine += expf(zi - zmax);
+        }
+    }
+    float Z2;
+    float before = block_exclusive_scan_f(mine, fs, &Z2);
+    float target = u * Z2;
+    __syncthreads();
+    // the last survivor overall is the fallback (src/sampler.rs:78); first the walk
+    int last_surv = -1, hit = -1;
+    {
+        int rk = eqk_before, rp = eqp_before;
+        float cum = before;
+        for (int i = c0; i < c1; ++i) {
+            float zi = z[i] / temperature;
+            unsigned key = ordered_key(zi);
+            bool s = !use_k || key > tk || (key == tk && rk < k_eq);
+            if (use_p) s = s && (key > tp || (key == tp && rp < p_eq));
+            if (use_k && key == tk) ++rk;
+            if (use_p && key == tp) ++rp;
+            if (s) {
+                cum += expf(zi - zmax);
+                last_surv = i;
+                if (hit < 0 && target < cum) hit = i;
+            }
+        }
+    }
+    // lowest hit over the block; else the highest survivor
+    int h = hit < 0 ? 0x7fffffff : hit;
+    for (int o = 16; o > 0; o >>= 1) h = min(h, __shfl_xor_sync(0xffffffffu, h, o));
+    int ls = last_surv;
+    for (int o = 16; o > 0; o >>= 1) ls = max(ls, __shfl_xor_sync(0xffffffffu, ls, o));
+    __syncthreads();
+    if ((tid & 31) == 0) { is[tid >> 5] = h; best_i[tid >> 5] = ls; }
+    __syncthreads();
+    h = 0x7fffffff; ls = -1;
+    for (int w = 0; w < SM_THREADS / 32; ++w) { h = min(h, is[w]); ls = max(ls, best_i[w]); }
+    return h != 0x7fffffff ? h : (ls >= 0 ? ls : bi);
+}
+
+// Calls f(index, value) for every logit of the row, the block's threads reading neighbouring elements (four
+// each where the row allows 16-byte loads).  The loads of a round (four a thread) are issued before any of
+// them is used: a pass over the row costs round trips to L2, not arithmetic.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* z, int V, F f) {
+    const int tid = threadIdx.x;
+    if ((reinterpret_cast<uintptr_t>(z) & 15) == 0) {
+        const float4* z4 = reinterpret_cast<const float4*>(z);
+        const int n4 = V >> 2;
+        for (int j0 = 0; j0 < n4; j0 += 4 * SM_THREADS) {
+            float4 v[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int j = j0 + r * SM_THREADS + tid;
+                v[r] = j < n4 ? z4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int j = j0 + r * SM_THREADS + tid;
+                if (j < n4) {
+                    f(4 * j, v[r].x);
+                    f(4 * j + 1, v[r].y);
+                    f(4 * j + 2, v[r].z);
+                    f(4 * j + 3, v[r].w);
+                }
+            }
+        }
+        for (int i = 4 * n4 + tid; i < V; i += SM_THREADS) f(i, z[i]);
+    } else {
+#pragma unroll 4
+        for (int i = tid; i < V; i += SM_THREADS) f(i, z[i]);
+    }
+}
+
+// The same with every thread of the block making the same number of calls (`valid` false beyond the row), for
+// callers whose f talks to the other lanes of its warp.
+template <typename F>
+__device__ __forceinline__ void for_each_logit_in_step(const float* z, int V, F f) {
+    const int tid = threadIdx.x;
+    if ((reinterpret_cast<uintptr_t>(z) & 15) == 0) {
+        const float4* z4 = reinterpret_cast<const float4*>(z);
+        const int n4 = V >> 2;
+        for (int j0 = 0; j0 < n4; j0 += 4 * SM_THREADS) {
+            float4 v[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int j = j0 + r * SM_THREADS + tid;
+                v[r] = j < n4 ? z4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const bool valid = j0 + r * SM_THREADS + tid < n4;
+                f(v[r].x, valid);
+                f(v[r].y, valid);
+                f(v[r].z, valid);
+                f(v[r].w, valid);
+            }
+        }
+        const int i = 4 * n4 + tid;                         // the up to three elements left over
+        f(i < V ? z[i] : 0.f, i < V);
+    } else {
+        for (int i0 = 0; i0 < V; i0 += 4 * SM_THREADS) {
+            float v[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) v[r] = i0 + r * SM_THREADS + tid < V ? z[i0 + r * SM_THREADS + tid] : 0.f;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) f(v[r], i0 + r * SM_THREADS + tid < V);
+        }
+    }
+}
+
+// A warp's piece [seg0, seg1) of the row, 512 elements a round: the sixteen loads of a round are issued
+// together, then f(index, value, inside) runs sixteen times on 32 neighbouring elements each, in index order
+// (every lane calls it, `inside` false beyond the piece).  f returns false to stop.
+template <typename F>
+__device__ __forceinline__ void for_each_in_piece(const float* z, int seg0, int seg1, int lane, F f) {
+    constexpr int R = 16;
+    bool go = true;
+    for (int base = seg0; base < seg1 && go; base += 32 * R) {
+        float v[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int i = base + 32 * q + lane;
+            v[q] = i < seg1 ? z[i] : 0.f;
+        }
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int i = base + 32 * q + lane;
+            if (go && base + 32 * q < seg1) go = f(i, v[q], i < seg1);
+        }
+    }
+}
+
+// exp(d), d <= 0, in 64-bit fixed point with 40 binary places: sums of these do not depend on their order.
+__device__ __forceinline__ unsigned long long fixed_mass(float d) { return __float2ull_rn(expf(d) * 1099511627776.0f); }
+
+// Inclusive sum over the lanes of a warp, in lane order.
+__device__ __forceinline__ float warp_inclusive(float v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        float n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+    }
+    return v;
+}
+
 __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ logits, long long ld, int V,
                                                             const int* __restrict__ slots,
                                                             const long long* __restrict__ seeds, float temperature,
@@ -96,16 +360,26 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     __shared__ int chosen;
+    __shared__ int hist[256];
+    __shared__ unsigned sel_prefix;
+    __shared__ int sel_need;
+    __shared__ int gt_s[SM_WARPS], eq_s[SM_WARPS];
+    __shared__ int list_idx[SM_LIST];
+    __shared__ float list_z[SM_LIST], list_e[SM_LIST], sorted_e[SM_LIST];
+    __shared__ short sorted_pos[SM_LIST];
+    __shared__ int cut_s;
+    __shared__ unsigned long long mh[256];
+    __shared__ unsigned long long sel_above, sel_goal;
     gb_grid_launch_dependents();
     gb_grid_wait();
-    int row = blockIdx.x, tid = threadIdx.x;
-    int slot = slots[row];
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int slot = slots[row];
     if (slot < 0) {
         if (tid == 0) out[row] = 0;
         return;
     }
     float* z = logits + size_t(row) * ld;
-    int n_before = count[slot];
+    const int n_before = count[slot];
 
     // 1. repetition penalty, once per occurrence in the ring (src/sampler.rs:23-30)
     if (rep_penalty != 1.0f && tid == 0) {
@@ -117,173 +391,385 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
     }
     __syncthreads();
 
-    // 2. the largest logit and its lowest index
+    // 2. the largest logit and its lowest index; with a temperature the row becomes logits / temperature on
+    // the way (src/sampler.rs:41), which every later pass reads
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = tid; i < V; i += SM_THREADS) {
-        float v = z[i];
-        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    if (temperature > 0.f && (reinterpret_cast<uintptr_t>(z) & 15) == 0) {
+        float4* z4 = reinterpret_cast<float4*>(z);
+        const int n4 = V >> 2;
+        for (int j0 = 0; j0 < n4; j0 += 4 * SM_THREADS) {
+            float4 v[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int j = j0 + r * SM_THREADS + tid;
+                v[r] = j < n4 ? z4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int j = j0 + r * SM_THREADS + tid;
+                if (j < n4) {
+                    const float e[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (e[q] > bv || (e[q] == bv && 4 * j + q < bi)) { bv = e[q]; bi = 4 * j + q; }
+                    z4[j] = make_float4(e[0] / temperature, e[1] / temperature, e[2] / temperature, e[3] / temperature);
+                }
+            }
+        }
+        for (int i = 4 * n4 + tid; i < V; i += SM_THREADS) {
+            const float v = z[i];
+            if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+            z[i] = v / temperature;
+        }
+    } else {
+        for_each_logit(z, V, [&](int i, float v) {
+            if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+            if (temperature > 0.f) z[i] = v / temperature;
+        });
     }
     for (int o = 16; o > 0; o >>= 1) {
         float ov = __shfl_xor_sync(0xffffffffu, bv, o);
         int oi = __shfl_xor_sync(0xffffffffu, bi, o);
         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
-    if ((tid & 31) == 0) { best_v[tid >> 5] = bv; best_i[tid >> 5] = bi; }
+    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
     __syncthreads();
     bv = best_v[0]; bi = best_i[0];
-    for (int w = 1; w < SM_THREADS / 32; ++w)
+    for (int w = 1; w < SM_WARPS; ++w)
         if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
 
     int pick = bi;
     if (temperature > 0.f) {
-        float zmax = bv / temperature;
-        // contiguous index range of this thread, for everything that depends on index order
-        int chunk = (V + SM_THREADS - 1) / SM_THREADS;
-        int c0 = min(V, tid * chunk), c1 = min(V, c0 + chunk);
-
-        // 3. top_k: threshold key tk = the k-th largest; `k_eq` of the elements equal to it survive
-        unsigned tk = 0;
-        int k_eq = 0x7fffffff;
-        bool use_k = top_k > 0 && top_k < V;
-        if (use_k) {
-            for (int bit = 31; bit >= 0; --bit) {
-                unsigned cand = tk | (1u << bit);
-                int c = 0;
-                for (int i = tid; i < V; i += SM_THREADS) c += ordered_key(z[i] / temperature) >= cand;
-                if (block_sum<int>(c, is) >= top_k) tk = cand;
-            }
-            int c = 0;
-            for (int i = tid; i < V; i += SM_THREADS) c += ordered_key(z[i] / temperature) > tk;
-            k_eq = top_k - block_sum<int>(c, is);
-        }
-        // rank, in index order, of this thread's first element among those equal to tk
-        int eqk_before = 0;
-        if (use_k) {
-            int c = 0, tot;
-            for (int i = c0; i < c1; ++i) c += ordered_key(z[i] / temperature) == tk;
-            eqk_before = block_exclusive_scan(c, is, &tot);
-        }
-        // survivors of top_k: key > tk, or key == tk with rank < k_eq
-        // 4. their mass
-        float mass = 0.f;
-        {
-            int r = eqk_before;
-            for (int i = c0; i < c1; ++i) {
-                float zi = z[i] / temperature;
-                unsigned key = ordered_key(zi);
-                bool s = !use_k || key > tk || (key == tk && r < k_eq);
-                if (use_k && key == tk) ++r;
-                if (s) mass += expf(zi - zmax);
-            }
-        }
-        float Z = block_sum<float>(mass, fs);
-
-        // 5. top_p: threshold key tp = lowest value still inside the nucleus; p_eq of the equal ones survive
-        bool use_p = top_p < 1.0f;
-        unsigned tp = 0;
-        int p_eq = 0x7fffffff;
-        if (use_p) {
-            float goal = top_p * Z;
-            for (int bit = 31; bit >= 0; --bit) {
-                unsigned cand = tp | (1u << bit);
-                float msum = 0.f;
-                int r = eqk_before;
-                for (int i = c0; i < c1; ++i) {
-                    float zi = z[i] / temperature;
-                    unsigned key = ordered_key(zi);
-                    bool s = !use_k || key > tk || (key == tk && r < k_eq);
-                    if (use_k && key == tk) ++r;
-                    if (s && key >= cand) msum += expf(zi - zmax);
-                }
-                if (block_sum<float>(msum, fs) >= goal) tp = cand;
-            }
-            float mgt = 0.f, e_eq = 0.f;
-            int r = eqk_before;
-            for (int i = c0; i < c1; ++i) {
-                float zi = z[i] / temperature;
-                unsigned key = ordered_key(zi);
-                bool s = !use_k || key > tk || (key == tk && r < k_eq);
-                if (use_k && key == tk) ++r;
-                if (s && key > tp) mgt += expf(zi - zmax);
-                if (s && key == tp) e_eq = expf(zi - zmax);
-            }
-            mgt = block_sum<float>(mgt, fs);
-            // every element equal to tp has the same weight; any thread that saw one knows it
-            float e_all = e_eq;
-            for (int o = 16; o > 0; o >>= 1) e_all = fmaxf(e_all, __shfl_xor_sync(0xffffffffu, e_all, o));
-            __syncthreads();
-            if ((tid & 31) == 0) fs[tid >> 5] = e_all;
-            __syncthreads();
-            e_all = 0.f;
-            for (int w = 0; w < SM_THREADS / 32; ++w) e_all = fmaxf(e_all, fs[w]);
-            __syncthreads();
-            // the smallest count c with mgt + c * e >= goal, accumulated as the reference does
-            int c = 1;
-            float cum = mgt + e_all;
-            while (cum < goal && c < V) { cum += e_all; ++c; }
-            p_eq = c;
-        }
-        // rank among elements equal to tp (same ranks as for tk when the thresholds coincide)
-        int eqp_before = 0;
-        if (use_p) {
-            int c = 0, tot;
-            for (int i = c0; i < c1; ++i) c += ordered_key(z[i] / temperature) == tp;
-            eqp_before = block_exclusive_scan(c, is, &tot);
-        }
-
-        // 6. mass of the final survivors, in index order, and the walk
-        float mine = 0.f;
-        {
-            int rk = eqk_before, rp = eqp_before;
-            for (int i = c0; i < c1; ++i) {
-                float zi = z[i] / temperature;
-                unsigned key = ordered_key(zi);
-                bool s = !use_k || key > tk || (key == tk && rk < k_eq);
-                if (use_p) s = s && (key > tp || (key == tp && rp < p_eq));
-                if (use_k && key == tk) ++rk;
-                if (use_p && key == tp) ++rp;
-                if (s) mine += expf(zi - zmax);
-            }
-        }
-        float Z2;
-        float before = block_exclusive_scan_f(mine, fs, &Z2);
-        unsigned long long st = splitmix64((unsigned long long)seeds[row] +
-                                           (unsigned long long)(n_before + 1) * 0x9E3779B97F4A7C15ull);
-        float u = float(st >> 40) * (1.0f / 16777216.0f);
-        float target = u * Z2;
+        const unsigned long long st = splitmix64((unsigned long long)seeds[row] +
+                                                 (unsigned long long)(n_before + 1) * 0x9E3779B97F4A7C15ull);
+        const float u = float(st >> 40) * (1.0f / 16777216.0f);
+        const float zmax = bv / temperature;
+        const bool use_k = top_k > 0 && top_k < V, use_p = top_p < 1.0f;
+        // every warp's contiguous piece of the vocabulary (a multiple of 32 long), read 32 elements at a time
+        const int seg = ((V + SM_WARPS - 1) / SM_WARPS + 31) / 32 * 32;
+        const int seg0 = min(V, warp * seg), seg1 = min(V, seg0 + seg);
         if (tid == 0) chosen = -1;
-        __syncthreads();
-        // the last survivor overall is the fallback (src/sampler.rs:78); first the walk
-        int last_surv = -1, hit = -1;
-        {
-            int rk = eqk_before, rp = eqp_before;
-            float cum = before;
-            for (int i = c0; i < c1; ++i) {
-                float zi = z[i] / temperature;
-                unsigned key = ordered_key(zi);
-                bool s = !use_k || key > tk || (key == tk && rk < k_eq);
-                if (use_p) s = s && (key > tp || (key == tp && rp < p_eq));
-                if (use_k && key == tk) ++rk;
-                if (use_p && key == tp) ++rp;
-                if (s) {
-                    cum += expf(zi - zmax);
-                    last_surv = i;
-                    if (hit < 0 && target < cum) hit = i;
+
+        if (use_k && top_k <= SM_LIST) {
+            // 3. the k-th largest key, eight bits a pass: among the elements whose higher bits equal the prefix
+            // found so far, count by the next eight bits and take the bin in which the count from above reaches
+            // what is still needed.
+            unsigned prefix = 0;
+            int need = top_k;
+            // Nothing lies above the bin of the largest value: where that bin alone holds top_k elements (the usual
+            // case) the first pass is a count of it, without a histogram.
+            int first_pass = 0;
+            {
+                const unsigned top_bin = ordered_key(zmax) >> 24;
+                int c = 0;
+                for_each_logit(z, V, [&](int, float v) { c += (ordered_key(v) >> 24) == top_bin; });
+                if (block_sum<int>(c, is) >= top_k) {
+                    prefix = top_bin << 24;
+                    first_pass = 1;
                 }
             }
+            for (int pass = first_pass; pass < 4; ++pass) {
+                const int shift = 24 - 8 * pass;
+                if (tid < 256) hist[tid] = 0;
+                __syncthreads();
+                for_each_logit_in_step(z, V, [&](float v, bool valid) {
+                    const unsigned key = ordered_key(v);
+                    const bool in = valid && (pass == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8)));
+                    if (__ballot_sync(0xffffffffu, in) == 0) return;       // after the first pass few elements are left
+                    const int bin = in ? int((key >> shift) & 255u) : -1;
+                    // the lanes of a warp that hit the same bin add to it once (most logits share their high bits)
+                    const unsigned same = __match_any_sync(0xffffffffu, bin);
+                    if (in && lane == __ffs(same) - 1) atomicAdd(&hist[bin], __popc(same));
+                });
+                __syncthreads();
+                if (tid == 0) {
+                    int above = 0, b = 255;
+                    for (; b > 0; --b) {
+                        if (above + hist[b] >= need) break;
+                        above += hist[b];
+                    }
+                    sel_prefix = prefix | (unsigned(b) << shift);
+                    sel_need = need - above;
+                }
+                __syncthreads();
+                prefix = sel_prefix;
+                need = sel_need;
+            }
+            const unsigned tk = prefix;
+            const int k_eq = need;                       // of the elements equal to tk, the first k_eq (by index) survive
+            // 4. the survivors, in index order, into shared memory: per warp the number above tk and equal to it ...
+            {
+                int gt = 0, eq = 0;
+                for_each_in_piece(z, seg0, seg1, lane, [&](int, float v, bool inside) {
+                    const unsigned key = ordered_key(v);
+                    gt += (inside && key > tk);
+                    eq += (inside && key == tk);
+                    return true;
+                });
+                for (int o = 16; o > 0; o >>= 1) {
+                    gt += __shfl_xor_sync(0xffffffffu, gt, o);
+                    eq += __shfl_xor_sync(0xffffffffu, eq, o);
+                }
+                if (lane == 0) { gt_s[warp] = gt; eq_s[warp] = eq; }
+            }
+            __syncthreads();
+            int eq_before = 0, write_at = 0;
+            for (int w = 0; w < warp; ++w) {
+                write_at += gt_s[w] + max(0, min(eq_s[w], k_eq - eq_before));
+                eq_before += eq_s[w];
+            }
+            // ... then every warp writes its own at its place
+            for_each_in_piece(z, seg0, seg1, lane, [&](int i, float v, bool inside) {
+                const float zi = v;
+                const unsigned key = ordered_key(zi);
+                const bool is_eq = inside && key == tk;
+                const unsigned eq_mask = __ballot_sync(0xffffffffu, is_eq);
+                const unsigned below = (1u << lane) - 1u;
+                const bool surv = inside && (key > tk || (is_eq && eq_before + __popc(eq_mask & below) < k_eq));
+                const unsigned s_mask = __ballot_sync(0xffffffffu, surv);
+                if (surv) {
+                    const int at = write_at + __popc(s_mask & below);
+                    list_idx[at] = i;
+                    list_z[at] = zi;
+                }
+                write_at += __popc(s_mask);
+                eq_before += __popc(eq_mask);
+                return true;
+            });
+            __syncthreads();
+            const int n = top_k;                         // exactly top_k survive
+            // 5. the list in descending order (equal values: lower index first): every element counts those before it
+            if (tid < n) {
+                const float zj = list_z[tid];
+                const unsigned kj = ordered_key(zj);
+                const float e = expf(zj - zmax);
+                list_e[tid] = e;
+                int rank = 0;
+                for (int i = 0; i < n; ++i) {
+                    const unsigned ki = ordered_key(list_z[i]);
+                    rank += (ki > kj) || (ki == kj && i < tid);
+                }
+                sorted_e[rank] = e;
+                sorted_pos[rank] = short(tid);
+            }
+            __syncthreads();
+            // 6. top_p: the shortest prefix in that order whose mass reaches top_p of the whole (src/sampler.rs:59-69)
+            if (tid == 0) {
+                int cut = n;
+                if (use_p) {
+                    float Z = 0.f;
+                    for (int r = 0; r < n; ++r) Z += sorted_e[r];
+                    const float goal = top_p * Z;
+                    float cum = 0.f;
+                    for (int r = 0; r < n; ++r) {
+                        cum += sorted_e[r];
+                        if (cum >= goal) { cut = r + 1; break; }
+                    }
+                }
+                cut_s = cut;
+            }
+            __syncthreads();
+            if (tid < cut_s) list_idx[sorted_pos[tid]] |= 0x40000000;      // marks the kept ones (indices are below 2^30)
+            __syncthreads();
+            // 7. the walk over the kept ones in index order
+            if (tid == 0) {
+                float Z2 = 0.f;
+                for (int j = 0; j < n; ++j)
+                    if (list_idx[j] & 0x40000000) Z2 += list_e[j];
+                const float target = u * Z2;
+                float cum = 0.f;
+                int hit = -1, last = -1;
+                for (int j = 0; j < n; ++j) {
+                    if (!(list_idx[j] & 0x40000000)) continue;
+                    cum += list_e[j];
+                    last = j;
+                    if (target < cum) { hit = j; break; }
+                }
+                if (hit < 0) hit = last;                    // the last survivor (src/sampler.rs:78)
+                chosen = hit >= 0 ? (list_idx[hit] & 0x3fffffff) : bi;
+            }
+            __syncthreads();
+            pick = chosen;
+        } else if (!use_k && !use_p) {
+            // The whole vocabulary survives.  3. every warp's mass: each lane sums its own elements of the piece,
+            // then the lanes in order ...
+            auto mass_of = [&](int a, int b) {
+                float acc = 0.f;
+                for_each_in_piece(z, a, b, lane, [&](int, float v, bool inside) {
+                    acc += inside ? expf(v - zmax) : 0.f;
+                    return true;
+                });
+                return __shfl_sync(0xffffffffu, warp_inclusive(acc, lane), 31);
+            };
+            // ... and which of 32 masses (in order, after `before`) holds the target
+            auto holder_of = [&](const float* m, float target, float& before) {
+                int sel = -1;
+                float runsum = before;
+                for (int w = 0; w < SM_WARPS; ++w) {
+                    if (sel < 0 && target < runsum + m[w]) { sel = w; before = runsum; }
+                    runsum += m[w];
+                }
+                return sel;
+            };
+            const float tot = mass_of(seg0, seg1);
+            if (lane == 0) fs[warp] = tot;
+            __syncthreads();
+            float Z2 = 0.f;
+            for (int w = 0; w < SM_WARPS; ++w) Z2 += fs[w];
+            const float target = u * Z2;
+            float before = 0.f;
+            const int wsel = holder_of(fs, target, before);
+            // 4. the piece that holds the target again, every warp with a part of it ...
+            const int p0 = wsel < 0 ? V : min(V, wsel * seg), p1 = min(V, p0 + seg);
+            const int part = ((p1 - p0 + SM_WARPS - 1) / SM_WARPS + 31) / 32 * 32;
+            const int q0 = min(p1, p0 + warp * part), q1 = min(p1, q0 + part);
+            const float tot2 = mass_of(q0, q1);
+            if (lane == 0) best_v[warp] = tot2;
+            __syncthreads();
+            const int vsel = wsel < 0 ? -1 : holder_of(best_v, target, before);
+            // ... 5. and the warp whose part holds it walks that part, 32 elements at a time in index order
+            if (warp == vsel) {
+                float c = before;
+                int hit = -1;
+                for_each_in_piece(z, q0, q1, lane, [&](int i, float v, bool inside) {
+                    const float inc = warp_inclusive(inside ? expf(v - zmax) : 0.f, lane);
+                    const unsigned mask = __ballot_sync(0xffffffffu, inside && target < c + inc);
+                    if (mask) hit = i - lane + __ffs(mask) - 1;
+                    c += __shfl_sync(0xffffffffu, inc, 31);
+                    return mask == 0;
+                });
+                if (hit < 0) hit = q1 - 1;                  // rounding left the target just beyond the part's last element
+                if (lane == 0) chosen = hit;
+            }
+            __syncthreads();
+            // a target at or beyond a whole mass (rounding): the last element of what was searched
+            pick = chosen >= 0 ? chosen : (wsel >= 0 ? p1 - 1 : V - 1);
+        } else if (!use_k) {
+            // The whole vocabulary is in play.  3. top_p: the lowest key still inside the nucleus, eight bits a
+            // pass as above, but the histogram holds masses; they are summed as 64-bit fixed point (2^-40 of the
+            // largest weight), so that a sum does not depend on the order of its terms.
+            unsigned tp = 0;
+            int p_eq = 0x7fffffff;                       // of the elements equal to tp, the first p_eq (by index) survive
+            if (use_p) {
+                unsigned prefix = 0;
+                unsigned long long above = 0, goal = 0;
+                for (int pass = 0; pass < 4; ++pass) {
+                    const int shift = 24 - 8 * pass;
+                    if (tid < 256) mh[tid] = 0;
+                    __syncthreads();
+                    for_each_logit_in_step(z, V, [&](float v, bool valid) {
+                        const unsigned key = ordered_key(v);
+                        const bool in = valid && (pass == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8)));
+                        if (__ballot_sync(0xffffffffu, in) == 0) return;
+                        const int bin = in ? int((key >> shift) & 255u) : -1;
+                        const unsigned long long m = in ? fixed_mass(v - zmax) : 0ull;
+                        // the lanes of a warp that hit the same bin add their masses (41 bits at most, as two halves) once
+                        const unsigned same = __match_any_sync(0xffffffffu, bin);
+                        const unsigned lo = __reduce_add_sync(same, unsigned(m & 0xfffffu));
+                        const unsigned hi = __reduce_add_sync(same, unsigned(m >> 20));
+                        if (in && lane == __ffs(same) - 1) atomicAdd(&mh[bin], ((unsigned long long)hi << 20) + lo);
+                    });
+                    __syncthreads();
+                    if (tid == 0) {
+                        if (pass == 0) {
+                            unsigned long long Z = 0;
+                            for (int b = 0; b < 256; ++b) Z += mh[b];
+                            goal = (unsigned long long)(double(top_p) * double(Z));
+                            if (goal == 0) goal = 1;
+                            sel_goal = goal;
+                        }
+                        int b = 255;
+                        for (; b > 0; --b) {
+                            if (above + mh[b] >= goal) break;
+                            above += mh[b];
+                        }
+                        sel_prefix = prefix | (unsigned(b) << shift);
+                        sel_above = above;
+                    }
+                    __syncthreads();
+                    prefix = sel_prefix;
+                    above = sel_above;
+                    goal = sel_goal;
+                }
+                tp = prefix;
+                // every element equal to tp weighs the same: the fewest of them that reach the goal
+                const unsigned bits = (tp & 0x80000000u) ? (tp & 0x7fffffffu) : ~tp;
+                const unsigned long long e_eq = fixed_mass(__uint_as_float(bits) - zmax);
+                if (e_eq > 0 && goal > above) {
+                    const unsigned long long c = (goal - above + e_eq - 1) / e_eq;
+                    p_eq = c > 0x7ffffffeull ? 0x7fffffff : int(c);
+                }
+                if (p_eq < 1) p_eq = 1;
+            }
+            // 4. rank among the elements equal to tp, in index order: per warp how many its piece holds
+            int eq_before = 0;
+            if (use_p) {
+                int eq = 0;
+                for_each_in_piece(z, seg0, seg1, lane, [&](int, float v, bool inside) {
+                    eq += (inside && ordered_key(v) == tp);
+                    return true;
+                });
+                for (int o = 16; o > 0; o >>= 1) eq += __shfl_xor_sync(0xffffffffu, eq, o);
+                if (lane == 0) eq_s[warp] = eq;
+                __syncthreads();
+                for (int w = 0; w < warp; ++w) eq_before += eq_s[w];
+            }
+            const unsigned below = (1u << lane) - 1u;
+            // 5. every warp's mass of survivors, 32 elements at a time in index order, and its last survivor ...
+            float cum = 0.f;
+            int last = -1, eq_seen = eq_before;
+            for_each_in_piece(z, seg0, seg1, lane, [&](int i, float v, bool inside) {
+                const float zi = v;
+                const unsigned key = ordered_key(zi);
+                const unsigned eq_mask = __ballot_sync(0xffffffffu, inside && use_p && key == tp);
+                const bool surv = inside && (!use_p || key > tp || (key == tp && eq_seen + __popc(eq_mask & below) < p_eq));
+                eq_seen += __popc(eq_mask);
+                const float m = surv ? expf(zi - zmax) : 0.f;
+                cum += __shfl_sync(0xffffffffu, warp_inclusive(m, lane), 31);
+                const unsigned s_mask = __ballot_sync(0xffffffffu, surv);
+                if (s_mask) last = i - lane + 31 - __clz(s_mask);
+                return true;
+            });
+            if (lane == 0) { fs[warp] = cum; is[warp] = last; }
+            __syncthreads();
+            // ... 6. the warp in whose piece the target falls ...
+            float Z2 = 0.f;
+            int last_all = -1;
+            for (int w = 0; w < SM_WARPS; ++w) { Z2 += fs[w]; last_all = max(last_all, is[w]); }
+            const float target = u * Z2;
+            int wsel = -1;
+            float before = 0.f, runsum = 0.f;
+            for (int w = 0; w < SM_WARPS; ++w) {
+                if (wsel < 0 && target < runsum + fs[w]) { wsel = w; before = runsum; }
+                runsum += fs[w];
+            }
+            // ... 7. and that warp walks its piece again
+            if (warp == wsel) {
+                float c = before;
+                int hit = -1;
+                eq_seen = eq_before;
+                for_each_in_piece(z, seg0, seg1, lane, [&](int i, float v, bool inside) {
+                    const float zi = v;
+                    const unsigned key = ordered_key(zi);
+                    const unsigned eq_mask = __ballot_sync(0xffffffffu, inside && use_p && key == tp);
+                    const bool surv = inside && (!use_p || key > tp || (key == tp && eq_seen + __popc(eq_mask & below) < p_eq));
+                    eq_seen += __popc(eq_mask);
+                    const float m = surv ? expf(zi - zmax) : 0.f;
+                    const float inc = warp_inclusive(m, lane);
+                    const unsigned mask = __ballot_sync(0xffffffffu, surv && target < c + inc);
+                    if (mask) hit = i - lane + __ffs(mask) - 1;
+                    c += __shfl_sync(0xffffffffu, inc, 31);
+                    return mask == 0;
+                });
+                if (hit < 0) hit = last;                    // rounding left the target just beyond the piece's last survivor
+                if (lane == 0) chosen = hit;
+            }
+            __syncthreads();
+            pick = chosen >= 0 ? chosen : (last_all >= 0 ? last_all : bi);   // target at or beyond the whole mass: the last survivor
+        } else {
+            pick = sample_by_bisection(z, V, 1.0f, top_k, top_p, zmax, bi, u, fs, is, best_i);   // the row is scaled already
         }
-        // lowest hit over the block; else the highest survivor
-        int h = hit < 0 ? 0x7fffffff : hit;
-        for (int o = 16; o > 0; o >>= 1) h = min(h, __shfl_xor_sync(0xffffffffu, h, o));
-        int ls = last_surv;
-        for (int o = 16; o > 0; o >>= 1) ls = max(ls, __shfl_xor_sync(0xffffffffu, ls, o));
-        __syncthreads();
-        if ((tid & 31) == 0) { is[tid >> 5] = h; best_i[tid >> 5] = ls; }
-        __syncthreads();
-        h = 0x7fffffff; ls = -1;
-        for (int w = 0; w < SM_THREADS / 32; ++w) { h = min(h, is[w]); ls = max(ls, best_i[w]); }
-        pick = h != 0x7fffffff ? h : (ls >= 0 ? ls : bi);
     }
     if (tid == 0) {
         out[row] = pick;
@@ -292,7 +778,8 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
     }
 }
 
-// logits: [n, V] 32-bit, rows ld apart; the penalty is applied to them in place.
+// logits: [n, V] 32-bit, rows ld apart; the penalty is applied to them in place, and with a temperature they
+// are left divided by it.
 // slots[row] < 0 marks padding.  recent: [slots, 64]; count: [slots].
 GB_API int gb_sample(float* logits, long long ld, int n, int V, const int* slots, const long long* seeds,
                      float temperature, int top_k, float top_p, float rep_penalty, int* recent, int* count, int* out,

@@ -107,8 +107,9 @@ def gemm_generic(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
 
 def sample(logits: torch.Tensor, slots: torch.Tensor, seeds: torch.Tensor, temperature: float, top_k: int,
            top_p: float, rep_penalty: float, recent: torch.Tensor, count: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """One token per row of float32 logits [n, V]; the repetition penalty changes the logits
-    in place.  recent [slots, 64] and count [slots] are the sequences' own state."""
+    """One token per row of float32 logits [n, V].  The logits are the kernel's scratch: the repetition
+    penalty is applied to them in place, and with a temperature they are left divided by it.
+    recent [slots, 64] and count [slots] are the sequences' own state."""
     _cuda(logits, slots, seeds, recent, count, out)
     n, V = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and seeds.dtype == torch.int64
