@@ -1,4 +1,4 @@
-// Sampling on the device, one block per sequence, in the order of the reference's
+// Sampling on the device, a cluster of up to eight CTAs per sequence, in the order of the reference's
 // sampler (src/sampler.rs:35-79): repetition penalty on recently emitted tokens;
 // temperature <= 0 takes the largest logit; else logits / temperature, the top_k
 // largest survive, softmax over them, top_p keeps the smallest set of the most
@@ -349,6 +349,67 @@ __device__ __forceinline__ float warp_inclusive(float v, int lane) {
     return v;
 }
 
+// ------------------------------------------------------ a cluster of CTAs per sequence
+// The CTAs of a cluster share one row: each takes a contiguous part of it (a multiple of 128 logits), and what
+// they have to tell each other (largest values, histograms, counts, masses) they read from each other's shared
+// memory after a cluster barrier.  A cluster of one CTA is the plain case.
+constexpr int SM_MAX_CLUSTER = 8;
+
+__device__ __forceinline__ unsigned cl_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ unsigned cl_size() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+// Every thread of every CTA of the cluster executes this; what was written before it, to shared or to global
+// memory, is visible to all of them after it.
+__device__ __forceinline__ void cl_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address that CTA `rank` of the cluster has for what this CTA calls p (a __shared__ variable).
+__device__ __forceinline__ unsigned cl_addr(const void* p, unsigned rank) {
+    unsigned a = unsigned(__cvta_generic_to_shared(p)), r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ int cl_load(const int* p, unsigned rank) {
+    int v;
+    asm volatile("ld.shared::cluster.b32 %0, [%1];" : "=r"(v) : "r"(cl_addr(p, rank)) : "memory");
+    return v;
+}
+__device__ __forceinline__ float cl_load(const float* p, unsigned rank) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cl_addr(p, rank)) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long cl_load(const unsigned long long* p, unsigned rank) {
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.b64 %0, [%1];" : "=l"(v) : "r"(cl_addr(p, rank)) : "memory");
+    return v;
+}
+__device__ __forceinline__ void cl_store(int* p, unsigned rank, int v) {
+    asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(cl_addr(p, rank)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void cl_store(float* p, unsigned rank, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cl_addr(p, rank)), "f"(v) : "memory");
+}
+
+// Which of n masses (in order, after `before`) holds the target; `before` becomes the mass in front of it.
+__device__ __forceinline__ int holder_of(const float* m, int n, float target, float& before) {
+    int sel = -1;
+    float runsum = before;
+    for (int w = 0; w < n; ++w) {
+        if (sel < 0 && target < runsum + m[w]) { sel = w; before = runsum; }
+        runsum += m[w];
+    }
+    return sel;
+}
+
 __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ logits, long long ld, int V,
                                                             const int* __restrict__ slots,
                                                             const long long* __restrict__ seeds, float temperature,
@@ -359,8 +420,11 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
     __shared__ int is[32];
     __shared__ float best_v[32];
     __shared__ int best_i[32];
+    __shared__ float am_v;                                 // this CTA's largest value and its index, for the others
+    __shared__ int am_i;
+    __shared__ int cnt_s, tot_gt, tot_eq;                  // counts of this CTA, for the others
     __shared__ int chosen;
-    __shared__ int hist[256];
+    __shared__ int hist[2][256], hist_all[256];
     __shared__ unsigned sel_prefix;
     __shared__ int sel_need;
     __shared__ int gt_s[SM_WARPS], eq_s[SM_WARPS];
@@ -368,25 +432,32 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
     __shared__ float list_z[SM_LIST], list_e[SM_LIST], sorted_e[SM_LIST];
     __shared__ short sorted_pos[SM_LIST];
     __shared__ int cut_s;
-    __shared__ unsigned long long mh[256];
+    __shared__ unsigned long long mh[2][256], mh_all[256];
     __shared__ unsigned long long sel_above, sel_goal;
+    __shared__ float all_m[SM_MAX_CLUSTER * SM_WARPS];     // every warp's mass, of every CTA
+    __shared__ int all_last[SM_MAX_CLUSTER * SM_WARPS];
     gb_grid_launch_dependents();
     gb_grid_wait();
-    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned rank = cl_rank(), C = cl_size();
+    const int row = blockIdx.x / int(C), tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int slot = slots[row];
-    if (slot < 0) {
-        if (tid == 0) out[row] = 0;
+    if (slot < 0) {                                        // the whole cluster leaves
+        if (rank == 0 && tid == 0) out[row] = 0;
         return;
     }
-    float* z = logits + size_t(row) * ld;
+    float* zrow = logits + size_t(row) * ld;
+    // this CTA's part [lo, hi) of the row; z[i] is logit lo + i
+    const int part = ((V + int(C) - 1) / int(C) + 127) / 128 * 128;
+    const int lo = min(V, int(rank) * part), hi = min(V, lo + part), n = hi - lo;
+    float* z = zrow + lo;
     const int n_before = count[slot];
 
-    // 1. repetition penalty, once per occurrence in the ring (src/sampler.rs:23-30)
+    // 1. repetition penalty, once per occurrence in the ring (src/sampler.rs:23-30), on the tokens of this part
     if (rep_penalty != 1.0f && tid == 0) {
-        int n = min(n_before, SM_RECENT);
-        for (int i = 0; i < n; ++i) {
-            int tok = recent[size_t(slot) * SM_RECENT + i];
-            if (tok >= 0 && tok < V) z[tok] = z[tok] > 0.f ? z[tok] / rep_penalty : z[tok] * rep_penalty;
+        const int m = min(n_before, SM_RECENT);
+        for (int i = 0; i < m; ++i) {
+            const int tok = recent[size_t(slot) * SM_RECENT + i];
+            if (tok >= lo && tok < hi) zrow[tok] = zrow[tok] > 0.f ? zrow[tok] / rep_penalty : zrow[tok] * rep_penalty;
         }
     }
     __syncthreads();
@@ -397,7 +468,7 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
     int bi = 0x7fffffff;
     if (temperature > 0.f && (reinterpret_cast<uintptr_t>(z) & 15) == 0) {
         float4* z4 = reinterpret_cast<float4*>(z);
-        const int n4 = V >> 2;
+        const int n4 = n >> 2;
         for (int j0 = 0; j0 < n4; j0 += 4 * SM_THREADS) {
             float4 v[4];
 #pragma unroll
@@ -412,19 +483,19 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
                     const float e[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
-                        if (e[q] > bv || (e[q] == bv && 4 * j + q < bi)) { bv = e[q]; bi = 4 * j + q; }
+                        if (e[q] > bv || (e[q] == bv && lo + 4 * j + q < bi)) { bv = e[q]; bi = lo + 4 * j + q; }
                     z4[j] = make_float4(e[0] / temperature, e[1] / temperature, e[2] / temperature, e[3] / temperature);
                 }
             }
         }
-        for (int i = 4 * n4 + tid; i < V; i += SM_THREADS) {
+        for (int i = 4 * n4 + tid; i < n; i += SM_THREADS) {
             const float v = z[i];
-            if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+            if (v > bv || (v == bv && lo + i < bi)) { bv = v; bi = lo + i; }
             z[i] = v / temperature;
         }
     } else {
-        for_each_logit(z, V, [&](int i, float v) {
-            if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+        for_each_logit(z, n, [&](int i, float v) {
+            if (v > bv || (v == bv && lo + i < bi)) { bv = v; bi = lo + i; }
             if (temperature > 0.f) z[i] = v / temperature;
         });
     }
@@ -435,21 +506,35 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
     }
     if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
     __syncthreads();
-    bv = best_v[0]; bi = best_i[0];
-    for (int w = 1; w < SM_WARPS; ++w)
-        if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
+    if (tid == 0) {
+        bv = best_v[0]; bi = best_i[0];
+        for (int w = 1; w < SM_WARPS; ++w)
+            if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
+        am_v = bv;
+        am_i = bi;
+        chosen = -1;
+    }
+    cl_sync();
+    bv = -INFINITY;
+    bi = 0x7fffffff;
+    for (unsigned r = 0; r < C; ++r) {
+        const float ov = cl_load(&am_v, r);
+        const int oi = cl_load(&am_i, r);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
 
     int pick = bi;
+    bool writer = rank == 0;                               // the CTA that gives the result out
     if (temperature > 0.f) {
         const unsigned long long st = splitmix64((unsigned long long)seeds[row] +
                                                  (unsigned long long)(n_before + 1) * 0x9E3779B97F4A7C15ull);
         const float u = float(st >> 40) * (1.0f / 16777216.0f);
         const float zmax = bv / temperature;
         const bool use_k = top_k > 0 && top_k < V, use_p = top_p < 1.0f;
-        // every warp's contiguous piece of the vocabulary (a multiple of 32 long), read 32 elements at a time
-        const int seg = ((V + SM_WARPS - 1) / SM_WARPS + 31) / 32 * 32;
-        const int seg0 = min(V, warp * seg), seg1 = min(V, seg0 + seg);
-        if (tid == 0) chosen = -1;
+        // every warp's contiguous piece of the part (a multiple of 32 long), read 32 elements at a time
+        const int seg = ((n + SM_WARPS - 1) / SM_WARPS + 31) / 32 * 32;
+        const int seg0 = min(n, warp * seg), seg1 = min(n, seg0 + seg);
+        const unsigned below = (1u << lane) - 1u;
 
         if (use_k && top_k <= SM_LIST) {
             // 3. the k-th largest key, eight bits a pass: among the elements whose higher bits equal the prefix
@@ -463,31 +548,43 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
             {
                 const unsigned top_bin = ordered_key(zmax) >> 24;
                 int c = 0;
-                for_each_logit(z, V, [&](int, float v) { c += (ordered_key(v) >> 24) == top_bin; });
-                if (block_sum<int>(c, is) >= top_k) {
+                for_each_logit(z, n, [&](int, float v) { c += (ordered_key(v) >> 24) == top_bin; });
+                c = block_sum<int>(c, is);
+                if (tid == 0) cnt_s = c;
+                cl_sync();
+                int all = 0;
+                for (unsigned r = 0; r < C; ++r) all += cl_load(&cnt_s, r);
+                if (all >= top_k) {
                     prefix = top_bin << 24;
                     first_pass = 1;
                 }
             }
             for (int pass = first_pass; pass < 4; ++pass) {
                 const int shift = 24 - 8 * pass;
-                if (tid < 256) hist[tid] = 0;
+                int* h = hist[pass & 1];                 // two in turn: the others may still read the last one
+                if (tid < 256) h[tid] = 0;
                 __syncthreads();
-                for_each_logit_in_step(z, V, [&](float v, bool valid) {
+                for_each_logit_in_step(z, n, [&](float v, bool valid) {
                     const unsigned key = ordered_key(v);
                     const bool in = valid && (pass == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8)));
                     if (__ballot_sync(0xffffffffu, in) == 0) return;       // after the first pass few elements are left
                     const int bin = in ? int((key >> shift) & 255u) : -1;
                     // the lanes of a warp that hit the same bin add to it once (most logits share their high bits)
                     const unsigned same = __match_any_sync(0xffffffffu, bin);
-                    if (in && lane == __ffs(same) - 1) atomicAdd(&hist[bin], __popc(same));
+                    if (in && lane == __ffs(same) - 1) atomicAdd(&h[bin], __popc(same));
                 });
+                cl_sync();
+                if (tid < 256) {
+                    int sum = 0;
+                    for (unsigned r = 0; r < C; ++r) sum += cl_load(&h[tid], r);
+                    hist_all[tid] = sum;
+                }
                 __syncthreads();
                 if (tid == 0) {
                     int above = 0, b = 255;
                     for (; b > 0; --b) {
-                        if (above + hist[b] >= need) break;
-                        above += hist[b];
+                        if (above + hist_all[b] >= need) break;
+                        above += hist_all[b];
                     }
                     sel_prefix = prefix | (unsigned(b) << shift);
                     sel_need = need - above;
@@ -498,7 +595,8 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
             }
             const unsigned tk = prefix;
             const int k_eq = need;                       // of the elements equal to tk, the first k_eq (by index) survive
-            // 4. the survivors, in index order, into shared memory: per warp the number above tk and equal to it ...
+            // 4. the survivors, in index order, into the first CTA's shared memory: per warp (and per CTA) the
+            // number above tk and equal to it ...
             {
                 int gt = 0, eq = 0;
                 for_each_in_piece(z, seg0, seg1, lane, [&](int, float v, bool inside) {
@@ -514,151 +612,111 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
                 if (lane == 0) { gt_s[warp] = gt; eq_s[warp] = eq; }
             }
             __syncthreads();
+            if (tid == 0) {
+                int g = 0, e = 0;
+                for (int w = 0; w < SM_WARPS; ++w) { g += gt_s[w]; e += eq_s[w]; }
+                tot_gt = g;
+                tot_eq = e;
+            }
+            cl_sync();
             int eq_before = 0, write_at = 0;
+            for (unsigned r = 0; r < rank; ++r) {
+                const int g = cl_load(&tot_gt, r), e = cl_load(&tot_eq, r);
+                write_at += g + max(0, min(e, k_eq - eq_before));
+                eq_before += e;
+            }
             for (int w = 0; w < warp; ++w) {
                 write_at += gt_s[w] + max(0, min(eq_s[w], k_eq - eq_before));
                 eq_before += eq_s[w];
             }
             // ... then every warp writes its own at its place
             for_each_in_piece(z, seg0, seg1, lane, [&](int i, float v, bool inside) {
-                const float zi = v;
-                const unsigned key = ordered_key(zi);
+                const unsigned key = ordered_key(v);
                 const bool is_eq = inside && key == tk;
                 const unsigned eq_mask = __ballot_sync(0xffffffffu, is_eq);
-                const unsigned below = (1u << lane) - 1u;
                 const bool surv = inside && (key > tk || (is_eq && eq_before + __popc(eq_mask & below) < k_eq));
                 const unsigned s_mask = __ballot_sync(0xffffffffu, surv);
                 if (surv) {
                     const int at = write_at + __popc(s_mask & below);
-                    list_idx[at] = i;
-                    list_z[at] = zi;
+                    cl_store(&list_idx[at], 0, lo + i);
+                    cl_store(&list_z[at], 0, v);
                 }
                 write_at += __popc(s_mask);
                 eq_before += __popc(eq_mask);
                 return true;
             });
-            __syncthreads();
-            const int n = top_k;                         // exactly top_k survive
-            // 5. the list in descending order (equal values: lower index first): every element counts those before it
-            if (tid < n) {
-                const float zj = list_z[tid];
-                const unsigned kj = ordered_key(zj);
-                const float e = expf(zj - zmax);
-                list_e[tid] = e;
-                int rank = 0;
-                for (int i = 0; i < n; ++i) {
-                    const unsigned ki = ordered_key(list_z[i]);
-                    rank += (ki > kj) || (ki == kj && i < tid);
-                }
-                sorted_e[rank] = e;
-                sorted_pos[rank] = short(tid);
-            }
-            __syncthreads();
-            // 6. top_p: the shortest prefix in that order whose mass reaches top_p of the whole (src/sampler.rs:59-69)
-            if (tid == 0) {
-                int cut = n;
-                if (use_p) {
-                    float Z = 0.f;
-                    for (int r = 0; r < n; ++r) Z += sorted_e[r];
-                    const float goal = top_p * Z;
-                    float cum = 0.f;
-                    for (int r = 0; r < n; ++r) {
-                        cum += sorted_e[r];
-                        if (cum >= goal) { cut = r + 1; break; }
+            cl_sync();
+            if (rank == 0) {
+                const int m = top_k;                     // exactly top_k survive
+                // 5. the list in descending order (equal values: lower index first): every element counts those before it
+                if (tid < m) {
+                    const float zj = list_z[tid];
+                    const unsigned kj = ordered_key(zj);
+                    const float e = expf(zj - zmax);
+                    list_e[tid] = e;
+                    int before = 0;
+                    for (int i = 0; i < m; ++i) {
+                        const unsigned ki = ordered_key(list_z[i]);
+                        before += (ki > kj) || (ki == kj && i < tid);
                     }
+                    sorted_e[before] = e;
+                    sorted_pos[before] = short(tid);
                 }
-                cut_s = cut;
-            }
-            __syncthreads();
-            if (tid < cut_s) list_idx[sorted_pos[tid]] |= 0x40000000;      // marks the kept ones (indices are below 2^30)
-            __syncthreads();
-            // 7. the walk over the kept ones in index order
-            if (tid == 0) {
-                float Z2 = 0.f;
-                for (int j = 0; j < n; ++j)
-                    if (list_idx[j] & 0x40000000) Z2 += list_e[j];
-                const float target = u * Z2;
-                float cum = 0.f;
-                int hit = -1, last = -1;
-                for (int j = 0; j < n; ++j) {
-                    if (!(list_idx[j] & 0x40000000)) continue;
-                    cum += list_e[j];
-                    last = j;
-                    if (target < cum) { hit = j; break; }
+                __syncthreads();
+                // 6. top_p: the shortest prefix in that order whose mass reaches top_p of the whole (src/sampler.rs:59-69)
+                if (tid == 0) {
+                    int cut = m;
+                    if (use_p) {
+                        float Z = 0.f;
+                        for (int r = 0; r < m; ++r) Z += sorted_e[r];
+                        const float goal = top_p * Z;
+                        float cum = 0.f;
+                        for (int r = 0; r < m; ++r) {
+                            cum += sorted_e[r];
+                            if (cum >= goal) { cut = r + 1; break; }
+                        }
+                    }
+                    cut_s = cut;
                 }
-                if (hit < 0) hit = last;                    // the last survivor (src/sampler.rs:78)
-                chosen = hit >= 0 ? (list_idx[hit] & 0x3fffffff) : bi;
-            }
-            __syncthreads();
-            pick = chosen;
-        } else if (!use_k && !use_p) {
-            // The whole vocabulary survives.  3. every warp's mass: each lane sums its own elements of the piece,
-            // then the lanes in order ...
-            auto mass_of = [&](int a, int b) {
-                float acc = 0.f;
-                for_each_in_piece(z, a, b, lane, [&](int, float v, bool inside) {
-                    acc += inside ? expf(v - zmax) : 0.f;
-                    return true;
-                });
-                return __shfl_sync(0xffffffffu, warp_inclusive(acc, lane), 31);
-            };
-            // ... and which of 32 masses (in order, after `before`) holds the target
-            auto holder_of = [&](const float* m, float target, float& before) {
-                int sel = -1;
-                float runsum = before;
-                for (int w = 0; w < SM_WARPS; ++w) {
-                    if (sel < 0 && target < runsum + m[w]) { sel = w; before = runsum; }
-                    runsum += m[w];
+                __syncthreads();
+                if (tid < cut_s) list_idx[sorted_pos[tid]] |= 0x40000000;      // marks the kept ones (indices are below 2^30)
+                __syncthreads();
+                // 7. the walk over the kept ones in index order
+                if (tid == 0) {
+                    float Z2 = 0.f;
+                    for (int j = 0; j < m; ++j)
+                        if (list_idx[j] & 0x40000000) Z2 += list_e[j];
+                    const float target = u * Z2;
+                    float cum = 0.f;
+                    int hit = -1, last = -1;
+                    for (int j = 0; j < m; ++j) {
+                        if (!(list_idx[j] & 0x40000000)) continue;
+                        cum += list_e[j];
+                        last = j;
+                        if (target < cum) { hit = j; break; }
+                    }
+                    if (hit < 0) hit = last;                    // the last survivor (src/sampler.rs:78)
+                    chosen = hit >= 0 ? (list_idx[hit] & 0x3fffffff) : bi;
                 }
-                return sel;
-            };
-            const float tot = mass_of(seg0, seg1);
-            if (lane == 0) fs[warp] = tot;
-            __syncthreads();
-            float Z2 = 0.f;
-            for (int w = 0; w < SM_WARPS; ++w) Z2 += fs[w];
-            const float target = u * Z2;
-            float before = 0.f;
-            const int wsel = holder_of(fs, target, before);
-            // 4. the piece that holds the target again, every warp with a part of it ...
-            const int p0 = wsel < 0 ? V : min(V, wsel * seg), p1 = min(V, p0 + seg);
-            const int part = ((p1 - p0 + SM_WARPS - 1) / SM_WARPS + 31) / 32 * 32;
-            const int q0 = min(p1, p0 + warp * part), q1 = min(p1, q0 + part);
-            const float tot2 = mass_of(q0, q1);
-            if (lane == 0) best_v[warp] = tot2;
-            __syncthreads();
-            const int vsel = wsel < 0 ? -1 : holder_of(best_v, target, before);
-            // ... 5. and the warp whose part holds it walks that part, 32 elements at a time in index order
-            if (warp == vsel) {
-                float c = before;
-                int hit = -1;
-                for_each_in_piece(z, q0, q1, lane, [&](int i, float v, bool inside) {
-                    const float inc = warp_inclusive(inside ? expf(v - zmax) : 0.f, lane);
-                    const unsigned mask = __ballot_sync(0xffffffffu, inside && target < c + inc);
-                    if (mask) hit = i - lane + __ffs(mask) - 1;
-                    c += __shfl_sync(0xffffffffu, inc, 31);
-                    return mask == 0;
-                });
-                if (hit < 0) hit = q1 - 1;                  // rounding left the target just beyond the part's last element
-                if (lane == 0) chosen = hit;
+                __syncthreads();
+                pick = chosen;
             }
-            __syncthreads();
-            // a target at or beyond a whole mass (rounding): the last element of what was searched
-            pick = chosen >= 0 ? chosen : (wsel >= 0 ? p1 - 1 : V - 1);
         } else if (!use_k) {
             // The whole vocabulary is in play.  3. top_p: the lowest key still inside the nucleus, eight bits a
             // pass as above, but the histogram holds masses; they are summed as 64-bit fixed point (2^-40 of the
             // largest weight), so that a sum does not depend on the order of its terms.
             unsigned tp = 0;
             int p_eq = 0x7fffffff;                       // of the elements equal to tp, the first p_eq (by index) survive
+            int eq_before = 0;
             if (use_p) {
                 unsigned prefix = 0;
                 unsigned long long above = 0, goal = 0;
                 for (int pass = 0; pass < 4; ++pass) {
                     const int shift = 24 - 8 * pass;
-                    if (tid < 256) mh[tid] = 0;
+                    unsigned long long* h = mh[pass & 1];
+                    if (tid < 256) h[tid] = 0;
                     __syncthreads();
-                    for_each_logit_in_step(z, V, [&](float v, bool valid) {
+                    for_each_logit_in_step(z, n, [&](float v, bool valid) {
                         const unsigned key = ordered_key(v);
                         const bool in = valid && (pass == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8)));
                         if (__ballot_sync(0xffffffffu, in) == 0) return;
@@ -666,23 +724,29 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
                         const unsigned long long m = in ? fixed_mass(v - zmax) : 0ull;
                         // the lanes of a warp that hit the same bin add their masses (41 bits at most, as two halves) once
                         const unsigned same = __match_any_sync(0xffffffffu, bin);
-                        const unsigned lo = __reduce_add_sync(same, unsigned(m & 0xfffffu));
-                        const unsigned hi = __reduce_add_sync(same, unsigned(m >> 20));
-                        if (in && lane == __ffs(same) - 1) atomicAdd(&mh[bin], ((unsigned long long)hi << 20) + lo);
+                        const unsigned mlo = __reduce_add_sync(same, unsigned(m & 0xfffffu));
+                        const unsigned mhi = __reduce_add_sync(same, unsigned(m >> 20));
+                        if (in && lane == __ffs(same) - 1) atomicAdd(&h[bin], ((unsigned long long)mhi << 20) + mlo);
                     });
+                    cl_sync();
+                    if (tid < 256) {
+                        unsigned long long sum = 0;
+                        for (unsigned r = 0; r < C; ++r) sum += cl_load(&h[tid], r);
+                        mh_all[tid] = sum;
+                    }
                     __syncthreads();
                     if (tid == 0) {
                         if (pass == 0) {
                             unsigned long long Z = 0;
-                            for (int b = 0; b < 256; ++b) Z += mh[b];
+                            for (int b = 0; b < 256; ++b) Z += mh_all[b];
                             goal = (unsigned long long)(double(top_p) * double(Z));
                             if (goal == 0) goal = 1;
                             sel_goal = goal;
                         }
                         int b = 255;
                         for (; b > 0; --b) {
-                            if (above + mh[b] >= goal) break;
-                            above += mh[b];
+                            if (above + mh_all[b] >= goal) break;
+                            above += mh_all[b];
                         }
                         sel_prefix = prefix | (unsigned(b) << shift);
                         sel_above = above;
@@ -701,10 +765,7 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
                     p_eq = c > 0x7ffffffeull ? 0x7fffffff : int(c);
                 }
                 if (p_eq < 1) p_eq = 1;
-            }
-            // 4. rank among the elements equal to tp, in index order: per warp how many its piece holds
-            int eq_before = 0;
-            if (use_p) {
+                // 4. rank among the elements equal to tp, in index order: how many the pieces (and parts) before hold
                 int eq = 0;
                 for_each_in_piece(z, seg0, seg1, lane, [&](int, float v, bool inside) {
                     eq += (inside && ordered_key(v) == tp);
@@ -713,69 +774,125 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
                 for (int o = 16; o > 0; o >>= 1) eq += __shfl_xor_sync(0xffffffffu, eq, o);
                 if (lane == 0) eq_s[warp] = eq;
                 __syncthreads();
+                if (tid == 0) {
+                    int e = 0;
+                    for (int w = 0; w < SM_WARPS; ++w) e += eq_s[w];
+                    tot_eq = e;
+                }
+                cl_sync();
+                for (unsigned r = 0; r < rank; ++r) eq_before += cl_load(&tot_eq, r);
                 for (int w = 0; w < warp; ++w) eq_before += eq_s[w];
             }
-            const unsigned below = (1u << lane) - 1u;
-            // 5. every warp's mass of survivors, 32 elements at a time in index order, and its last survivor ...
+            // 5. every warp's mass of survivors, and its last survivor ...
+            const bool wide = !use_p;                       // everything survives: no ranks to keep, sums lane by lane
             float cum = 0.f;
             int last = -1, eq_seen = eq_before;
-            for_each_in_piece(z, seg0, seg1, lane, [&](int i, float v, bool inside) {
-                const float zi = v;
-                const unsigned key = ordered_key(zi);
-                const unsigned eq_mask = __ballot_sync(0xffffffffu, inside && use_p && key == tp);
-                const bool surv = inside && (!use_p || key > tp || (key == tp && eq_seen + __popc(eq_mask & below) < p_eq));
-                eq_seen += __popc(eq_mask);
-                const float m = surv ? expf(zi - zmax) : 0.f;
-                cum += __shfl_sync(0xffffffffu, warp_inclusive(m, lane), 31);
-                const unsigned s_mask = __ballot_sync(0xffffffffu, surv);
-                if (s_mask) last = i - lane + 31 - __clz(s_mask);
-                return true;
-            });
+            if (wide) {
+                float acc = 0.f;
+                for_each_in_piece(z, seg0, seg1, lane, [&](int, float v, bool inside) {
+                    acc += inside ? expf(v - zmax) : 0.f;
+                    return true;
+                });
+                cum = __shfl_sync(0xffffffffu, warp_inclusive(acc, lane), 31);
+                last = seg1 > seg0 ? lo + seg1 - 1 : -1;
+            } else {
+                for_each_in_piece(z, seg0, seg1, lane, [&](int i, float v, bool inside) {
+                    const unsigned key = ordered_key(v);
+                    const unsigned eq_mask = __ballot_sync(0xffffffffu, inside && key == tp);
+                    const bool surv = inside && (key > tp || (key == tp && eq_seen + __popc(eq_mask & below) < p_eq));
+                    eq_seen += __popc(eq_mask);
+                    const float m = surv ? expf(v - zmax) : 0.f;
+                    cum += __shfl_sync(0xffffffffu, warp_inclusive(m, lane), 31);
+                    const unsigned s_mask = __ballot_sync(0xffffffffu, surv);
+                    if (s_mask) last = lo + i - lane + 31 - __clz(s_mask);
+                    return true;
+                });
+            }
             if (lane == 0) { fs[warp] = cum; is[warp] = last; }
+            cl_sync();
+            // ... 6. the piece in which the target falls, among the pieces of all CTAs ...
+            const int pieces = int(C) * SM_WARPS;
+            if (tid < pieces) {
+                all_m[tid] = cl_load(&fs[tid & 31], unsigned(tid >> 5));
+                all_last[tid] = cl_load(&is[tid & 31], unsigned(tid >> 5));
+            }
             __syncthreads();
-            // ... 6. the warp in whose piece the target falls ...
             float Z2 = 0.f;
             int last_all = -1;
-            for (int w = 0; w < SM_WARPS; ++w) { Z2 += fs[w]; last_all = max(last_all, is[w]); }
+            for (int w = 0; w < pieces; ++w) { Z2 += all_m[w]; last_all = max(last_all, all_last[w]); }
             const float target = u * Z2;
-            int wsel = -1;
-            float before = 0.f, runsum = 0.f;
-            for (int w = 0; w < SM_WARPS; ++w) {
-                if (wsel < 0 && target < runsum + fs[w]) { wsel = w; before = runsum; }
-                runsum += fs[w];
+            float before = 0.f;
+            const int gsel = holder_of(all_m, pieces, target, before);
+            writer = gsel < 0 ? rank == 0 : int(rank) == (gsel >> 5);
+            if (gsel < 0) {
+                pick = last_all >= 0 ? last_all : bi;       // target at or beyond the whole mass (rounding): the last survivor
+            } else if (writer) {
+                const int wsel = gsel & 31;
+                if (wide) {
+                    // 7. the piece that holds the target again, every warp with a part of it, and the warp whose
+                    // part holds it walks that part, 32 elements at a time in index order
+                    const int p0 = min(n, wsel * seg), p1 = min(n, p0 + seg);
+                    const int sub = ((p1 - p0 + SM_WARPS - 1) / SM_WARPS + 31) / 32 * 32;
+                    const int q0 = min(p1, p0 + warp * sub), q1 = min(p1, q0 + sub);
+                    float acc = 0.f;
+                    for_each_in_piece(z, q0, q1, lane, [&](int, float v, bool inside) {
+                        acc += inside ? expf(v - zmax) : 0.f;
+                        return true;
+                    });
+                    const float tot2 = __shfl_sync(0xffffffffu, warp_inclusive(acc, lane), 31);
+                    if (lane == 0) best_v[warp] = tot2;
+                    __syncthreads();
+                    const int vsel = holder_of(best_v, SM_WARPS, target, before);
+                    if (warp == vsel) {
+                        float c = before;
+                        int hit = -1;
+                        for_each_in_piece(z, q0, q1, lane, [&](int i, float v, bool inside) {
+                            const float inc = warp_inclusive(inside ? expf(v - zmax) : 0.f, lane);
+                            const unsigned mask = __ballot_sync(0xffffffffu, inside && target < c + inc);
+                            if (mask) hit = i - lane + __ffs(mask) - 1;
+                            c += __shfl_sync(0xffffffffu, inc, 31);
+                            return mask == 0;
+                        });
+                        if (hit < 0) hit = q1 - 1;          // rounding left the target just beyond the part's last element
+                        if (lane == 0) chosen = lo + hit;
+                    }
+                    __syncthreads();
+                    pick = chosen >= 0 ? chosen : lo + p1 - 1;
+                } else {
+                    // 7. the warp whose piece holds the target walks it again
+                    if (warp == wsel) {
+                        float c = before;
+                        int hit = -1;
+                        eq_seen = eq_before;
+                        for_each_in_piece(z, seg0, seg1, lane, [&](int i, float v, bool inside) {
+                            const unsigned key = ordered_key(v);
+                            const unsigned eq_mask = __ballot_sync(0xffffffffu, inside && key == tp);
+                            const bool surv = inside && (key > tp || (key == tp && eq_seen + __popc(eq_mask & below) < p_eq));
+                            eq_seen += __popc(eq_mask);
+                            const float inc = warp_inclusive(surv ? expf(v - zmax) : 0.f, lane);
+                            const unsigned mask = __ballot_sync(0xffffffffu, surv && target < c + inc);
+                            if (mask) hit = lo + i - lane + __ffs(mask) - 1;
+                            c += __shfl_sync(0xffffffffu, inc, 31);
+                            return mask == 0;
+                        });
+                        if (hit < 0) hit = last;            // rounding left the target just beyond the piece's last survivor
+                        if (lane == 0) chosen = hit;
+                    }
+                    __syncthreads();
+                    pick = chosen >= 0 ? chosen : last_all;
+                }
             }
-            // ... 7. and that warp walks its piece again
-            if (warp == wsel) {
-                float c = before;
-                int hit = -1;
-                eq_seen = eq_before;
-                for_each_in_piece(z, seg0, seg1, lane, [&](int i, float v, bool inside) {
-                    const float zi = v;
-                    const unsigned key = ordered_key(zi);
-                    const unsigned eq_mask = __ballot_sync(0xffffffffu, inside && use_p && key == tp);
-                    const bool surv = inside && (!use_p || key > tp || (key == tp && eq_seen + __popc(eq_mask & below) < p_eq));
-                    eq_seen += __popc(eq_mask);
-                    const float m = surv ? expf(zi - zmax) : 0.f;
-                    const float inc = warp_inclusive(m, lane);
-                    const unsigned mask = __ballot_sync(0xffffffffu, surv && target < c + inc);
-                    if (mask) hit = i - lane + __ffs(mask) - 1;
-                    c += __shfl_sync(0xffffffffu, inc, 31);
-                    return mask == 0;
-                });
-                if (hit < 0) hit = last;                    // rounding left the target just beyond the piece's last survivor
-                if (lane == 0) chosen = hit;
-            }
-            __syncthreads();
-            pick = chosen >= 0 ? chosen : (last_all >= 0 ? last_all : bi);   // target at or beyond the whole mass: the last survivor
         } else {
-            pick = sample_by_bisection(z, V, 1.0f, top_k, top_p, zmax, bi, u, fs, is, best_i);   // the row is scaled already
+            cl_sync();                                      // every part of the row is divided by the temperature
+            if (rank == 0) pick = sample_by_bisection(zrow, V, 1.0f, top_k, top_p, zmax, bi, u, fs, is, best_i);
         }
     }
-    if (tid == 0) {
+    if (writer && tid == 0) {
         out[row] = pick;
         recent[size_t(slot) * SM_RECENT + (n_before % SM_RECENT)] = pick;
         count[slot] = n_before + 1;
     }
+    cl_sync();                                              // nobody leaves while its shared memory may still be read
 }
 
 // logits: [n, V] 32-bit, rows ld apart; the penalty is applied to them in place, and with a temperature they
@@ -788,8 +905,28 @@ GB_API int gb_sample(float* logits, long long ld, int n, int V, const int* slots
     GB_REQUIRE(top_k >= 0 && top_p > 0.f && rep_penalty > 0.f, "gb_sample: bad parameters top_k=%d top_p=%g rep_penalty=%g",
                top_k, top_p, rep_penalty);
     if (n == 0) return 0;
-    gb_launch(sample_kernel, dim3(n), dim3(SM_THREADS), 0, stream, logits, ld, V, slots, seeds, temperature, top_k, top_p,
-              rep_penalty, recent, count, out);
+    // CTAs per sequence: as many as leave every CTA 4,096 logits or more and fit the device at once, eight at most
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int cluster = 1;
+    while (cluster < SM_MAX_CLUSTER && V / (2 * cluster) >= 4096 && (long long)n * 2 * cluster <= sms) cluster *= 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(n) * cluster);
+    cfg.blockDim = dim3(SM_THREADS);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = unsigned(cluster);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = gb_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, sample_kernel, logits, ld, V, slots, seeds, temperature, top_k, top_p, rep_penalty, recent,
+                       count, out);
     GB_LAUNCH_OK("gb_sample");
     return 0;
 }

@@ -340,7 +340,7 @@ def test_sampling_matches_the_plain_sampler(V):
         assert count.cpu().tolist() == [steps if s in slots else 0 for s in range(n_slots)]
 
 
-@pytest.mark.parametrize("V", [50, 1000, 4099])
+@pytest.mark.parametrize("V", [50, 1000, 4099, 33001])
 def test_sampling_with_many_equal_logits(V):
     """Logits that take few distinct values: the k-th largest and the edge of the nucleus fall among equal
     values, of which the lower indices are taken.  top_k from 1 to beyond the list the kernel keeps in shared
@@ -351,12 +351,17 @@ def test_sampling_with_many_equal_logits(V):
     slots = list(range(n))
     settings = [(1.0, 1, 1.0), (0.9, 7, 1.0), (1.1, 40, 0.8), (0.7, min(V - 1, 1024), 0.95), (1.0, min(V - 1, 1030), 0.9),
                 (1.0, min(V - 1, 2000), 1.0), (1.5, 0, 1.0), (0.8, 0, 0.6), (1.0, 33, 0.05)]
-    for levels in (2, 5, 64):
+    steps = 3
+    all_levels = (2, 5, 64)
+    if V > 30000:                                   # several CTAs share a row from here on; the plain sampler sorts in Python
+        n, all_levels, steps = 2, (5,), 1
+        slots = slots[:n]
+    for levels in all_levels:
         for temperature, top_k, top_p in settings:
             recent = torch.zeros(n_slots, 64, dtype=torch.int32, device=DEV)
             count = torch.zeros(n_slots, dtype=torch.int32, device=DEV)
             keys = [stream_key(5, i) for i in range(n)]
-            for step in range(3):
+            for step in range(steps):
                 logits = (torch.randint(0, levels, (n, V), generator=g).float() * (6.0 / levels) - 2.0).to(DEV)
                 ref = logits.cpu()
                 got = run_sample(logits, torch.tensor(slots, dtype=torch.int32, device=DEV),
