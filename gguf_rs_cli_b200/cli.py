@@ -25,6 +25,11 @@ def parse_ids(text: str) -> List[int]:
     return ids
 
 
+def parse_stop_ids(text: str) -> List[int]:
+    """Stop tokens; an empty string means none (generation then runs to --max-tokens)."""
+    return parse_ids(text) if text.strip() else []
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="gguf_rs_cli_b200", description="Llama generation on one B200: token ids in, token ids out")
     src = ap.add_mutually_exclusive_group(required=True)
@@ -45,7 +50,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--gpu", action="store_true", help="accepted for compatibility: this library always runs on the GPU")
     ap.add_argument("--debug-gpu", action="store_true", help="print the kernel launch count and time per step")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
-    ap.add_argument("--stop-ids", type=parse_ids, default=None, help="stop tokens (default: the model's eos ids)")
+    ap.add_argument("--stop-ids", type=parse_stop_ids, default=None,
+                    help="stop tokens (default: the model's eos ids; an empty string: none)")
     ap.add_argument("--max-batch", type=int, default=64, help="most requests generated together")
     return ap
 

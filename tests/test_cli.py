@@ -20,6 +20,9 @@ def test_option_names_and_defaults_are_the_reference_s():
                                    "1", "--rep-penalty", "1", "-c", "100", "--seed", "7", "--stats", "--gpu", "--debug-gpu"])
     assert a.prompts == [[4, 5], [6]] and (a.max_tokens, a.temperature, a.ctx_len, a.seed) == (3, 0.0, 100, 7) and a.stats
     assert parse_ids("1, 2,3") == [1, 2, 3]
+    assert a.stop_ids is None                                      # the model's own end tokens
+    assert build_parser().parse_args(["-m", "f", "-p", "1", "--stop-ids", ""]).stop_ids == []      # none: run to --max-tokens
+    assert build_parser().parse_args(["-m", "f", "-p", "1", "--stop-ids", "2,7"]).stop_ids == [2, 7]
     with pytest.raises(SystemExit):
         build_parser().parse_args(["-p", "1"])                     # no model
     with pytest.raises(SystemExit):
