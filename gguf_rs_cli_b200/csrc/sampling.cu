@@ -41,8 +41,6 @@ __device__ __forceinline__ unsigned long long splitmix64(unsigned long long z) {
     return z ^ (z >> 31);
 }
 
-template <typename T> struct SumOp { __device__ T operator()(T a, T b) const { return a + b; } };
-
 // Block-wide sum that every thread receives.
 template <typename T> __device__ T block_sum(T v, T* scratch) {
     __syncthreads();
