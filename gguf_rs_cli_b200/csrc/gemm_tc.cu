@@ -361,7 +361,8 @@ GB_API int gb_gemm_tc_splits(int T, int N, int K, int sms) {
     int slots = bn <= 64 ? 2 * sms : sms;          // CTAs that can be resident at once
     if (tiles >= sms || kb < 8) return 1;
     int s = int(slots / tiles);
-    if (s > kb / 4) s = kb / 4;       // at least 4 K blocks per split
+    if (s > kb / 4) s = kb / 4;       // at least 4 K blocks per split,
+    if (kb >= 64 && s > kb / 8) s = kb / 8;      // and 8 where K is long enough (4096 x 4096 at 8 to 16 tokens: 9.3 instead of 9.9 us)
     if (s > 16) s = 16;
     return s < 1 ? 1 : s;
 }
