@@ -115,7 +115,7 @@ def prefill_flops(cfg, layers, T):
     return linear + attn + 2 * V * E
 
 
-def measure_decode(llm, batch, steps, warmup, cfg):
+def measure_decode(llm, batch, steps, warmup, cfg, sampling=None):
     """K decode steps at `batch` after 512-token prompts.  Returns (tokens/s, ms/step,
     launches per step, context at the middle of the timed steps)."""
     import torch
@@ -124,7 +124,7 @@ def measure_decode(llm, batch, steps, warmup, cfg):
     g = torch.Generator().manual_seed(batch)
     prompts = [torch.randint(0, cfg["vocab_size"], (PROMPT,), generator=g).tolist() for _ in range(batch)]
     backend = llm.backend(n_tokens=64 * CONTEXT, n_slots=64, max_len=CONTEXT)
-    params = SamplingParams(temperature=0.0)
+    params = SamplingParams(**(sampling or {"temperature": 0.0}))
     keys = [stream_key(0, i) for i in range(batch)]
     slots = [backend.open() for _ in range(batch)]
     toks = backend.run(slots, prompts, keys, params)
@@ -199,6 +199,10 @@ def main():
     ap.add_argument("--layers", type=int, default=SHAPE_8B["num_hidden_layers"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1/64, prefill and e2e")
+    ap.add_argument("--temperature", type=float, default=0.0, help="sampling of the device-timed decode steps (default greedy)")
+    ap.add_argument("--top-k", type=int, default=0)
+    ap.add_argument("--top-p", type=float, default=1.0)
+    ap.add_argument("--rep-penalty", type=float, default=1.0)
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -223,7 +227,8 @@ def main():
     sampler = ClockSampler()
     sampler.start()
     t0 = sampler.mark()
-    tok_s, ms, launches, ctx_mid = measure_decode(llm, args.batch, args.steps, warmup, cfg)
+    sampling = {"temperature": args.temperature, "top_k": args.top_k, "top_p": args.top_p, "rep_penalty": args.rep_penalty}
+    tok_s, ms, launches, ctx_mid = measure_decode(llm, args.batch, args.steps, warmup, cfg, sampling)
     t1 = sampler.mark()
     clocks = sampler.summary(t0, t1)
 

@@ -397,6 +397,38 @@ __device__ __forceinline__ void cl_store(float* p, unsigned rank, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cl_addr(p, rank)), "f"(v) : "memory");
 }
 
+// One warp over a histogram of 256 bins: walking down from bin 255 with `above` as the sum so far, the first bin
+// with above + h[bin] >= goal (bin 0 if none), and the sum of the bins above it (on top of the `above` given).
+// Every lane takes eight bins; the lanes' sums are added up from the top lane down.
+template <typename T>
+__device__ __forceinline__ void pick_bin(const T* h, T goal, int lane, int& bin, T& above) {
+    T c[8], s = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { c[j] = h[8 * lane + j]; s += c[j]; }
+    T suf = s;                                             // this lane's bins and all bins above them
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const T n = __shfl_down_sync(0xffffffffu, suf, o);
+        if (lane + o < 32) suf += n;
+    }
+    T ab = above + (suf - s);                              // everything above this lane's bins
+    const unsigned mask = __ballot_sync(0xffffffffu, ab + s >= goal);
+    const int src = mask ? 31 - __clz(mask) : 0;           // the highest lane in whose bins the goal is reached
+    int b = 0;
+    if (mask) {
+        b = 8 * lane;
+#pragma unroll
+        for (int j = 7; j >= 0; --j) {
+            if (ab + c[j] >= goal) { b = 8 * lane + j; break; }
+            ab += c[j];
+        }
+    } else {
+        ab = above + suf - c[0];                           // (lane 0) all bins but the lowest
+    }
+    bin = __shfl_sync(0xffffffffu, b, src);
+    above = __shfl_sync(0xffffffffu, ab, src);
+}
+
 // Which of n masses (in order, after `before`) holds the target; `before` becomes the mass in front of it.
 __device__ __forceinline__ int holder_of(const float* m, int n, float target, float& before) {
     int sel = -1;
@@ -578,14 +610,13 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
                     hist_all[tid] = sum;
                 }
                 __syncthreads();
-                if (tid == 0) {
-                    int above = 0, b = 255;
-                    for (; b > 0; --b) {
-                        if (above + hist_all[b] >= need) break;
-                        above += hist_all[b];
+                if (warp == 0) {
+                    int above = 0, b;
+                    pick_bin<int>(hist_all, need, lane, b, above);
+                    if (lane == 0) {
+                        sel_prefix = prefix | (unsigned(b) << shift);
+                        sel_need = need - above;
                     }
-                    sel_prefix = prefix | (unsigned(b) << shift);
-                    sel_need = need - above;
                 }
                 __syncthreads();
                 prefix = sel_prefix;
@@ -733,21 +764,21 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(float* __restrict__ 
                         mh_all[tid] = sum;
                     }
                     __syncthreads();
-                    if (tid == 0) {
+                    if (warp == 0) {
                         if (pass == 0) {
                             unsigned long long Z = 0;
-                            for (int b = 0; b < 256; ++b) Z += mh_all[b];
+                            for (int j = 0; j < 8; ++j) Z += mh_all[8 * lane + j];
+                            for (int o = 16; o > 0; o >>= 1) Z += __shfl_xor_sync(0xffffffffu, Z, o);
                             goal = (unsigned long long)(double(top_p) * double(Z));
                             if (goal == 0) goal = 1;
+                        }
+                        int b;
+                        pick_bin<unsigned long long>(mh_all, goal, lane, b, above);
+                        if (lane == 0) {
                             sel_goal = goal;
+                            sel_prefix = prefix | (unsigned(b) << shift);
+                            sel_above = above;
                         }
-                        int b = 255;
-                        for (; b > 0; --b) {
-                            if (above + mh_all[b] >= goal) break;
-                            above += mh_all[b];
-                        }
-                        sel_prefix = prefix | (unsigned(b) << shift);
-                        sel_above = above;
                     }
                     __syncthreads();
                     prefix = sel_prefix;
