@@ -113,3 +113,22 @@ def test_streaming_callback_and_keys():
     assert seen == [(0, 11), (1, 21), (0, 12), (1, 22)]
     assert stream_key(1, 0) != stream_key(1, 1) != stream_key(2, 1)
     assert -(1 << 63) <= stream_key(123, 4) < (1 << 63)
+
+
+def test_decode_split_rule_is_fixed_within_a_graph_class():
+    """A captured decode graph is keyed by the class of the longest sequence: within a class the number of page
+    splits must not change, for any batch size, and it never asks for more CTAs than the rule allows."""
+    from gguf_rs_cli_b200 import kernels
+    sms = 148
+    for heads, kv in ((32, 8), (40, 40), (6, 3), (32, 1)):
+        for T in (1, 2, 3, 8, 16, 64, 200):
+            seen = {}
+            for max_kv in list(range(1, 3000, 7)) + list(range(3000, 140000, 997)):
+                cls = kernels.decode_split_class(max_kv)
+                s = kernels.decode_splits(T, heads, kv, max_kv, sms, True)
+                assert seen.setdefault(cls, s) == s, (heads, kv, T, max_kv)
+                pages = (max_kv + 63) // 64
+                group = heads // kv
+                ctas = T * kv * ((group + 15) // 16)
+                assert 1 <= s <= max(1, pages) and (s == 1 or s * ctas <= 2 * sms)
+    assert kernels.decode_splits(1, 32, 8, 2048, sms, True) == 8 and kernels.decode_splits(8, 32, 8, 520, sms, True) == 1
