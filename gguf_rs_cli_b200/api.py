@@ -51,11 +51,11 @@ class LLM:
         if (e is not None and e.cache.slots.held_count == 0 and e.cache.n_slots >= n_slots
                 and e.cache.n_pages * 64 >= n_tokens and e.cache.max_len >= (max_len or self.spec.max_position)):
             return e
-        if self._engine is None or self._engine_key != key:
-            self._backend = None
-            self._engine = None          # free the old cache before the new one is made
-            self._engine = Engine(self.model, n_tokens=n_tokens, n_slots=n_slots, max_len=max_len)
-            self._engine_key = key
+        # too small, or still holding sequences that an interrupted caller left behind: a new one
+        self._backend = None
+        self._engine = None              # free the old cache before the new one is made
+        self._engine = Engine(self.model, n_tokens=n_tokens, n_slots=n_slots, max_len=max_len)
+        self._engine_key = key
         return self._engine
 
     def backend(self, n_tokens: int, n_slots: int, max_len: Optional[int] = None) -> EngineBackend:
@@ -92,11 +92,13 @@ def generate(llm: LLM, prompt_ids: Sequence[Sequence[int]], max_tokens: int = 51
              top_k: int = 0, top_p: float = 1.0, rep_penalty: float = 1.0, seed: int = 42,
              stop_token_ids: Optional[Sequence[int]] = None, max_batch: int = 64, ctx_len: Optional[int] = None,
              on_token: Optional[Callable[[int, int], None]] = None,
-             stats: Optional[GenerationStats] = None) -> List[List[int]]:
+             stats: Optional[GenerationStats] = None, profile: bool = False) -> List[List[int]]:
     """Generated ids for each prompt, in order.  Option names and meanings are the
     reference's (src/main.rs:13-50): max_tokens, temperature (<= 0 is greedy), top_k,
     top_p, rep_penalty, seed, ctx_len (positions one sequence may hold).  Stop tokens
-    default to the model's eos ids; a stop token ends a sequence and is not returned."""
+    default to the model's eos ids; a stop token ends a sequence and is not returned.
+    profile: every step runs without CUDA graphs, with a time stamp after each stage, and prints
+    one line to standard error (the reference's --debug-gpu, src/main.rs:45-47)."""
     prompts = [list(p) for p in prompt_ids]
     if not prompts:
         return []
@@ -107,6 +109,7 @@ def generate(llm: LLM, prompt_ids: Sequence[Sequence[int]], max_tokens: int = 51
     backend = llm.backend(n_tokens=n_tokens, n_slots=batch, max_len=limit)
     stops = llm.spec.stop_token_ids if stop_token_ids is None else stop_token_ids
     params = SamplingParams(temperature, top_k, top_p, rep_penalty, seed)
+    backend.profile = bool(profile)
 
     def clock():
         torch.cuda.synchronize()

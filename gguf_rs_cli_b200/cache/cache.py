@@ -88,14 +88,31 @@ class Cache:
                 self.group_of_run[run] = (g.index, i)
             self.groups.append(g)
         self.states = {}
+        self._arena = self._arena_table = None
         if device is not None:
             import torch
             for g in self.groups:
                 shape = (len(g.runs), g.n_pages, g.spec.n_kv_heads, PAGE, g.spec.head_dim)
                 g.k = torch.empty(shape, dtype=dtype, device=device)
                 g.v = torch.empty(shape, dtype=dtype, device=device)
+            # all fixed-size state lies in one arena, region after region (each [slots, row]), so that one
+            # kernel launch zeroes a slot's row of every state when the slot opens
+            regions, off = [], 0
             for name, (shape, dt) in layout.states.items():
-                self.states[name] = torch.zeros((self.n_slots,) + tuple(shape), dtype=getattr(torch, dt), device=device)
+                td = getattr(torch, dt)
+                n = 1
+                for d in shape:
+                    n *= int(d)
+                row = n * torch.empty((), dtype=td).element_size()
+                if row % 4:
+                    raise CacheError(f"state {name}: a sequence's share ({row} bytes) must be a multiple of 4 bytes")
+                regions.append((name, tuple(shape), td, off, row))
+                off += (self.n_slots * row + 255) // 256 * 256
+            self._arena = torch.zeros(max(off, 256), dtype=torch.uint8, device=device)
+            for name, shape, td, at, row in regions:
+                self.states[name] = self._arena[at:at + self.n_slots * row].view(td).view((self.n_slots,) + shape)
+            if regions and torch.device(device).type == "cuda":
+                self._arena_table = torch.tensor([[at, row] for _, _, _, at, row in regions], dtype=torch.int64, device=device)
 
     # ------------------------------------------------------------ sequences
     def open(self) -> int:
@@ -104,8 +121,12 @@ class Cache:
         self.lengths[slot] = 0
         for g in self.groups:
             g.tables[slot] = []
-        for t in self.states.values():
-            t[slot].zero_()
+        if self._arena_table is not None:
+            from .. import kernels
+            kernels.zero_rows(self._arena, self._arena_table, slot)
+        else:
+            for t in self.states.values():
+                t[slot].zero_()
         return slot
 
     def close(self, slot: int) -> None:
@@ -183,5 +204,8 @@ class Cache:
                     assert g.pool.is_held(p), f"slot {s} lists page {p} that the pool thinks free"
                     assert p not in seen, f"page {p} of group {g.index} is in two tables"
                     seen.add(p)
-                assert len(pages) == g.pages_needed(self.lengths[s]) or len(pages) >= g.pages_needed(self.lengths[s])
+                # a reservation made for a step that has not been counted yet may hold more pages than the
+                # length needs, never fewer and never more than the ring
+                assert g.pages_needed(self.lengths[s]) <= len(pages) <= g.ring_pages, \
+                    f"slot {s} of length {self.lengths[s]} holds {len(pages)} pages of group {g.index}"
             assert len(seen) == g.pool.held_count, f"group {g.index}: {g.pool.held_count - len(seen)} pages are lost"

@@ -2,7 +2,8 @@
 names, meanings and defaults where it has them, with token ids in place of text.
 
     python -m gguf_rs_cli_b200 -m MODEL_DIR -p 1,2,3 [-p 4,5 ...] [-n 512] [-t 0.7] [--top-k 40]
-        [--top-p 0.9] [--rep-penalty 1.1] [-c 8192] [--seed 42] [--stats]
+        [--top-p 0.9] [--rep-penalty 1.1] [-c 8192] [--seed 42] [--stats] [--debug-gpu]
+        [--stop-ids 7,9] [--no-eos]
 
 Generated ids go to standard output, one line per prompt, comma separated; everything
 else goes to standard error (docs/INFERENCE.md:57 of the reference).  Not taken over:
@@ -48,10 +49,14 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--stats", action="store_true", help="print token throughput after the run")
     ap.add_argument("--gpu", action="store_true", help="accepted for compatibility: this library always runs on the GPU")
-    ap.add_argument("--debug-gpu", action="store_true", help="print the kernel launch count and time per step")
+    ap.add_argument("--debug-gpu", "--profile", dest="debug_gpu", action="store_true",
+                    help="time stamps after each stage of every step (embedding, the first layer's norm, q/k/v, "
+                         "attention, output projection, gate+up, down, all layers, head, sampling), one line per step")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
     ap.add_argument("--stop-ids", type=parse_stop_ids, default=None,
-                    help="stop tokens (default: the model's eos ids; an empty string: none)")
+                    help="further stop tokens, joined with the model's eos ids")
+    ap.add_argument("--no-eos", action="store_true",
+                    help="leave the model's eos ids out (with no --stop-ids generation runs to --max-tokens)")
     ap.add_argument("--max-batch", type=int, default=64, help="most requests generated together")
     return ap
 
@@ -76,7 +81,10 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     spec = llm.spec
     print(f"Model: {spec.architecture} | layers {len(spec.layers)} | hidden {spec.hidden_size} | vocab {spec.vocab_size}",
           file=sys.stderr)
-    stops = spec.stop_token_ids if args.stop_ids is None else args.stop_ids
+    # the model's end tokens joined with the caller's, as the reference joins the tokenizer's with the chat
+    # template's (src/chat.rs:57-72)
+    stops = [] if args.no_eos else list(spec.stop_token_ids)
+    stops += [t for t in (args.stop_ids or []) if t not in stops]
     print(f"EOS tokens: {list(stops)}", file=sys.stderr)
     print(f"Params: temp={args.temperature} top_k={args.top_k} top_p={args.top_p} rep_penalty={args.rep_penalty}",
           file=sys.stderr)
@@ -86,7 +94,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     try:
         out = generate(llm, prompts, max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k,
                        top_p=args.top_p, rep_penalty=args.rep_penalty, seed=args.seed, stop_token_ids=stops,
-                       max_batch=args.max_batch, ctx_len=args.ctx_len, stats=stats)
+                       max_batch=args.max_batch, ctx_len=args.ctx_len, stats=stats, profile=args.debug_gpu)
     except (ValueError, RuntimeError) as e:
         print(f"error: {e}", file=sys.stderr)
         return 1

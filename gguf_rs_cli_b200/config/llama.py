@@ -49,6 +49,15 @@ def _opt(raw, key, default, kind=int):
     return _need(raw, key, kind)
 
 
+def _head_dim_default(hidden: int, heads: int) -> int:
+    """head_dim = hidden_size / heads when config.json gives none (src/model/config.rs:48); the division
+    must come out even, else the projections' shapes would not match the folder's."""
+    if hidden % heads:
+        raise ConfigError(f"config.json: hidden_size {hidden} is not a multiple of num_attention_heads {heads} "
+                          f"(and there is no 'head_dim')")
+    return hidden // heads
+
+
 def _id_list(v) -> List[int]:
     """An id or a list of ids (the reference takes eos ids as scalar or list,
     src/gguf/types.rs:24-29)."""
@@ -106,7 +115,7 @@ class LlamaConfig:
             num_hidden_layers=_need(raw, "num_hidden_layers"),
             num_attention_heads=heads,
             num_key_value_heads=_opt(raw, "num_key_value_heads", heads),
-            head_dim=_opt(raw, "head_dim", hidden // heads),
+            head_dim=(_need(raw, "head_dim") if raw.get("head_dim") is not None else _head_dim_default(hidden, heads)),
             max_position_embeddings=_opt(raw, "max_position_embeddings", 32768),
             rms_norm_eps=_opt(raw, "rms_norm_eps", 1e-6, float),
             rope_theta=_opt(raw, "rope_theta", 10000.0, float),
@@ -197,8 +206,10 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
                    "feed_forward": PartSpec("rmsnorm", dict(size=cfg.hidden_size, eps=cfg.rms_norm_eps),
                                             {"weight": p + "post_attention_layernorm.weight"})},
             position=rope))
+    # the head falls back to the embedding table whenever the folder has no matrix for it, whatever
+    # tie_word_embeddings says (src/model/llama.rs:124); the flag only decides what random weights hold
     head_params = dict(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
-                       tied_to=("model.embed_tokens.weight" if cfg.tie_word_embeddings else None))
+                       tied_to="model.embed_tokens.weight", tied=cfg.tie_word_embeddings)
     spec = ModelSpec(
         architecture="LlamaForCausalLM",
         vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
@@ -212,6 +223,8 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
         max_position=cfg.max_position_embeddings,
         stop_token_ids=list(cfg.eos_token_ids),
         bos_token_id=cfg.bos_token_id,
+        # older exports keep each layer's table of rotation frequencies beside the parameters
+        ignored_tensors=["*.rotary_emb.inv_freq"],
     )
     spec.validate()
     return spec

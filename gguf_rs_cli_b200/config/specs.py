@@ -58,6 +58,8 @@ class ModelSpec:
     max_position: int
     stop_token_ids: List[int] = field(default_factory=list)
     bos_token_id: Optional[int] = None
+    # shell-style patterns of tensor names a folder may hold although no part asks for them
+    ignored_tensors: List[str] = field(default_factory=list)
 
     def validate(self) -> None:
         for r, run in enumerate(self.schedule):

@@ -380,3 +380,21 @@ GB_API int gb_swiglu(const void* gu, long long ld, void* out, int T, int F, int 
     GB_LAUNCH_OK("gb_swiglu");
     return 0;
 }
+
+// ------------------------------------------------------------- per-slot state
+// Zeroes one slot's row in every region of a byte arena: region r starts at table[2r] and holds rows of
+// table[2r+1] bytes (a multiple of 4), one per slot.  One block per region.
+__global__ void zero_rows_kernel(uint8_t* __restrict__ arena, const long long* __restrict__ table, int slot) {
+    const long long off = table[2 * blockIdx.x], row = table[2 * blockIdx.x + 1];
+    uint32_t* p = reinterpret_cast<uint32_t*>(arena + off + row * slot);
+    for (long long i = threadIdx.x; i < row / 4; i += blockDim.x) p[i] = 0u;
+}
+
+// The fixed-size state of a sequence that opens: every state tensor's row `slot` becomes zero in one launch.
+GB_API int gb_zero_rows(void* arena, const long long* table, int n_regions, int slot, cudaStream_t stream) {
+    GB_REQUIRE(n_regions >= 0 && slot >= 0, "gb_zero_rows: bad sizes regions=%d slot=%d", n_regions, slot);
+    if (n_regions == 0) return 0;
+    zero_rows_kernel<<<n_regions, 128, 0, stream>>>(reinterpret_cast<uint8_t*>(arena), table, slot);
+    GB_LAUNCH_OK("gb_zero_rows");
+    return 0;
+}

@@ -3,11 +3,13 @@ from __future__ import annotations
 
 from typing import List, Sequence
 
+import sys
+
 import numpy as np
 import torch
 
-from .. import kernels
 from ..cache.pool import PAGE, CacheFull, pages_for
+from ..parts.base import HostBatch
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .step import Engine, Entry, StepError
@@ -35,7 +37,16 @@ class DecodeGraph:
         self.layout = None
         self.table_offs = None
         self.n_words = 0
+        self.plan_words = 0          # words that parts planned for the step: such a graph is laid out anew every step
         self.host_np = self.meta[0].numpy()
+
+
+def format_marks(marks, n_tokens: int) -> str:
+    """One line per profiled step, stage by stage, in the manner of the reference's
+    `[ts0-1: 0.02ms] ... [total GPU: 1.23ms]` (src/gpu/mod.rs:345-361), with the stages' names."""
+    parts = [f"[{marks[i][0]}: {marks[i - 1][1].elapsed_time(marks[i][1]):.3f}ms]" for i in range(1, len(marks))]
+    total = marks[0][1].elapsed_time(marks[-1][1]) if len(marks) > 1 else 0.0
+    return f"[GPU step of {n_tokens} tokens] " + " ".join(parts) + f" [total GPU: {total:.3f}ms]"
 
 
 def bucket_of(n: int) -> int:
@@ -47,8 +58,13 @@ def bucket_of(n: int) -> int:
 
 class EngineBackend:
     def __init__(self, engine: Engine, use_graphs: bool = True):
+        """use_graphs: decode steps run as captured CUDA graphs where every part of the model allows it
+        (`graph_class`).  profile: every step runs eagerly with a time stamp after each stage and one line
+        per step goes to `profile_out` (the reference's --debug-gpu, src/gpu/mod.rs:345-361)."""
         self.engine = engine
         self.use_graphs = use_graphs
+        self.profile = False
+        self.profile_out = sys.stderr
         self._graphs = {}
         self._batch = None           # (slots of the last decode step, their lengths after it)
         self._last_graph = None
@@ -61,6 +77,7 @@ class EngineBackend:
         self._keys_dev = torch.zeros(n, dtype=torch.int64, device=engine.device)
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self._ones = [1] * n
 
     def admit(self, prompt_lens: Sequence[int], max_new: int) -> int:
         """Prompts are admitted in order while slots and pages last, counting each at the
@@ -99,14 +116,19 @@ class EngineBackend:
             lengths = self._batch[1]
         else:
             lengths = np.array([cache.length(s) for s in slots], dtype=np.int64)
-        # the attention kernels' page splits are fixed in a captured graph: one graph per class of length
-        key = (bucket_of(n), kernels.decode_split_class(int(lengths.max()) + 1), params.temperature, params.top_k,
-               params.top_p, params.rep_penalty)
+        # what a captured graph fixes (grids that depend on the lengths, a part's host-side choices) is the
+        # parts' to say: one graph per class of step
+        longest = int(lengths.max())
+        cls = eng.model.graph_class(HostBatch(slots, lengths, self._ones[:n], decode=True, max_qlen=1, max_kv=longest + 1))
+        if cls is None:
+            return None
+        key = (bucket_of(n), cls, params.temperature, params.top_k, params.top_p, params.rep_penalty)
         dg = self._graphs.get(key)
         if dg is None:
             dg = self._graphs[key] = DecodeGraph(eng, key[0])
         tokens = np.fromiter((f[0] for f in feeds), dtype=np.int64, count=n)
-        if dg.graph is not None and self._last_graph is dg and dg.laid_out_for == slots_t and dg.keys == keys:
+        if (dg.graph is not None and self._last_graph is dg and dg.laid_out_for == slots_t and dg.keys == keys
+                and dg.plan_words == 0):
             self._advance_in_place(dg, slots, tokens, lengths)
             dg.graph.replay()
             native.count_launches(dg.launches)
@@ -116,6 +138,10 @@ class EngineBackend:
             ctx, want_rows, _ = eng.plan(entries, pad_to=dg.bucket, full_tables=True, want_all=True, meta=dg.meta)
             dg.laid_out_for, dg.layout = slots_t, ctx.host["layout"]
             dg.table_offs, dg.n_words = ctx.host["table_offs"], ctx.host["n_words"]
+            if dg.graph is not None and ctx.host["plan_words"] != dg.plan_words:
+                raise StepError("a part planned index arrays of another size than in the step its graph was captured "
+                                "from: its graph_class must tell such steps apart")
+            dg.plan_words = ctx.host["plan_words"]
             dg.keys = list(keys)
             dg.keys_host[:n] = torch.tensor(keys, dtype=torch.int64)
             dg.keys_dev.copy_(dg.keys_host, non_blocking=True)
@@ -173,19 +199,27 @@ class EngineBackend:
             cache.lengths[s] += 1
 
     def run(self, slots: List[int], feeds: List[List[int]], keys: List[int], params: SamplingParams) -> List[int]:
-        if self.use_graphs and all(len(f) == 1 for f in feeds):
-            return self._run_decode_graph(slots, feeds, keys, params)
+        if self.use_graphs and not self.profile and all(len(f) == 1 for f in feeds):
+            out = self._run_decode_graph(slots, feeds, keys, params)
+            if out is not None:
+                return out
         eng, n = self.engine, len(slots)
         self._batch = self._last_graph = None
         entries = [Entry(s, f, (len(f) - 1,)) for s, f in zip(slots, feeds)]
         self._keys_host[:n] = torch.tensor(keys, dtype=torch.int64)
         self._keys_dev[:n].copy_(self._keys_host[:n], non_blocking=True)
         ctx, want_rows, n_want = eng.plan(entries)
+        if self.profile:
+            ctx.marks = []
+            ctx.mark("start")
         logits = eng.model.forward(ctx, eng.runs, want_rows)
         eng.cache.advance(ctx.host["slots"], ctx.host["qlens"])
         self.sampler.sample(logits, ctx.slots[:n], self._keys_dev[:n], params, self._out_dev)
+        ctx.mark("sample")
         self._out_host[:n].copy_(self._out_dev[:n], non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        if self.profile:
+            print(format_marks(ctx.marks, ctx.T), file=self.profile_out, flush=True)
         eng.check()
         self.h2d_bytes += ctx.host["h2d_bytes"] + 8 * n
         self.d2h_bytes += 4 * n

@@ -23,7 +23,7 @@ class GenerationError(ValueError):
 @dataclass
 class _Live:
     request: int
-    slot: int
+    slot: Optional[int]
     feed: List[int]
     pos: int = 0
 
@@ -71,37 +71,47 @@ def generate_ids(backend, prompts: Sequence[Sequence[int]], max_tokens: int, par
         n = backend.admit([len(p) for p in window], max_tokens)
         if n < 1:
             raise GenerationError(f"prompt {nxt} does not fit the cache even alone")
-        live = [_Live(i, backend.open(), list(prompts[i])) for i in range(nxt, nxt + n)]
-        nxt += n
-        first = True
-        if stats:
-            stats.batches += 1
-        while live:
-            t0 = now()
-            sampled = backend.run([s.slot for s in live], [s.feed for s in live], [keys[s.request] for s in live], params)
-            dt = now() - t0
+        live = []
+        try:
+            for i in range(nxt, nxt + n):
+                live.append(_Live(i, backend.open(), list(prompts[i])))
+            nxt += n
+            first = True
             if stats:
-                stats.step_batch_sizes.append(len(live))
-                if first:
-                    stats.prompt_tokens += sum(len(s.feed) for s in live)
-                    stats.prefill_seconds += dt
-                else:
-                    stats.decode_steps += 1
-                    stats.decode_seconds += dt
-            first = False
-            still = []
-            for s, tok in zip(live, sampled):
-                s.pos += len(s.feed)
-                tok = int(tok)
-                if tok in stops or len(results[s.request]) >= max_tokens or s.pos >= ctx - 1:
-                    backend.close(s.slot)          # given back at once: the next batch may use it
-                    continue
-                results[s.request].append(tok)
+                stats.batches += 1
+            while live:
+                t0 = now()
+                sampled = backend.run([s.slot for s in live], [s.feed for s in live], [keys[s.request] for s in live], params)
+                dt = now() - t0
                 if stats:
-                    stats.generated_tokens += 1
-                if on_token:
-                    on_token(s.request, tok)
-                s.feed = [tok]
-                still.append(s)
-            live = still
+                    stats.step_batch_sizes.append(len(live))
+                    if first:
+                        stats.prompt_tokens += sum(len(s.feed) for s in live)
+                        stats.prefill_seconds += dt
+                    else:
+                        stats.decode_steps += 1
+                        stats.decode_seconds += dt
+                first = False
+                still = []
+                for k, (s, tok) in enumerate(zip(live, sampled)):
+                    s.pos += len(s.feed)
+                    tok = int(tok)
+                    if tok in stops or len(results[s.request]) >= max_tokens or s.pos >= ctx - 1:
+                        backend.close(s.slot)          # given back at once: the next batch may use it
+                        s.slot = None
+                        continue
+                    results[s.request].append(tok)
+                    if stats:
+                        stats.generated_tokens += 1
+                    if on_token:
+                        on_token(s.request, tok)
+                    s.feed = [tok]
+                    still.append(s)
+                live = still
+        finally:
+            # a step, a callback or the cache may raise: whatever the batch still holds is given back
+            for s in live:
+                if s.slot is not None:
+                    backend.close(s.slot)
+                    s.slot = None
     return results

@@ -15,10 +15,11 @@ from typing import List, Optional, Sequence, Tuple
 
 import torch
 
-from .. import kernels, native
+from .. import native
 from ..cache.cache import Cache
+from ..kernels import check_tc_status
 from ..models.decoder import Decoder
-from ..parts.base import StepContext, Workspace
+from ..parts.base import HostBatch, StepContext, Workspace
 
 SAMPLER_STATES = {"sampler.recent": ((64,), "int32"), "sampler.count": ((), "int32")}
 
@@ -67,7 +68,7 @@ class Engine:
     def check(self) -> None:
         """After a synchronise: raises if a kernel's bounded wait gave up during the steps
         since the last check."""
-        kernels.check_tc_status()
+        check_tc_status()
 
     # ----------------------------------------------------------------- plan
     def _meta(self, n: int) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -87,9 +88,12 @@ class Engine:
         self._meta_slot = i
         return self._meta_ring[i]
 
+    PLAN_WORDS = 4096
+
     def meta_size(self, batch: int) -> int:
-        """int32 words of index arrays for a padded batch of single tokens with full tables."""
-        return 8 * batch + 1 + batch * sum(g.table_width for g in self.cache.groups)
+        """int32 words of index arrays for a padded batch of single tokens with full tables, and room for
+        what parts plan for such a step."""
+        return 8 * batch + 1 + batch * sum(g.table_width for g in self.cache.groups) + self.PLAN_WORDS
 
     def plan(self, entries: Sequence[Entry], pad_to: Optional[int] = None, full_tables: bool = False,
              want_all: bool = False, meta: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
@@ -141,15 +145,22 @@ class Engine:
         qlens_p = qlens + [0] * padB
         if want_all:
             want = list(range(Tp))
-        tiles = [] if max(qlens) == 1 else kernels.attention_prefill_tiles(qlens)
-        flat = tokens + seq_of + pos + slots_p + starts_p + qlens_p + cu + want + tiles
+        flat = tokens + seq_of + pos + slots_p + starts_p + qlens_p + cu + want
         offs, o = {}, 0
         for name, n in (("tokens", Tp), ("seq_of", Tp), ("pos", Tp), ("slots", Bp), ("starts", Bp), ("qlens", Bp),
-                        ("cu", Bp + 1), ("want", len(want)), ("tiles", len(tiles))):
+                        ("cu", Bp + 1), ("want", len(want))):
             offs[name] = (o, n)
             o += n
-        table_offs = []
         max_kv = max(s + q for s, q in zip(starts, qlens))
+        # index arrays that parts lay out for themselves travel in the same copy
+        batch = HostBatch(slots, starts, qlens, decode=max(qlens) == 1, max_qlen=max(qlens), max_kv=max_kv)
+        plan_offs = []
+        for key, part in self.model.planners:
+            for name, values in part.plan(batch).items():
+                values = [int(v) for v in values]
+                plan_offs.append((key, name, len(flat), len(values)))
+                flat += values
+        table_offs = []
         for g in self.cache.groups:
             # only as many table entries as this step's longest sequence uses, unless the
             # caller needs the same layout every step (a captured graph)
@@ -179,15 +190,21 @@ class Engine:
             tables=[dev[a:a + b * w].view(b, w) for a, b, w in table_offs], cache=self.cache, ws=self.ws,
             decode=max(qlens) == 1, max_qlen=max(qlens), max_kv=max_kv,
             host={"slots": slots, "starts": starts, "qlens": qlens, "h2d_bytes": 4 * len(flat), "layout": offs,
-                  "table_offs": table_offs, "n_words": len(flat)},
-            tiles=view("tiles").view(-1, 2) if tiles else None)
+                  "table_offs": table_offs, "n_words": len(flat), "batch": batch,
+                  "plan_words": sum(n for _, _, _, n in plan_offs)})
+        for key, name, a, n in plan_offs:
+            ctx.plans.setdefault(key, {})[name] = dev[a:a + n]
         return ctx, view("want"), len(want)
 
     # ----------------------------------------------------------------- step
     def step(self, entries: Sequence[Entry]) -> Optional[torch.Tensor]:
         """Runs the entries' tokens as one batch from the cache and advances the sequences.
         Returns float32 logits [wanted, V] in the order of the entries and of each `want`
-        (None when nothing is wanted; the tokens still enter the cache)."""
+        (None when nothing is wanted; the tokens still enter the cache).
+
+        The tensor returned is one of the engine's own buffers (a step allocates nothing): a later
+        step that wants the same number of rows writes over it.  Copy what has to outlive the next
+        step (`.clone()`, or `.cpu()` as the replay program does)."""
         entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
         ctx, want_rows, n_want = self.plan(entries)
         logits = self.model.forward(ctx, self.runs, want_rows)

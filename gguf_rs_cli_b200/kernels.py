@@ -94,6 +94,13 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def zero_rows(arena: torch.Tensor, table: torch.Tensor, slot: int) -> None:
+    """Zeroes row `slot` of every region of a byte arena; table int64 [regions, 2] = (offset, bytes per row)."""
+    _cuda(arena, table)
+    assert arena.dtype == torch.uint8 and table.dtype == torch.int64 and table.is_contiguous()
+    call("gb_zero_rows", ptr(arena), ptr(table), table.shape[0], int(slot), stream_ptr())
+
+
 def gemm_generic(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
     """out[t,n] = sum_k x[t,k] w[n,k] + bias[n], 32-bit FMAs on the CUDA cores."""
     _cuda(x, w, bias, out)
@@ -121,21 +128,27 @@ def sample(logits: torch.Tensor, slots: torch.Tensor, seeds: torch.Tensor, tempe
 
 
 class _TcScratch:
-    """Scratch of the kernels that split their work and merge it without waiting (the
-    tensor-core product's K split, decode attention's page split), per device: partial
-    results and arrival counters (zero between launches).  Launches on one stream follow
-    one another, so they can share it."""
+    """Scratch of the kernels that split their work and merge it (the tensor-core product's K split,
+    decode attention's page split), per device: partial results and arrival counters (zero between
+    launches).  Launches on one stream follow one another, so they can share it.
+
+    It is allocated once, at the most any launch can need, and never again: a captured CUDA graph
+    holds its address, so a buffer that grew would leave every graph captured before pointing at
+    freed memory.  The product needs at most one partial tile per resident CTA (two CTAs per SM with
+    tiles of up to 64 tokens, one with wider tiles: 2 * sms * 64 * 128 floats), decode attention
+    (head_dim + 2) floats per head and split with no more CTAs than two per SM.  A launch that would
+    need more (only a tuning override can ask for it) runs without splitting instead."""
     COUNTERS = 4096
 
     def __init__(self, device):
         self.device = device
         self.sms = native.library().gb_sm_count()
-        self.floats = torch.empty(1 << 20, dtype=torch.float32, device=device)
+        self.capacity = 2 * max(self.sms, 1) * 256 * 128
+        self.floats = torch.empty(self.capacity, dtype=torch.float32, device=device)
         self.counters = torch.zeros(self.COUNTERS, dtype=torch.int32, device=device)
 
-    def ensure(self, n_floats: int) -> None:
-        if n_floats > self.floats.numel():
-            self.floats = torch.empty(int(n_floats * 1.25), dtype=torch.float32, device=self.device)
+    def fits(self, n_floats: int) -> bool:
+        return n_floats <= self.capacity
 
 
 _tc_scratch = {}
@@ -193,8 +206,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
     scratch = counters = None
     if split_k:
         need = native.library().gb_gemm_tc_scratch_floats(T, N, K, sc.sms)
-        if need:
-            sc.ensure(need)
+        if need and sc.fits(need):
             scratch, counters = sc.floats, sc.counters
     call("gb_gemm_tc_fused", ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(bias), 0 if bias is None else dtype_code(bias),
          ptr(out), 1 if out is None else dtype_code(out), 0 if out is None else out.stride(0), T, N, K, ptr(scratch),
@@ -269,9 +281,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_head
     need = lib.gb_attention_decode_scratch_floats(T, n_heads, head_dim, splits)
     scratch = counters = None
     if need:
-        sc.ensure(need)
         scratch, counters = sc.floats, sc.counters
-        if T * n_heads > sc.COUNTERS:
+        if T * n_heads > sc.COUNTERS or not sc.fits(need):
             splits, scratch, counters = 1, None, None
     if rope is not None:
         k, v, inv_freq, rotary_dim, pairing = rope
@@ -371,17 +382,18 @@ def decode_rotates(ctx, q: torch.Tensor, kcache: torch.Tensor, head_dim: int) ->
 
 def attention(q: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, ctx, table: torch.Tensor,
               ring_pages: int, kcache: torch.Tensor, vcache: torch.Tensor, window: int, scale: float,
-              rope: Optional[tuple] = None) -> torch.Tensor:
+              rope: Optional[tuple] = None, tiles: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of one step over the cache; picks the kernel for the step's shape.  rope: see
-    attention_decode; allowed where decode_rotates() says so (q, k and v then come unrotated)."""
+    attention_decode; allowed where decode_rotates() says so (q, k and v then come unrotated).
+    tiles: attention_prefill_tiles() of the step's sequences on the device (prompts on the tiled kernels)."""
     if rope is not None:
         assert decode_rotates(ctx, q, kcache, head_dim)
     if ctx.decode and attention_decode_supported(q, kcache, head_dim):
         return attention_decode(q, out, n_heads, n_kv_heads, head_dim, ctx.seq_of, ctx.pos, table, ring_pages, kcache,
                                 vcache, window, scale, max_kv=min(ctx.max_kv, window) if window else ctx.max_kv,
                                 mma=True if rope is not None else None, rope=rope)
-    if not ctx.decode and ctx.tiles is not None and attention_prefill_supported(q, kcache, head_dim):
-        return attention_prefill(q, out, n_heads, n_kv_heads, head_dim, ctx.tiles, ctx.cu, ctx.starts, ctx.qlens, table,
+    if not ctx.decode and tiles is not None and attention_prefill_supported(q, kcache, head_dim):
+        return attention_prefill(q, out, n_heads, n_kv_heads, head_dim, tiles, ctx.cu, ctx.starts, ctx.qlens, table,
                                  ring_pages, kcache, vcache, window, scale)
     return attention_generic(q, out, n_heads, n_kv_heads, head_dim, ctx.seq_of, ctx.pos, table, ring_pages, kcache,
                              vcache, window, scale)

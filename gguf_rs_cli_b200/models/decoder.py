@@ -15,7 +15,7 @@ import torch
 
 from ..cache.cache import Cache, CacheLayout
 from ..config.specs import LayerSpec, ModelSpec, PartSpec
-from ..parts.base import RunView, StepContext, Stream
+from ..parts.base import HostBatch, RunView, StepContext, Stream, plan_key_of
 from ..parts.registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS
 from ..weights.loader import TensorRequest, WeightStore
 
@@ -71,6 +71,44 @@ class Decoder:
                     raise ValueError(f"schedule[{r}] cannot read the cache of run {run.cache_of}: {src} does not match "
                                      f"{mixer.reads_kv_spec()}")
 
+        # parts that lay out index arrays on the host, one per plan key, and what decides whether and how a
+        # decode step is captured: every computing part's graph_class (constant, callable, or missing)
+        self.planners = []
+        self._graph_constants, self._graph_callables, self.capturable = [], [], True
+        seen_plans, seen_classes = set(), set()
+        computing = [self.embedding, self.final_norm, self.head]
+        for r in spec.schedule:
+            l = self.layers[r.layer]
+            computing += [l.block, l.mixer, l.feed_forward] + list(l.norms.values())
+        for part in computing:
+            key = plan_key_of(part)
+            if hasattr(part, "plan") and key not in seen_plans:
+                seen_plans.add(key)
+                self.planners.append((key, part))
+            if key in seen_classes:
+                continue
+            seen_classes.add(key)
+            gc = getattr(part, "graph_class", None)
+            if gc is None:
+                self.capturable = False
+            elif callable(gc):
+                self._graph_callables.append(gc)
+            else:
+                self._graph_constants.append(gc)
+
+    def graph_class(self, batch: HostBatch):
+        """Hashable class of a decode step for capture in a CUDA graph, or None when a part of the model
+        cannot be captured."""
+        if not self.capturable:
+            return None
+        classes = []
+        for fn in self._graph_callables:
+            c = fn(batch)
+            if c is None:
+                return None
+            classes.append(c)
+        return tuple(classes)
+
     # ---------------------------------------------------------------- weights
     def parts(self):
         out = [self.embedding]
@@ -82,7 +120,7 @@ class Decoder:
         return _requests_of(self.spec, self.parts())
 
     def load(self, store: WeightStore) -> "Decoder":
-        store.check(self.tensor_requests())
+        store.check(self.tensor_requests(), allow_unused=self.spec.ignored_tensors)
         for p in self.parts():
             p.load(store)
         store.release()
@@ -123,10 +161,16 @@ class Decoder:
         """Logits float32 [len(want_rows), V] at the packed token rows asked for."""
         make = getattr(self.embedding, "forward_stream", None)
         stream = make(ctx.tokens, ctx) if make else Stream(self.embedding.forward(ctx.tokens, ctx))
+        ctx.mark("embed")
         for view in runs:
+            ctx.mark_detail = view.index == 0         # stages are stamped in the first run only, as the reference does
             self.layers[view.layer].block.forward(stream, ctx, view)
+        ctx.mark_detail = True
+        ctx.mark("layers")
         h = self.final_norm.apply(stream, ctx, rows=want_rows, buffer="final_normed")
-        return self.head.forward(h, ctx)
+        logits = self.head.forward(h, ctx)
+        ctx.mark("head")
+        return logits
 
 
 def tensor_requests(spec: ModelSpec) -> List[TensorRequest]:

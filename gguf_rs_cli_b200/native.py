@@ -130,6 +130,7 @@ _SIGNATURES = {
     "gb_add_rmsnorm": [_P, _P, _I, _I, _L, _P, _I, _I, _P, _I, _F, _P, _I, _I, _P],
     "gb_rope_kv_write": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _P],
     "gb_swiglu": [_P, _L, _P, _I, _I, _I, _P],
+    "gb_zero_rows": [_P, _P, _I, _I, _P],
     "gb_gemm_generic": [_P, _I, _L, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P],
     "gb_attention_generic": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _F, _P],
     "gb_sample": [_P, _L, _I, _I, _P, _P, _F, _I, _F, _F, _P, _P, _P, _P],

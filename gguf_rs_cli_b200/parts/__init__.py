@@ -1,5 +1,5 @@
 from . import attention, block, embedding, feed_forward, norm, rotary  # noqa: F401  (register the built-in parts)
-from .base import Part, RunView, StepContext, Stream, Workspace
+from .base import HostBatch, Part, RunView, StepContext, Stream, Workspace, plan_key_of
 from .linear import Linear
 from .registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, register_block,
                        register_embedding, register_feed_forward, register_head, register_mixer, register_norm,

@@ -17,7 +17,7 @@ import torch
 from .. import kernels
 from ..cache.cache import KVSpec
 from ..weights.loader import TensorRequest, WeightStore
-from .base import Part, RunView, StepContext
+from .base import HostBatch, Part, RunView, StepContext
 from .linear import Linear
 from .registry import register_mixer
 
@@ -74,6 +74,21 @@ class Attention(Part):
 
     accepts_residual = True
 
+    # ---- planning on the host
+    def plan_key(self):
+        return ("attention", self.hd, self.window)
+
+    def plan(self, batch: HostBatch):
+        """Prompts: the list of query tiles (sequence row, first query) that the prefill kernel's CTAs take."""
+        if batch.decode:
+            return {}
+        return {"tiles": kernels.attention_prefill_tiles(batch.qlens)}
+
+    def graph_class(self, batch: HostBatch):
+        """The decode kernel splits each sequence's pages over CTAs by a rule of the longest sequence; steps
+        of one class launch the same grid and may share a captured graph."""
+        return kernels.decode_split_class(min(batch.max_kv, self.window) if self.window else batch.max_kv)
+
     def absorb_input_norm(self, weight: torch.Tensor) -> bool:
         """Multiplies the weight of the norm in front of this mixer into the q/k/v matrix, where
         the tensor-core product (which can apply the norm's per-token scale) will run it."""
@@ -85,6 +100,7 @@ class Attention(Part):
     def forward(self, h, ctx: StepContext, run: RunView, residual=None) -> Optional[torch.Tensor]:
         nh, nkv, hd = self.nh, self.nkv, self.hd
         qkv = self.qkv(h, ctx)
+        ctx.mark("qkv")
         q = qkv[:, :nh * hd]
         k = v = None
         if not self.shares_kv:
@@ -101,5 +117,8 @@ class Attention(Part):
                                   run.ring_pages, run.k if k is not None else None, run.v if k is not None else None)
         out = ctx.ws.get("attn.out", (h.shape[0], nh * hd), ctx.dtype)
         kernels.attention(q, out, nh, nkv, hd, ctx, table, run.ring_pages, run.k, run.v, self.window or 0, self.scale,
-                          rope=rope)
-        return self.o(out, ctx, residual=residual)
+                          rope=rope, tiles=ctx.plan_of(self).get("tiles"))
+        ctx.mark("attention")
+        term = self.o(out, ctx, residual=residual)
+        ctx.mark("o")
+        return term

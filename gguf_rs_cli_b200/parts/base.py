@@ -21,11 +21,23 @@ Roles:
   block         forward(stream, ctx, run): wires norms, mixer and feed-forward around x
   embedding     forward(tokens, ctx) -> float32 x [T, E]
   head          forward(h, ctx) -> float32 logits [rows, V]
+
+Optional hooks of any part (a part without them works):
+  plan(batch: HostBatch) -> {name: list of int}   index arrays the part lays out on the host for this
+                step; they travel in the step's one host-to-device copy and come back as int32
+                device tensors in ctx.plan_of(part)
+  plan_key() -> hashable   parts with equal keys share one plan and one graph class (layers with the
+                same constants); default: every part for itself
+  graph_class   whether and how decode steps that contain the part may be captured in a CUDA graph:
+                a hashable constant, or graph_class(batch) -> hashable, equal for steps whose launches
+                (grids, buffer shapes, host-side branches, plan sizes) are the same; None or no
+                attribute at all: never captured (a part that computes with host values each step)
+  ctx.mark(label)          a time stamp after a stage, recorded when a step is profiled
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -68,6 +80,23 @@ class Workspace:
 
 
 @dataclass
+class HostBatch:
+    """One step as the host sees it, for parts that plan there: the sequences' cache slots, their
+    lengths before the step and the tokens each brings."""
+    slots: Sequence[int]
+    starts: Sequence[int]
+    qlens: Sequence[int]
+    decode: bool                  # every sequence brings exactly one token
+    max_qlen: int
+    max_kv: int                   # longest cached length after this step
+
+
+def plan_key_of(part) -> Hashable:
+    key = getattr(part, "plan_key", None)
+    return key() if key else id(part)
+
+
+@dataclass
 class RunView:
     """What one entry of the run order sees of the cache: its group's geometry and its
     own K and V storage [pages, kv heads, PAGE, head_dim] (None when the mixer keeps no
@@ -103,11 +132,25 @@ class StepContext:
     max_qlen: int
     max_kv: int                   # longest cached length after this step
     host: Dict = field(default_factory=dict)    # host copies for parts that plan on the host
-    tiles: Optional[torch.Tensor] = None        # int32 [n, 2] (sequence row, first query) per tile of queries; prompts only
+    plans: Dict = field(default_factory=dict)   # plan key -> {name: int32 device tensor} (see plan_of)
+    marks: Optional[List] = None                # (label, CUDA event) after each stage, when the step is profiled
+    mark_detail: bool = True
 
     def state(self, name: str) -> torch.Tensor:
         """Fixed-size per-sequence state [slots, ...]; index it with ctx.slots."""
         return self.cache.states[name]
+
+    def plan_of(self, part) -> Dict[str, torch.Tensor]:
+        """The index arrays that `part.plan(batch)` laid out for this step, on the device."""
+        return self.plans.get(plan_key_of(part), {})
+
+    def mark(self, label: str) -> None:
+        """A time stamp on the current stream after the stage `label`; nothing unless the step is profiled
+        (the reference stamps its command buffer the same way, src/gpu/mod.rs:333-343)."""
+        if self.marks is not None and self.mark_detail:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.marks.append((label, ev))
 
 
 # Steps of at most this many tokens fold residual adds and norms into the products' epilogues (there the

@@ -12,6 +12,7 @@ class PreNormBlock:
     in 32-bit while it normalises."""
 
     norm_names = ("mixer", "feed_forward")
+    graph_class = ()
 
     def __init__(self, mixer, feed_forward, norms):
         self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
@@ -28,12 +29,14 @@ class PreNormBlock:
 
     def forward(self, stream: Stream, ctx: StepContext, run: RunView) -> None:
         h = self._norm("mixer", stream, ctx)
+        ctx.mark("norm")
         if getattr(self.mixer, "accepts_residual", False):
             term = self.mixer.forward(h, ctx, run, residual=stream)
         else:
             term = self.mixer.forward(h, ctx, run)
         self._add(stream, term)
         h = self._norm("feed_forward", stream, ctx)
+        ctx.mark("ff_norm")
         if getattr(self.feed_forward, "accepts_residual", False):
             term = self.feed_forward.forward(h, ctx, residual=stream)
         else:

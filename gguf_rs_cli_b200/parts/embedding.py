@@ -21,6 +21,8 @@ class Embedding(Part):
     def tensor_requests(self) -> List[TensorRequest]:
         return [TensorRequest(self.spec.tensors["weight"], (self.p["vocab_size"], self.p["hidden_size"]))]
 
+    graph_class = ()
+
     def load(self, store: WeightStore) -> None:
         self.weight = store.get(self.tensor_requests()[0])
 
@@ -44,14 +46,20 @@ class Embedding(Part):
 
 @register_head("lm_head")
 class LMHead(Part):
-    """params: vocab_size, hidden_size, tied_to (a tensor name or None).
-    tensors: weight [V, E], absent from a folder whose head is tied."""
+    """params: vocab_size, hidden_size, tied_to (the tensor that stands in when the folder has no
+    head matrix of its own, or None), tied (the configuration says the head is the embedding: the
+    random-weights mode then writes no matrix for it).
+    tensors: weight [V, E].  As in the reference, presence decides: a folder that has the matrix
+    uses it, one that lacks it uses `tied_to` (src/model/llama.rs:124)."""
 
     def tensor_requests(self) -> List[TensorRequest]:
         shape = (self.p["vocab_size"], self.p["hidden_size"])
+        init = None if self.p.get("tied") else "normal"
         if self.p.get("tied_to"):
-            return [TensorRequest(self.spec.tensors["weight"], shape, optional=True, fallback=self.p["tied_to"])]
-        return [TensorRequest(self.spec.tensors["weight"], shape)]
+            return [TensorRequest(self.spec.tensors["weight"], shape, optional=True, fallback=self.p["tied_to"], init=init)]
+        return [TensorRequest(self.spec.tensors["weight"], shape, init=init)]
+
+    graph_class = ()
 
     def load(self, store: WeightStore) -> None:
         self.proj = Linear(store.get(self.tensor_requests()[0]), name="logits")

@@ -44,6 +44,7 @@ class GatedMLP(Part):
         self.down = Linear(d, name="ff.down")
 
     accepts_residual = True
+    graph_class = ()              # the same launches every step
 
     def absorb_input_norm(self, weight: torch.Tensor) -> bool:
         """Multiplies the weight of the norm in front of this part into the gate/up matrix (only
@@ -64,4 +65,7 @@ class GatedMLP(Part):
             raise RuntimeError("gated_mlp: the activations given do not fit the fused product it was loaded for")
         else:
             kernels.swiglu(self.gate_up(h, ctx), act)
-        return self.down(act, ctx, residual=residual)
+        ctx.mark("gate_up")
+        term = self.down(act, ctx, residual=residual)
+        ctx.mark("down")
+        return term

@@ -18,11 +18,13 @@ class RMSNorm(Part):
     """params: size, eps.  tensors: weight [size]."""
 
     def tensor_requests(self) -> List[TensorRequest]:
-        return [TensorRequest(self.spec.tensors["weight"], (self.p["size"],))]
+        return [TensorRequest(self.spec.tensors["weight"], (self.p["size"],), init="ones")]
 
     def load(self, store: WeightStore) -> None:
         self.weight = store.get(self.tensor_requests()[0])
         self._ones = None
+
+    graph_class = ()
 
     def fold_weight(self) -> torch.Tensor:
         """The weight, for a consumer that multiplies it into the columns of its own matrix."""

@@ -13,6 +13,7 @@ tables become int32.
 """
 from __future__ import annotations
 
+import fnmatch
 from dataclasses import dataclass
 from typing import Dict, Iterable, List, Optional, Tuple
 
@@ -41,6 +42,9 @@ class TensorRequest:
     shape: Tuple[int, ...]
     optional: bool = False
     fallback: Optional[str] = None      # another tensor's name that is used when this one is absent
+    # what the random-weights mode writes for it: "normal" (N(0, 0.02)), "ones", "zeros", or None (nothing:
+    # the tensor is left out of the folder and its fallback stands in)
+    init: Optional[str] = "normal"
 
 
 class TensorSource:
@@ -111,7 +115,10 @@ class WeightStore:
         self._cache: Dict[str, torch.Tensor] = {}
 
     def check(self, requests: Iterable[TensorRequest], allow_unused: Iterable[str] = ()) -> None:
-        missing, wrong, asked = [], [], set(allow_unused)
+        """allow_unused: names or shell-style patterns of tensors a folder may hold although nobody asks
+        for them (buffers that older exports keep beside the parameters)."""
+        missing, wrong, asked = [], [], set()
+        patterns = list(allow_unused)
         for r in requests:
             name = r.name
             if not self.source.has(name):
@@ -126,7 +133,8 @@ class WeightStore:
             found = self.source.shape(name)
             if tuple(found) != tuple(r.shape):
                 wrong.append((name, tuple(r.shape), tuple(found)))
-        unexpected = sorted(n for n in self.source.names() if n not in asked)
+        unexpected = sorted(n for n in self.source.names()
+                            if n not in asked and not any(fnmatch.fnmatchcase(n, pat) for pat in patterns))
         if missing or unexpected or wrong:
             raise WeightError(sorted(set(missing)), unexpected, wrong, self.source.where)
 

@@ -2,9 +2,10 @@
 (config.json, model.safetensors), or to tensors in memory for a model too large to
 be worth writing.
 
-Matrices and biases are N(0, 0.02), norm weights are ones.  Every tensor has its own
-generator, seeded from (seed, tensor name), so a tensor's values do not depend on
-which other tensors exist.  The reference has no such mode (it only reads GGUF
+What is written for a tensor is what the part that asks for it says (`TensorRequest.init`):
+matrices and biases N(0, 0.02), norm weights ones.  Every tensor has its own generator,
+seeded from (seed, tensor name), so a tensor's values do not depend on which other
+tensors exist.  The reference has no such mode (it only reads GGUF
 files, src/model/llama.rs:83-153).
 """
 from __future__ import annotations
@@ -28,13 +29,14 @@ def _seed_of(seed: int, name: str) -> int:
     return int.from_bytes(h[:8], "little") & ((1 << 63) - 1)
 
 
-def _is_norm(name: str) -> bool:
-    return name.endswith("norm.weight") or name.endswith("layernorm.weight")
-
-
-def random_tensor(name: str, shape: Tuple[int, ...], seed: int, dtype=torch.bfloat16, device="cpu") -> torch.Tensor:
-    if _is_norm(name):
+def random_tensor(name: str, shape: Tuple[int, ...], seed: int, dtype=torch.bfloat16, device="cpu",
+                  init: str = "normal") -> torch.Tensor:
+    if init == "ones":
         return torch.ones(shape, dtype=dtype, device=device)
+    if init == "zeros":
+        return torch.zeros(shape, dtype=dtype, device=device)
+    if init != "normal":
+        raise ValueError(f"{name}: the random-weights mode knows no initial value {init!r} (normal, ones, zeros)")
     g = torch.Generator(device=device).manual_seed(_seed_of(seed, name))
     return (torch.randn(shape, generator=g, dtype=torch.float32, device=device) * STD).to(dtype)
 
@@ -47,14 +49,14 @@ def model_requests(raw_config: Dict) -> Iterable[TensorRequest]:
 
 
 def random_tensors(raw_config: Dict, seed: int, dtype=torch.bfloat16, device="cpu") -> Dict[str, torch.Tensor]:
-    """name -> tensor for every required tensor of the model (optional ones with a
-    fallback, such as a tied head, are left out)."""
+    """name -> tensor for every tensor the model's parts want written (a tied head asks for
+    none: its fallback stands in)."""
     out = {}
     for r in model_requests(raw_config):
-        if r.optional or r.fallback is not None:
+        if r.init is None:
             continue
         if r.name not in out:
-            out[r.name] = random_tensor(r.name, r.shape, seed, dtype, device)
+            out[r.name] = random_tensor(r.name, r.shape, seed, dtype, device, init=r.init)
     return out
 
 

@@ -5,7 +5,7 @@ import functools
 import torch
 
 from tests import plain_llama as P
-from tests.tiny import config
+from tests.tiny import config, qk_std
 
 # Largest |engine - plain| allowed, relative to the largest |plain| of the compared block.
 TOL = {"float32": 1e-4, "bfloat16": 2e-2}
@@ -23,8 +23,10 @@ def assert_close(got, want, dtype, what=""):
 @functools.lru_cache(maxsize=None)
 def plain_weights(name, seed=0, norm_noise=0.1):
     """Weights on the CPU, rounded to bfloat16 values so that both dtypes of the engine
-    hold exactly the same numbers as the plain reference."""
-    w = P.random_weights(config(name), seed, norm_noise=norm_noise)
+    hold exactly the same numbers as the plain reference.  q and k are scaled so that attention is
+    peaked: a wrong rotation, a dropped frequency scaling or a wrong head group then moves the logits by
+    many times the bfloat16 tolerance (tests/test_plain.py shows it)."""
+    w = P.random_weights(config(name), seed, norm_noise=norm_noise, qk_std=qk_std(config(name)))
     return {k: v.to(torch.bfloat16).to(torch.float32) for k, v in w.items()}
 
 

@@ -303,14 +303,17 @@ def weight_shapes(cfg):
     return s
 
 
-def random_weights(cfg, seed, std=0.02, norm_noise=0.0):
+def random_weights(cfg, seed, std=0.02, norm_noise=0.0, qk_std=None):
     """N(0, std) matrices, norm weights of one (+ noise when asked, so that a test sees
-    a norm weight that is ignored), biases N(0, std)."""
+    a norm weight that is ignored), biases N(0, std).  qk_std: the deviation of the q and k
+    matrices, for tests that need attention to be peaked (see tests/tiny.py)."""
     g = torch.Generator().manual_seed(seed)
     w = {}
     for name, shape in weight_shapes(cfg).items():
         if name.endswith("norm.weight") or name.endswith("layernorm.weight"):
             w[name] = torch.ones(shape) + norm_noise * torch.randn(shape, generator=g)
+        elif qk_std and (name.endswith("q_proj.weight") or name.endswith("k_proj.weight")):
+            w[name] = torch.randn(shape, generator=g) * qk_std
         else:
             w[name] = torch.randn(shape, generator=g) * std
     return w

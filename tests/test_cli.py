@@ -20,9 +20,10 @@ def test_option_names_and_defaults_are_the_reference_s():
                                    "1", "--rep-penalty", "1", "-c", "100", "--seed", "7", "--stats", "--gpu", "--debug-gpu"])
     assert a.prompts == [[4, 5], [6]] and (a.max_tokens, a.temperature, a.ctx_len, a.seed) == (3, 0.0, 100, 7) and a.stats
     assert parse_ids("1, 2,3") == [1, 2, 3]
-    assert a.stop_ids is None                                      # the model's own end tokens
-    assert build_parser().parse_args(["-m", "f", "-p", "1", "--stop-ids", ""]).stop_ids == []      # none: run to --max-tokens
-    assert build_parser().parse_args(["-m", "f", "-p", "1", "--stop-ids", "2,7"]).stop_ids == [2, 7]
+    assert a.stop_ids is None and not a.no_eos and a.debug_gpu      # the model's own end tokens
+    assert build_parser().parse_args(["-m", "f", "-p", "1", "--stop-ids", ""]).stop_ids == []
+    b = build_parser().parse_args(["-m", "f", "-p", "1", "--stop-ids", "2,7", "--no-eos", "--profile"])
+    assert b.stop_ids == [2, 7] and b.no_eos and b.debug_gpu
     with pytest.raises(SystemExit):
         build_parser().parse_args(["-p", "1"])                     # no model
     with pytest.raises(SystemExit):
@@ -35,7 +36,7 @@ def test_cli_generates_what_the_entry_point_generates(tmp_path):
     from gguf_rs_cli_b200.weights import write_random_model
     folder = write_random_model(str(tmp_path / "m"), config("B"), seed=1, dtype=torch.bfloat16)
     prompts = [[5, 6, 7], [300, 2, 9, 11, 80]]
-    args = ["-n", "6", "-t", "0.9", "--seed", "5", "--dtype", "float32", "--stop-ids", "383", "--stats", "--debug-gpu"]
+    args = ["-n", "6", "-t", "0.9", "--seed", "5", "--dtype", "float32", "--stop-ids", "383", "--no-eos", "--stats", "--debug-gpu"]
     cmd = [sys.executable, os.path.join(ROOT, "bin", "gguf-rs-cli"), "-m", folder] + args
     for p in prompts:
         cmd += ["-p", ",".join(map(str, p))]
@@ -46,6 +47,15 @@ def test_cli_generates_what_the_entry_point_generates(tmp_path):
                     stop_token_ids=[383])
     assert got == want and all(len(g) == 6 for g in got)
     assert "[Stats] prefill: 8 tok in" in r.stderr and "generated: 12 tok" in r.stderr and "[GPU]" in r.stderr
+    assert "EOS tokens: [383]" in r.stderr
+    # --debug-gpu: one line per step with a stamp after every stage, as the reference prints its timestamps
+    lines = [l for l in r.stderr.splitlines() if l.startswith("[GPU step")]
+    assert len(lines) == 7 and lines[0].startswith("[GPU step of 8 tokens]") and lines[1].startswith("[GPU step of 2 tokens]")
+    for stage in ("embed", "norm", "qkv", "attention", "o", "ff_norm", "gate_up", "down", "layers", "head", "sample", "total GPU"):
+        assert f"[{stage}: " in lines[1], (stage, lines[1])
+    # without --no-eos the model's end tokens (3 and 5 here) are joined with --stop-ids
+    r2 = subprocess.run([a for a in cmd if a != "--no-eos"], capture_output=True, text=True)
+    assert r2.returncode == 0 and "EOS tokens: [3, 5, 383]" in r2.stderr
     # a config for random weights, and a loud error for a broken folder
     cfg_path = tmp_path / "c.json"
     cfg_path.write_text(json.dumps(config("A")))

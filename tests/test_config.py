@@ -94,9 +94,23 @@ def test_spec_is_data_layer_by_layer():
     assert l0.mixer.params["num_kv_heads"] == 2 and l0.mixer.params["window"] is None
     assert l0.norms["mixer"].params["eps"] == 1e-5 and l0.position.params["theta"] == 10000.0
     assert l0.mixer.tensors["q"] == "model.layers.0.self_attn.q_proj.weight"
-    assert spec.head.params["tied_to"] is None
+    # presence decides (src/model/llama.rs:124): the head of every Llama names its stand-in, and the flag
+    # only says whether random weights hold a matrix for it
+    assert spec.head.params["tied_to"] == "model.embed_tokens.weight" and spec.head.params["tied"] is False
     _, cfg_b = load_config(config("B"))
-    assert arch.build_spec(cfg_b).head.params["tied_to"] == "model.embed_tokens.weight"
+    assert arch.build_spec(cfg_b).head.params["tied"] is True
+    assert spec.ignored_tensors == ["*.rotary_emb.inv_freq"]
+
+
+def test_head_dim_must_divide_when_it_is_not_given():
+    raw = config("A")
+    del raw["head_dim"]
+    assert load_config(raw)[1].head_dim == 16
+    raw["num_attention_heads"], raw["num_key_value_heads"] = 6, 2
+    with pytest.raises(ConfigError, match="not a multiple of num_attention_heads"):
+        load_config(raw)
+    raw["head_dim"] = 16                                      # given: any width goes
+    assert load_config(raw)[1].head_dim == 16
 
 
 def test_schedule_validation():

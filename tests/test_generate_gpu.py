@@ -118,6 +118,35 @@ def test_graph_and_eager_decode_agree():
     assert outs[0] == outs[2] and outs[1] == outs[3]
 
 
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_bfloat16_sampling_options_through_captured_graphs(name):
+    """top_k, top_p and the repetition penalty (the reference's defaults) in bfloat16: the captured decode
+    step (sampling inside the graph, its recent-token ring in the per-sequence state) gives the tokens of steps
+    launched one by one, also for a second batch in used slots; and every token chosen is one that the plain
+    sampler could choose from the plain logits (inside its top_k by the margin of bfloat16)."""
+    from gguf_rs_cli_b200.engine.backend import EngineBackend
+    from gguf_rs_cli_b200.engine.generate import generate_ids
+    from gguf_rs_cli_b200.sampling import SamplingParams
+    cfg, w = config(name), plain_weights(name)
+    prompts = [tokens_of(name, n, 400 + n) for n in (5, 66, 31)]
+    params = SamplingParams(temperature=0.7, top_k=40, top_p=0.9, rep_penalty=1.1, seed=11)
+    outs = []
+    for graphs in (False, True):
+        eng = new_engine(name, "bfloat16", n_tokens=64 * 8, n_slots=4)
+        backend = EngineBackend(eng, use_graphs=graphs)
+        outs.append([generate_ids(backend, prompts, 14, params, []) for _ in range(2)])
+        assert outs[-1][0] == outs[-1][1], "the second batch reuses slots whose ring of recent tokens must start empty"
+    assert outs[0] == outs[1]
+    for p, g in zip(prompts, outs[1][0]):
+        seq, recent = list(p), []
+        for tok in g:
+            logits = P.apply_rep_penalty(P.forward(cfg, w, seq)[-1], recent, 1.1)
+            kth = float(torch.topk(logits, 40).values[-1])
+            assert float(logits[tok]) >= kth - 2e-2 * float(logits.abs().max()), f"token {tok} at length {len(seq)} is outside top_k"
+            seq.append(tok)
+            recent = (recent + [tok])[-64:]
+
+
 @pytest.mark.parametrize("name", ["B", "C"])
 def test_decode_steps_updated_in_place_cross_pages(name):
     """While a batch goes on token by token, the captured step's index arrays are only

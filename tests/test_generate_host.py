@@ -106,6 +106,28 @@ def test_zero_max_tokens_and_errors():
         generate_ids(Scripted(), [[1]], 1, SamplingParams(top_p=0.0))
 
 
+def test_a_failing_step_or_callback_gives_every_slot_back():
+    class Failing(Scripted):
+        def run(self, slots, feeds, keys, params):
+            if len([e for e in self.log if e[0] == "run"]) == 2:
+                raise RuntimeError("the device gave up")
+            return super().run(slots, feeds, keys, params)
+
+    b = Failing(n_slots=3)
+    with pytest.raises(RuntimeError, match="gave up"):
+        generate_ids(b, [[10], [20], [30]], max_tokens=5, stop_token_ids=[21])       # request 1 has left before the failure
+    assert not b.state and b.free == [0, 1, 2]
+
+    def boom(i, t):
+        raise KeyError("callback")
+
+    b = Scripted(n_slots=2)
+    with pytest.raises(KeyError):
+        generate_ids(b, [[10], [20]], max_tokens=5, on_token=boom)
+    assert not b.state and b.free == [0, 1]
+    assert generate_ids(b, [[10], [20]], max_tokens=1) == [[11], [21]]               # and the backend is usable again
+
+
 def test_streaming_callback_and_keys():
     seen = []
     b = Scripted(n_slots=2)

@@ -8,7 +8,7 @@ from tests.gpu_util import assert_close, new_engine, plain_logits, tokens_of
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["A", "B", "C"]
+NAMES = ["A", "B", "C", "D"]
 
 
 def entry(slot, tokens, want):
@@ -95,6 +95,107 @@ def test_continuation_in_pieces_and_nothing_wanted(dtype):
     got = eng.step([entry(s, toks[63:], range(n - 63))])
     assert_close(got, want[63:], dtype, "third piece across a page boundary")
     eng.close(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_a_new_prompt_joins_sequences_that_are_decoding(name, dtype):
+    """One step that mixes two sequences going on by one token (at positions past a page boundary) with a
+    prompt that starts: the tiled prompt kernels (tensor cores at head sizes 64 and 128) then see rows of one
+    query at start > 0 beside a whole prompt.  Every entry's logits are checked, before, in and after the
+    mixed step."""
+    eng = new_engine(name, dtype, n_tokens=64 * 12, n_slots=4)
+    lens = {"a": 150, "b": 75, "c": 49}
+    toks = {r: tokens_of(name, n, 40 + n) for r, n in lens.items()}
+    want = {r: plain_logits(name, n, 40 + n) for r, n in lens.items()}
+    slot = {r: eng.open() for r in "ab"}
+    fed = {"a": 140, "b": 66}
+    got = eng.step([entry(slot[r], toks[r][:fed[r]], [fed[r] - 1]) for r in "ab"])
+    for i, r in enumerate("ab"):
+        assert_close(got[i], want[r][fed[r] - 1], dtype, f"{name} prompt {r}")
+    for _ in range(2):
+        got = eng.step([entry(slot[r], [toks[r][fed[r]]], [0]) for r in "ab"])
+        for i, r in enumerate("ab"):
+            assert_close(got[i], want[r][fed[r]], dtype, f"{name} {r} at {fed[r]}")
+            fed[r] += 1
+    slot["c"] = eng.open()
+    got = eng.step([entry(slot["a"], [toks["a"][fed["a"]]], [0]), entry(slot["c"], toks["c"][:45], range(45)),
+                    entry(slot["b"], [toks["b"][fed["b"]]], [0])])
+    assert_close(got[0], want["a"][fed["a"]], dtype, f"{name} a in the mixed step")
+    assert_close(got[1:46], want["c"][:45], dtype, f"{name} the joining prompt")
+    assert_close(got[46], want["b"][fed["b"]], dtype, f"{name} b in the mixed step")
+    fed["a"] += 1
+    fed["b"] += 1
+    fed["c"] = 45
+    for _ in range(4):
+        got = eng.step([entry(slot[r], [toks[r][fed[r]]], [0]) for r in "abc"])
+        for i, r in enumerate("abc"):
+            assert_close(got[i], want[r][fed[r]], dtype, f"{name} {r} at {fed[r]} after the mixed step")
+            fed[r] += 1
+    for r in "abc":
+        eng.close(slot[r])
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_float32_logits_do_not_depend_on_the_cut_to_the_bit(name):
+    """In 32-bit mode every product is one thread's sum in ascending k and attention runs its blocks in a fixed
+    order, so whole prompts, tokens one by one and unequal batches give the same bits."""
+    eng = new_engine(name, "float32", n_tokens=64 * 10, n_slots=4)
+    n = 80
+    toks = tokens_of(name, n, 5)
+    other = tokens_of(name, 60, 6)
+    s = eng.open()
+    whole = eng.step([entry(s, toks, range(n))]).clone()
+    eng.close(s)
+    # the last 32 one by one, in a slot used before, beside another sequence
+    o, s = eng.open(), eng.open()
+    head = eng.step([entry(o, other[:20], [19]), entry(s, toks[:n - 32], range(n - 32))])
+    assert torch.equal(head[1:], whole[:n - 32]), "a prompt beside another one"
+    for i in range(n - 32, n):
+        got = eng.step([entry(s, [toks[i]], [0]), entry(o, [other[20 + i - (n - 32)]], [])] if i % 2 else [entry(s, [toks[i]], [0])])
+        assert torch.equal(got[0], whole[i]), f"position {i} decoded"
+    eng.close(s)
+    eng.close(o)
+    # in three pieces cut inside a page
+    s = eng.open()
+    a = eng.step([entry(s, toks[:7], range(7))]).clone()
+    b = eng.step([entry(s, toks[7:70], range(63))]).clone()
+    c = eng.step([entry(s, toks[70:], range(10))]).clone()
+    assert torch.equal(torch.cat([a, b, c]), whole)
+    eng.close(s)
+
+
+def test_captured_graphs_survive_a_later_large_step():
+    """Decode graphs captured early keep the addresses of the scratch memory that split products and split
+    attention share.  A later step with larger needs (a prompt of a few hundred tokens at the benchmark's layer
+    width) must not move that memory under them: the tokens decoded afterwards through the old graphs equal
+    those of steps that are launched one by one."""
+    from gguf_rs_cli_b200.api import from_random
+    from gguf_rs_cli_b200.engine.backend import EngineBackend
+    from gguf_rs_cli_b200.engine.generate import generate_ids
+    from gguf_rs_cli_b200.engine.step import Engine
+    from gguf_rs_cli_b200.sampling import SamplingParams
+    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 1, "hidden_size": 4096,
+           "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336,
+           "vocab_size": 4096, "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 1024,
+           "tie_word_embeddings": True, "hidden_act": "silu"}
+    model = from_random(cfg, seed=3, dtype="bfloat16", device="cuda:0").model
+    g = torch.Generator().manual_seed(2)
+    short = [torch.randint(0, 4096, (10,), generator=g).tolist()]
+    long = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (200, 333)]
+    params = SamplingParams(temperature=0.0)
+    outs = []
+    for graphs in (True, False):
+        backend = EngineBackend(Engine(model, n_tokens=64 * 16, n_slots=4, max_len=1024), use_graphs=graphs)
+        first = generate_ids(backend, short, 6, params, [])          # captures the graph of one sequence
+        generate_ids(backend, long, 3, params, [])                   # a step of 533 tokens, then graphs of two sequences
+        again = generate_ids(backend, short, 6, params, [])          # replays the first graph
+        assert first == again
+        outs.append((first, again))
+    assert outs[0] == outs[1]
+    del model
+    torch.cuda.empty_cache()
 
 
 def test_step_errors_launch_nothing():

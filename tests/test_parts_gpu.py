@@ -473,3 +473,158 @@ def test_toy_architecture_with_routed_experts_and_a_position_encoding_of_its_own
     for s in slots:
         eng.close(s)
     eng.cache.check()
+
+
+# ------------------------------------------ hooks: planning on the host, and whether a step may be captured
+def test_a_mixer_without_hooks_generates_under_captured_graphs_untouched():
+    """The running-mean mixer above computes with host values every step and says nothing about CUDA graphs:
+    the backend then never captures a step that contains it, and generation with graphs switched on gives
+    the plain result."""
+    from gguf_rs_cli_b200.api import _build
+    from gguf_rs_cli_b200.engine.backend import EngineBackend
+    from gguf_rs_cli_b200.engine.generate import generate_ids
+    from gguf_rs_cli_b200.engine.step import Engine
+    from gguf_rs_cli_b200.sampling import SamplingParams
+    from gguf_rs_cli_b200.weights import TensorSource
+    register_toys()
+    w = toy_weights()
+    model = _build(dict(TOY), TensorSource(tensors={k: v.to(torch.bfloat16) for k, v in w.items()}, where="toy"),
+                   "float32", DEV).model
+    assert not model.capturable
+    g = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(0, 256, (n,), generator=g).tolist() for n in (9, 30)]
+    want = []
+    for p in prompts:
+        seq = list(p)
+        for _ in range(6):
+            seq.append(int(toy_plain_forward(w, seq)[-1].argmax()))
+        want.append(seq[len(p):])
+    backend = EngineBackend(Engine(model, n_tokens=64 * 8, n_slots=2, max_len=512, max_step_tokens=128), use_graphs=True)
+    assert generate_ids(backend, prompts, 6, SamplingParams(temperature=0.0), []) == want
+    assert backend._graphs == {}
+
+
+def register_shift_toy():
+    """A mixer that plans on the host and may be captured: it adds a projection of the row in front of each token
+    (the last row of the step before for a sequence's first token, kept as fixed-size state).  Which row that
+    is, and where each sequence's last row lies, it lays out on the host in `plan`; the arrays travel with the
+    step's own index arrays.  Its graph class is the number of sequences, which fixes the arrays' sizes."""
+    from gguf_rs_cli_b200.config import register_architecture
+    from gguf_rs_cli_b200.config.llama import LlamaConfig, build_llama_spec
+    from gguf_rs_cli_b200.config.specs import LayerSpec, ModelSpec, PartSpec
+    from gguf_rs_cli_b200.parts import MIXERS, Part, register_mixer
+    from gguf_rs_cli_b200.weights import TensorRequest
+    if "shift" in MIXERS.kinds():
+        return
+
+    @register_mixer("shift")
+    class Shift(Part):
+        def __init__(self, spec, dtype, device, position=None):
+            super().__init__(spec, dtype, device)
+
+        def kv_spec(self):
+            return None
+
+        def state_spec(self):
+            return {"last": ((self.p["hidden_size"],), "float32")}
+
+        def tensor_requests(self):
+            E = self.p["hidden_size"]
+            return [TensorRequest(self.spec.tensors["proj"], (E, E))]
+
+        def load(self, store):
+            self.proj = store.get(self.tensor_requests()[0]).float()
+
+        def plan(self, batch):
+            prev, last, t0 = [], [], 0
+            for n in batch.qlens:
+                prev += [-1] + list(range(t0, t0 + n - 1))
+                t0 += n
+                last.append(t0 - 1)
+            return {"prev": prev, "last": last}
+
+        def graph_class(self, batch):
+            return len(batch.slots)
+
+        def forward(self, h, ctx, run):
+            plan = ctx.plan_of(self)
+            prev, last = plan["prev"].long(), plan["last"].long()
+            n_tok, n_seq = prev.numel(), last.numel()             # real tokens and sequences (the rest is padding)
+            state = ctx.state(f"run{run.index}.last")
+            slots = ctx.slots[:n_seq].long()
+            hf = h[:n_tok].float()
+            before = state[slots][ctx.seq_of[:n_tok].long()]       # what each token's sequence left behind
+            rows = torch.where((prev < 0)[:, None], before, hf[prev.clamp(min=0)])
+            state.index_copy_(0, slots, hf[last])
+            out = torch.zeros(h.shape, dtype=torch.float32, device=h.device)
+            out[:n_tok] = rows @ self.proj.t()
+            return out.to(ctx.dtype)
+
+    @dataclass(frozen=True)
+    class ShiftConfig:
+        llama: LlamaConfig
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(LlamaConfig.from_dict(raw))
+
+    def build_shift_spec(cfg: ShiftConfig) -> ModelSpec:
+        base = build_llama_spec(cfg.llama)
+        layers = list(base.layers)
+        ls = layers[1]
+        layers[1] = LayerSpec(ls.block, PartSpec("shift", {"hidden_size": cfg.llama.hidden_size},
+                                                 {"proj": "model.layers.1.shift.proj.weight"}), ls.feed_forward, ls.norms, None)
+        return ModelSpec(**{**base.__dict__, "architecture": "ShiftForCausalLM", "layers": layers})
+
+    register_architecture("ShiftForCausalLM", ShiftConfig, build_shift_spec)
+
+
+def test_a_mixer_that_plans_on_the_host_is_captured_and_replanned_every_step():
+    from gguf_rs_cli_b200.api import _build
+    from gguf_rs_cli_b200.engine.backend import EngineBackend
+    from gguf_rs_cli_b200.engine.generate import generate_ids
+    from gguf_rs_cli_b200.engine.step import Engine
+    from gguf_rs_cli_b200.sampling import SamplingParams
+    from gguf_rs_cli_b200.weights import TensorSource
+    register_shift_toy()
+    raw = {**config("A"), "architectures": ["ShiftForCausalLM"], "model_type": "shift", "num_hidden_layers": 3}
+    w = P.random_weights({**raw, "architectures": ["LlamaForCausalLM"]}, 5, std=0.05, norm_noise=0.1)
+    for n in ("q_proj", "k_proj", "v_proj", "o_proj"):
+        del w[f"model.layers.1.self_attn.{n}.weight"]
+    w["model.layers.1.shift.proj.weight"] = torch.randn(64, 64, generator=torch.Generator().manual_seed(6)) * 0.3
+    w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+
+    def plain(tokens):
+        T, eps, inv = len(tokens), raw["rms_norm_eps"], P.inv_freq_table(raw)
+        x = P.embedding(w["model.embed_tokens.weight"], tokens)
+        for l in range(3):
+            p = f"model.layers.{l}."
+            xn = P.rmsnorm(x, w[p + "input_layernorm.weight"], eps)
+            if l == 1:
+                shifted = torch.cat([torch.zeros(1, 64), xn[:-1]])
+                x = x + P.linear(shifted, w[p + "shift.proj.weight"])
+            else:
+                x = P.layer(raw, w, l, x, torch.arange(T), inv)            # a whole plain layer
+                continue
+            xn = P.rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps)
+            x = x + P.feed_forward(xn, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        return P.linear(P.rmsnorm(x, w["model.norm.weight"], eps), w["lm_head.weight"])
+
+    model = _build(raw, TensorSource(tensors={k: v.to(torch.bfloat16) for k, v in w.items()}, where="shift"), "float32", DEV).model
+    assert model.capturable and len(model.planners) == 2          # the attention layers share one plan, the toy has its own
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 256, (n,), generator=g).tolist() for n in (7, 66, 20)]
+    want = []
+    for p in prompts:
+        seq = list(p)
+        for _ in range(8):
+            seq.append(int(plain(seq)[-1].argmax()))
+        want.append(seq[len(p):])
+    for graphs in (False, True):
+        backend = EngineBackend(Engine(model, n_tokens=64 * 8, n_slots=4, max_len=128), use_graphs=graphs)
+        for _ in range(2):                                          # the second batch uses the slots, and the graphs, again
+            assert generate_ids(backend, prompts, 8, SamplingParams(temperature=0.0), []) == want
+        if graphs:
+            captured = [dg for dg in backend._graphs.values() if dg.graph is not None]
+            assert captured and all(dg.plan_words == 2 * 3 for dg in captured)
+            assert {key[1][-1] for key in backend._graphs} == {3}  # the toy's class is part of every graph's key

@@ -1,10 +1,11 @@
 """The plain implementation against itself: formulas that can be checked by hand."""
 import math
 
+import pytest
 import torch
 
 from tests import plain_llama as P
-from tests.tiny import config
+from tests.tiny import config, qk_std
 
 
 def test_rmsnorm_by_hand():
@@ -82,3 +83,97 @@ def test_generate_stops():
     assert len(out) == 4
     assert P.generate(cfg, w, [5, 6, 7], max_tokens=4, stop=[out[2]]) == out[:2]
     assert P.generate(cfg, w, [5, 6, 7], max_tokens=40, max_len=6) == out[:2]
+
+
+def test_softmax_silu_and_linear_by_hand():
+    """src/math/ops.rs:5-11 and src/tensor/dequant.rs:315-317 on numbers small enough to do by hand."""
+    s = P.softmax(torch.tensor([[0.0, math.log(3.0)]]))
+    assert torch.allclose(s, torch.tensor([[0.25, 0.75]]))
+    big = P.softmax(torch.tensor([[1000.0, 1000.0]]))              # the maximum is subtracted first
+    assert torch.allclose(big, torch.tensor([[0.5, 0.5]]))
+    assert abs(float(P.silu(torch.tensor(0.0)))) == 0.0
+    assert abs(float(P.silu(torch.tensor(2.0))) - 2.0 / (1.0 + math.exp(-2.0))) < 1e-7
+    w = torch.tensor([[1.0, 2.0], [3.0, 4.0], [5.0, 6.0]])         # [out, in]: y[i] = sum_j w[i, j] x[j]
+    y = P.linear(torch.tensor([[1.0, -1.0]]), w, torch.tensor([0.5, 0.0, 0.0]))
+    assert y.tolist() == [[-0.5, -1.0, -1.0]]
+    ff = P.feed_forward(torch.tensor([[1.0, 0.0]]), torch.tensor([[2.0, 0.0]]), torch.tensor([[3.0, 0.0]]), torch.tensor([[1.0], [2.0]]))
+    a = 2.0 / (1.0 + math.exp(-2.0)) * 3.0                         # silu(gate) * up, then down
+    assert torch.allclose(ff, torch.tensor([[a, 2 * a]]))
+
+
+def test_rmsnorm_has_eps_inside_the_root_and_rope_keeps_lengths():
+    x = torch.zeros(1, 4)
+    assert torch.equal(P.rmsnorm(x, torch.ones(4), 1e-5), x)        # 0 / sqrt(0 + eps)
+    y = P.rmsnorm(torch.full((1, 4), 1e-3), torch.ones(4), 1e-6)    # mean square = eps: x / sqrt(2 eps)
+    assert torch.allclose(y, torch.full((1, 4), 1e-3 / math.sqrt(2e-6)))
+    f = P.inv_freq_table({"hidden_size": 16, "num_attention_heads": 2, "rope_theta": 100.0})
+    q = torch.randn(3, 2, 8, generator=torch.Generator().manual_seed(0))
+    r = P.rope(q, torch.tensor([0, 5, 77]), f)
+    assert torch.allclose(r.norm(dim=-1), q.norm(dim=-1), atol=1e-5)
+    # relative position only: <rope(q, m), rope(k, n)> depends on m - n
+    k = torch.randn(1, 2, 8, generator=torch.Generator().manual_seed(1))
+    d1 = (P.rope(q[:1], torch.tensor([9]), f) * P.rope(k, torch.tensor([4]), f)).sum()
+    d2 = (P.rope(q[:1], torch.tensor([25]), f) * P.rope(k, torch.tensor([20]), f)).sum()
+    assert abs(float(d1 - d2)) < 1e-4
+
+
+def test_sampler_order_of_steps():
+    """src/sampler.rs:35-79: penalty first, then temperature, then top_k on the scaled logits, softmax over
+    the survivors, top_p on the descending order, renormalise, walk."""
+    logits = torch.tensor([2.0, 1.0, 0.0, -1.0])
+    # penalty before greedy: token 0 is halved and no longer the maximum
+    assert P.sample(torch.tensor([2.0, 1.5, 0.0]), 0.0, 0, 1.0, 2.0, [0], 0.0) == 1
+    # top_k 2 keeps tokens 0 and 1 with p = e/(1+e), 1/(1+e); u just above the first mass picks token 1
+    p0 = math.e / (1 + math.e)
+    assert P.sample(logits, 1.0, 2, 1.0, 1.0, [], p0 - 1e-3) == 0 and P.sample(logits, 1.0, 2, 1.0, 1.0, [], p0 + 1e-3) == 1
+    # temperature divides before the softmax: at T = 0.5 the two survivors weigh e^2 : 1
+    p0 = math.exp(2) / (1 + math.exp(2))
+    assert P.sample(logits, 0.5, 2, 1.0, 1.0, [], p0 - 1e-3) == 0 and P.sample(logits, 0.5, 2, 1.0, 1.0, [], p0 + 1e-3) == 1
+    # top_p cuts the smallest prefix whose mass reaches it (here 0.644 + 0.237 >= 0.8) and renormalises
+    full = torch.softmax(logits, 0)
+    cut = float(full[0] / (full[0] + full[1]))
+    assert P.sample(logits, 1.0, 0, 0.8, 1.0, [], cut + 1e-3) == 1 and P.sample(logits, 1.0, 0, 0.8, 1.0, [], 0.999) == 1
+    # a uniform at the very top returns the last survivor
+    assert P.sample(logits, 1.0, 0, 1.0, 1.0, [], 1.0) == 3
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_the_test_weights_show_a_wrong_rotation_scaling_or_grouping(name, monkeypatch):
+    """What the engine is compared against must move when the model is wrong.  With the weights the GPU tests
+    use (q and k scaled so that attention is peaked), leaving the rotation out, dropping the frequency
+    scaling, or reading the wrong KV head each move the logits by at least five times the bfloat16
+    tolerance of those tests (2e-2 of the largest logit)."""
+    cfg = config(name)
+    w = P.random_weights(cfg, 0, norm_noise=0.1, qk_std=qk_std(cfg))
+    w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, cfg["vocab_size"], (90,), generator=g).tolist()
+    base = P.forward(cfg, w, toks)
+    ref = float(base.abs().max())
+    need = 5 * 2e-2
+
+    def moved(other):
+        return float((other - base).abs().max()) / ref
+
+    with monkeypatch.context() as m:
+        m.setattr(P, "rope", lambda x, positions, inv_freq: x)
+        assert moved(P.forward(cfg, w, toks)) >= need, "no rotation"
+    if cfg.get("rope_scaling"):
+        assert moved(P.forward(dict(cfg, rope_scaling=None), w, toks)) >= need, "no frequency scaling"
+    if P.kv_heads_of(cfg) > 1:
+        real = P.attention
+
+        def wrong_group(q, k, v, window=None):
+            nh, nkv = q.shape[1], k.shape[1]
+            order = [h % nkv for h in range(nh)]                 # head h reads KV head h % nkv instead of h // (nh/nkv)
+            return real(q, k[:, order, :], v[:, order, :], window)
+
+        with monkeypatch.context() as m:
+            m.setattr(P, "attention", wrong_group)
+            assert moved(P.forward(cfg, w, toks)) >= need, "wrong head group"
+    # and the plain N(0, 0.02) weights would not have shown the rotation (which is why they are not used)
+    flat = {k: v.to(torch.bfloat16).float() for k, v in P.random_weights(cfg, 0, norm_noise=0.1).items()}
+    with monkeypatch.context() as m:
+        flat_base = P.forward(cfg, flat, toks)
+        m.setattr(P, "rope", lambda x, positions, inv_freq: x)
+        assert float((P.forward(cfg, flat, toks) - flat_base).abs().max()) / float(flat_base.abs().max()) < need

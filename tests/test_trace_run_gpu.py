@@ -10,7 +10,7 @@ import torch
 
 from tests import plain_llama as P
 from tests.gpu_util import TOL
-from tests.tiny import config
+from tests.tiny import config, qk_std
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -44,11 +44,19 @@ class Replay:
 
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
-    from gguf_rs_cli_b200.weights import TensorSource, write_random_model
+    """Model folders in a temporary place: A as the random-weights mode writes it, B and D with q and k scaled
+    so that attention is peaked (see tests/tiny.py), written by the package's own writer."""
+    from gguf_rs_cli_b200.weights import TensorSource, write_random_model, write_safetensors
     out = {}
-    for name in ("A", "B"):
+    for name in ("A", "B", "D"):
         folder = str(tmp_path_factory.mktemp(f"model{name}"))
-        write_random_model(folder, config(name), seed=3, dtype=torch.bfloat16)
+        if name == "A":
+            write_random_model(folder, config(name), seed=3, dtype=torch.bfloat16)
+        else:
+            w = P.random_weights(config(name), 3, norm_noise=0.1, qk_std=qk_std(config(name)))
+            with open(os.path.join(folder, "config.json"), "w") as f:
+                json.dump(config(name), f)
+            write_safetensors(os.path.join(folder, "model.safetensors"), [(n, t.to(torch.bfloat16)) for n, t in w.items()])
         src = TensorSource.from_folder(folder)
         out[name] = (folder, {n: src.get(n).float() for n in src.names()})
     return out
@@ -62,7 +70,7 @@ def close(got, want, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_replay_whole_one_by_one_and_unequal_batches(name, dtype, folders, tmp_path):
     folder, w = folders[name]
     cfg = config(name)

@@ -84,8 +84,10 @@ def test_names_and_shapes_match_the_plain_reference():
     for name in "AB":
         raw = config(name)
         want = plain_llama.weight_shapes(raw)
-        got = {r.name: tuple(r.shape) for r in requests_of(raw) if not (r.optional and r.fallback)}
+        got = {r.name: tuple(r.shape) for r in requests_of(raw) if r.init is not None}       # what random weights hold
         assert got == {k: tuple(v) for k, v in want.items()}
+        inits = {r.name: r.init for r in requests_of(raw)}
+        assert all((init == "ones") == (name.endswith("norm.weight")) for name, init in inits.items() if init)
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes():
@@ -117,9 +119,83 @@ def test_tied_head_falls_back_to_the_embedding():
     head = [r for r in reqs if r.name == "lm_head.weight"][0]
     emb = [r for r in reqs if r.name == "model.embed_tokens.weight"][0]
     assert store.get(head) is store.get(emb)
-    raw["tie_word_embeddings"] = False           # now the head is required
-    with pytest.raises(WeightError, match="lm_head.weight"):
-        WeightStore(TensorSource(tensors=w), torch.float32, "cpu").check(requests_of(raw))
+    # presence decides, as in the reference (src/model/llama.rs:124): an untied configuration whose folder
+    # has no head matrix uses the embedding too, and a tied one whose folder has a matrix uses that
+    raw["tie_word_embeddings"] = False
+    WeightStore(TensorSource(tensors=w), torch.float32, "cpu").check(requests_of(raw))
+    assert "lm_head.weight" in random_tensors(raw, 0) and "lm_head.weight" not in random_tensors(config("B"), 0)
+    w["lm_head.weight"] = torch.zeros(384, 96)
+    store = WeightStore(TensorSource(tensors=w), torch.float32, "cpu")
+    store.check(requests_of(config("B")))
+    assert store.get(head) is not store.get(emb)
+
+
+def test_buffers_of_older_exports_are_ignored_other_extras_are_not():
+    raw = config("A")
+    w = plain_llama.random_weights(raw, 0)
+    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    arch, cfg = load_config(raw)
+    spec = arch.build_spec(cfg)
+    store = WeightStore(TensorSource(tensors=w, where="test"), torch.float32, "cpu")
+    store.check(tensor_requests(spec), allow_unused=spec.ignored_tensors)
+    with pytest.raises(WeightError, match="rotary_emb.inv_freq"):
+        store.check(tensor_requests(spec))
+    w["model.layers.0.self_attn.rotary_emb.other"] = torch.zeros(8)
+    with pytest.raises(WeightError, match="rotary_emb.other"):
+        WeightStore(TensorSource(tensors=w), torch.float32, "cpu").check(tensor_requests(spec), allow_unused=spec.ignored_tensors)
+
+
+def write_shards(folder, tensors, split_at, twice=()):
+    """model.safetensors.index.json and two shards; names in `twice` are stored in both."""
+    names = sorted(tensors)
+    a, b = names[:split_at], names[split_at:]
+    files = {"model-00001-of-00002.safetensors": a + [n for n in twice if n not in a],
+             "model-00002-of-00002.safetensors": b + [n for n in twice if n not in b]}
+    weight_map = {}
+    for fname, ns in files.items():
+        write_safetensors(str(folder / fname), [(n, tensors[n]) for n in ns])
+        for n in ns:
+            weight_map[n] = fname
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+
+
+def test_sharded_folder(tmp_path):
+    raw = config("A")
+    w = {k: v.to(torch.bfloat16) for k, v in plain_llama.random_weights(raw, 2).items()}
+    d = tmp_path / "sharded"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(raw))
+    write_shards(d, w, split_at=7)
+    src = TensorSource.from_folder(str(d))
+    assert sorted(src.names()) == sorted(w)
+    WeightStore(src, torch.bfloat16, "cpu").check(requests_of(raw))
+    for n in ("model.embed_tokens.weight", "model.layers.1.mlp.down_proj.weight", "lm_head.weight"):       # from both shards
+        assert torch.equal(src.get(n), w[n])
+    # a tensor stored in both shards is named in the one error
+    d2 = tmp_path / "twice"
+    d2.mkdir()
+    write_shards(d2, w, split_at=7, twice=["model.norm.weight"])
+    with pytest.raises(WeightError, match=r"model.norm.weight \(stored in more than one shard\)"):
+        TensorSource.from_folder(str(d2))
+    # an index that names a shard that is not there
+    d3 = tmp_path / "lost"
+    d3.mkdir()
+    write_shards(d3, w, split_at=7)
+    (d3 / "model-00002-of-00002.safetensors").unlink()
+    with pytest.raises(WeightFileError):
+        TensorSource.from_folder(str(d3))
+
+
+def test_file_written_by_the_installed_package_is_read_by_the_native_reader(tmp_path):
+    from safetensors.torch import save_file
+    t = {"w": torch.randn(5, 8).to(torch.bfloat16), "f": torch.randn(3), "h": torch.randn(4, 2).to(torch.float16),
+         "i": torch.arange(10, dtype=torch.int64)}
+    path = str(tmp_path / "pkg.safetensors")
+    save_file(t, path, metadata={"format": "pt"})
+    f = SafetensorsFile(path)
+    assert sorted(f.names()) == sorted(t)
+    for n, v in t.items():
+        assert f.shape(n) == tuple(v.shape) and f.dtype(n) == v.dtype and torch.equal(f.tensor(n), v)
 
 
 def test_storage_dtypes():
