@@ -146,19 +146,20 @@ def measure_decode(llm, batch, steps, warmup, cfg, sampling=None):
     return batch * 1000.0 / ms, ms, launches, ctx_mid
 
 
-def measure_prefill(llm, cfg, layers, reps=3):
+def measure_prefill(llm, cfg, layers, reps=3, tokens=PREFILL_TOKENS):
+    """Milliseconds of one prompt step of `tokens` tokens (one sequence, logits at its last place), best of reps."""
     import torch
     from gguf_rs_cli_b200.engine.step import Entry
     eng = llm.engine(n_tokens=64 * CONTEXT, n_slots=64, max_len=CONTEXT)
     g = torch.Generator().manual_seed(7)
-    toks = torch.randint(0, cfg["vocab_size"], (PREFILL_TOKENS,), generator=g).tolist()
+    toks = torch.randint(0, cfg["vocab_size"], (tokens,), generator=g).tolist()
     best = None
     for i in range(reps + 1):
         s = eng.open()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        eng.step([Entry(s, toks, [PREFILL_TOKENS - 1])])
+        eng.step([Entry(s, toks, [tokens - 1])])
         b.record()
         torch.cuda.synchronize()
         eng.close(s)
@@ -203,6 +204,7 @@ def main():
     ap.add_argument("--top-k", type=int, default=0)
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--rep-penalty", type=float, default=1.0)
+    ap.add_argument("--prompt-steps", default="", help="also time prompt steps of these many tokens, e.g. 128,256,512")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -265,6 +267,14 @@ def main():
             points[f"decode_b{b}"] = round(p_tok_s, 2)
             points[f"decode_b{b}_ms"] = round(p_ms, 4)
         line["points"] = points
+    if args.prompt_steps:
+        # short prompt steps: bound by the weights they stream (once) rather than by the tensor rate
+        extra = {}
+        for t in [int(x) for x in args.prompt_steps.split(",") if x.strip()]:
+            t_ms = measure_prefill(llm, cfg, args.layers, reps=5, tokens=t)
+            extra[f"prompt_{t}_ms"] = round(t_ms, 3)
+            extra[f"prompt_{t}_x_weights"] = round(t_ms * 1e-3 / (wbytes / (pk["hbm_gbs"] * 1e9)), 2)
+        line.setdefault("points", {}).update(extra)
     sampler.stop()
     print(json.dumps(line))
     return 0

@@ -36,9 +36,10 @@ bool gb_pdl_enabled();
 __device__ __forceinline__ void gb_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void gb_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// pdl false: an ordinary launch, which starts when everything before it on the stream has finished.
 template <typename... KArgs, typename... Args>
-static inline cudaError_t gb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                    Args&&... args) {
+static inline cudaError_t gb_launch_opt(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                        bool pdl, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -47,11 +48,16 @@ static inline cudaError_t gb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    if (gb_pdl_enabled()) {
+    if (pdl && gb_pdl_enabled()) {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+template <typename... KArgs, typename... Args>
+static inline cudaError_t gb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+    return gb_launch_opt(kernel, grid, block, smem, stream, true, static_cast<Args&&>(args)...);
 }
 
 static inline bool gb_is_dtype(int d) { return d == GB_F32 || d == GB_BF16; }

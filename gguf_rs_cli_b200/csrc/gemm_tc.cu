@@ -7,8 +7,8 @@
 // uses 128x256 tiles; both operands are K-major, as the model folder stores W [out,in]
 // (src/tensor/dequant.rs:258-259) and activations are [tokens, in].
 //
-// Persistent CTAs (at most as many as fit the device at once) take units of work (feature
-// tile, token tile, K split) in turn.  6 warps: warp 0 issues TMA loads of
+// Persistent CTAs, no more than are resident at once, each with an equal share of all (tile, K block)
+// pairs (gemm_tc.cuh).  6 warps: warp 0 issues TMA loads of
 // 128-byte-swizzled [rows x 64] bf16 tiles into a ring of shared-memory stages, warp 1
 // owns the TMEM allocation and issues the MMAs (one thread) into one of two accumulators,
 // warps 2..5 read the other accumulator back (each its quarter of the 128 lanes) and
@@ -17,10 +17,15 @@
 // of 8 (16-byte row pitch) work; other sizes are refused and the caller falls back to
 // the CUDA-core kernel.
 //
-// With K split over several CTAs (few tiles, as in decode, would leave SMs idle), each
-// split writes its partial tile to scratch memory and bumps the tile's counter; the
-// CTA that arrives last adds all partials in split order and writes the result.
-// Nobody waits for anybody, and the order of the sum does not depend on timing.
+// A tile whose K blocks are spread over several CTAs (few tiles, as in decode, would leave SMs idle, and a
+// number of tiles that is no multiple of the CTAs would leave some with twice the work) is merged by the last
+// of them to arrive: each writes its partial tile to scratch memory and bumps the tile's counter, and the one
+// that finds all others there adds the partial tiles in their fixed order and writes the result.  Nobody waits
+// for anybody, the order of the sum does not depend on timing, and a CTA that is not the last leaves at once,
+// which lets the CTAs of the next kernel on the stream take its place and ask for their weights early.
+// (Merging a tile by all of its CTAs together, each adding up a share of the tokens once all had arrived,
+// was built and measured: it needs every CTA to stay until the end, the next kernel starts later, and a decode
+// step of the 8B shape at batch 8 took 3.74 ms instead of 3.34 ms.)
 #include <mutex>
 #include <unordered_map>
 
@@ -30,8 +35,23 @@ using namespace sm100;
 
 namespace {
 
+// Barrier of the four epilogue warps that also tells every thread whether any of them raised `flag`.
+__device__ __forceinline__ bool epilogue_any(bool flag) {
+    uint32_t any;
+    asm volatile(
+        "{\n.reg .pred p, q;\n"
+        "setp.ne.u32 q, %1, 0;\n"
+        "barrier.cta.red.or.pred p, 1, 128, q;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(any)
+        : "r"(uint32_t(flag))
+        : "memory");
+    return any != 0;
+}
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 template <int BN>
-__global__ void __launch_bounds__(TC_THREADS, TileCfg<BN>::SMEM <= 112 * 1024 ? 2 : 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x, TcParams p) {
     using Cfg = TileCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -46,7 +66,7 @@ __global__ void __launch_bounds__(TC_THREADS, TileCfg<BN>::SMEM <= 112 * 1024 ? 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kb_total = (p.K + BK - 1) / BK;
     const int token_tiles = (p.T + BN - 1) / BN;
-    const int n_units = ((p.N + BM - 1) / BM) * token_tiles * p.splits;
+    const int g_begin = cta_begin(blockIdx.x, p, kb_total), g_end = cta_begin(blockIdx.x + 1, p, kb_total);   // this CTA's share
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -71,20 +91,23 @@ __global__ void __launch_bounds__(TC_THREADS, TileCfg<BN>::SMEM <= 112 * 1024 ? 
             // depend on the kernel before this one, so the first round of weight tiles is requested at
             // once; the activations only after that kernel has finished.
             int issued = 0;
-            for (int u = blockIdx.x; u < n_units && issued < Cfg::STAGES; u += gridDim.x) {
-                Unit w = unit_of(u, p, BN, token_tiles, kb_total);
-                for (int kb = w.kb_begin; kb < w.kb_end && issued < Cfg::STAGES; ++kb, ++issued) {
-                    mbar_expect_tx(&full_bar[issued], Cfg::STAGE_BYTES);
-                    tma_load_2d(ring + issued * Cfg::STAGE_BYTES, &map_w, kb * BK, w.n0, &full_bar[issued]);
-                }
+            {
+                UnitWalk walk(p, g_begin, g_end);
+                Unit w;
+                while (issued < Cfg::STAGES && walk.next(w, p, BN, token_tiles, kb_total))
+                    for (int kb = w.kb_begin; kb < w.kb_end && issued < Cfg::STAGES; ++kb, ++issued) {
+                        mbar_expect_tx(&full_bar[issued], Cfg::STAGE_BYTES);
+                        tma_load_2d(ring + issued * Cfg::STAGE_BYTES, &map_w, kb * BK, w.n0, &full_bar[issued]);
+                    }
             }
             const int pre = issued;
             gb_grid_wait();
             int item = 0, stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-                Unit w = unit_of(u, p, BN, token_tiles, kb_total);
+            UnitWalk walk(p, g_begin, g_end);
+            Unit w;
+            while (ok && walk.next(w, p, BN, token_tiles, kb_total)) {
                 for (int kb = w.kb_begin; kb < w.kb_end; ++kb, ++item) {
                     uint8_t* a = ring + stage * Cfg::STAGE_BYTES;
                     if (item >= pre) {
@@ -104,8 +127,9 @@ __global__ void __launch_bounds__(TC_THREADS, TileCfg<BN>::SMEM <= 112 * 1024 ? 
             int stage = 0, j = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++j) {
-                Unit w = unit_of(u, p, BN, token_tiles, kb_total);
+            UnitWalk walk(p, g_begin, g_end);
+            Unit w;
+            for (; ok && walk.next(w, p, BN, token_tiles, kb_total); ++j) {
                 const int buf = j & 1;
                 if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1)) { atomicExch(p.status, 4); ok = false; break; }
                 tc_fence_after();
@@ -126,20 +150,23 @@ __global__ void __launch_bounds__(TC_THREADS, TileCfg<BN>::SMEM <= 112 * 1024 ? 
             }
         }
     } else {
-        // ---- epilogue: 4 warps, warp w reads TMEM lanes 32*(w%4) .. +31
+        // ---- epilogue: 4 warps, warp w reads TMEM lanes 32*(w%4) .. +31.  The code that finishes 16 tokens of
+        // a tile exists once, for tiles of the CTA's own and for shared ones (every SM runs this code from a cold
+        // instruction cache after another kernel: its size is time).
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;        // feature within the tile = TMEM lane
-        bool first = true;
         int j = 0;
-        for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
-            const Unit w = unit_of(u, p, BN, token_tiles, kb_total);
+        gb_grid_wait();                             // before anything is read or written that the kernel before touches
+        UnitWalk walk(p, g_begin, g_end);
+        Unit w;
+        for (; walk.next(w, p, BN, token_tiles, kb_total); ++j) {
             const int buf = j & 1;
             const int n = w.n0 + row;
             const int cols = min(BN, p.T - w.t0);       // valid tokens of this tile
+            const bool whole = w.kb_begin == 0 && w.kb_end == kb_total;
             // What the kernel before left for this tile is fetched while the products still run: the sums of
             // squares behind the tokens' scales and, in the 16-token kernel, this thread's row of the residual
             // stream (each a trip to L2 that the kernel after this one would otherwise wait for).
-            if (first) { gb_grid_wait(); first = false; }    // also before anything is written that the kernel before may still read
             float bias = 0.f;
             if (p.bias && n < p.N) bias = gb_load(p.bias, p.bias_dtype, n);
             if (p.row_ssq) tc_token_scales<BN>(p, w.t0, cols, row, rstd_s, part_s);
@@ -149,61 +176,69 @@ __global__ void __launch_bounds__(TC_THREADS, TileCfg<BN>::SMEM <= 112 * 1024 ? 
                 for (int c = 0; c < 16; ++c)
                     x_early[c] = (n < p.N && c < cols) ? __ldcg(p.resid_x + size_t(w.t0 + c) * p.ld_x + n) : 0.f;
             }
-            const bool waited = mbar_wait(&acc_full[buf], (j >> 1) & 1);
-            if (!waited) {                               // the error path: give up on the remaining units too
-                if (lane == 0) atomicExch(p.status, 3);
+            // A tile that several CTAs work on: which they are.  The tile's first CTA may have begun before the
+            // tile (its partial sums then lie in its second slot); all others begin inside it.
+            int first_cta = 0, n_ctas = 1, first_which = 0, me = 0;
+            if (!whole) {
+                tile_ctas(w.tile, p, kb_total, first_cta, n_ctas);
+                first_which = cta_begin(first_cta, p, kb_total) < w.tile * kb_total ? 1 : 0;
+                me = int(blockIdx.x) - first_cta;
+            }
+            // all four warps go on, or none: a warp that left alone would miss the others' barriers
+            if (epilogue_any(!mbar_wait(&acc_full[buf], (j >> 1) & 1))) {
+                if (threadIdx.x == 64) atomicExch(p.status, 3);
                 break;
             }
             tc_fence_after();
             const uint32_t taddr = tmem_d + (uint32_t(quarter * 32) << 16) + buf * BN;
-            const float* partials = p.scratch + size_t(w.tile) * p.splits * (BN * BM);
             bool finish = true;                          // does this CTA write the tile's result?
-            if (p.splits > 1) {
-                float* mine = p.scratch + (size_t(w.tile) * p.splits + w.split) * (BN * BM);
+            if (!whole) {
+                // this CTA's share of the tile: the partial sums go to scratch memory
+                // (a partial tile lies token by token, each token's 128 features side by side: a warp's stores and loads
+                // of one token are one 128-byte line; feature by feature with 16-byte accesses was measured: slower)
+                float* mine = p.scratch + (size_t(blockIdx.x) * 2 + (me == 0 ? first_which : 0)) * (BN * BM) + row;
                 for (int c0 = 0; c0 < BN; c0 += 16) {
                     if (c0 >= cols) break;               // uniform over the warp
                     float v[16];
                     tmem_ld16(taddr + c0, v);
 #pragma unroll
                     for (int jj = 0; jj < 16; ++jj)
-                        if (c0 + jj < cols) mine[(c0 + jj) * BM + row] = v[jj];
+                        if (c0 + jj < cols) __stcg(mine + (c0 + jj) * BM, v[jj]);
                 }
                 tc_fence_before();
                 if (lane == 0) mbar_arrive(&acc_empty[buf]);     // the accumulator may be overwritten
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (threadIdx.x == 64) {
-                    int old = atomicAdd(&p.counters[w.tile], 1);
-                    last_flag = (old == p.splits - 1);
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                epilogue_sync();
+                if (threadIdx.x == 64) last_flag = atomicAdd(&p.counters[w.tile], 1) == n_ctas - 1;
+                epilogue_sync();
                 finish = last_flag != 0;
                 if (finish) __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag may be written again for the next unit
+                epilogue_sync();                         // last_flag may be written again for the next unit
             }
             if (finish) {
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    if (c0 >= cols) break;
+                for (int c0 = 0; c0 < cols; c0 += 16) {
                     float v[16];
-                    if (p.splits == 1) {
+                    if (whole) {
                         tmem_ld16(taddr + c0, v);
                     } else {
-                        // the splits' partial sums in ascending order; 8 columns x 8 splits of loads in flight
+                        // the CTAs' partial sums in ascending order; 8 tokens x 8 partial tiles of loads in flight
                         // (every round of loads costs a trip to L2, and the kernel after this one waits for it)
 #pragma unroll
                         for (int jj = 0; jj < 16; ++jj) v[jj] = 0.f;
+                        const float* base = p.scratch + size_t(first_cta) * 2 * (BN * BM) + row;
 #pragma unroll
                         for (int j0 = 0; j0 < 16; j0 += 8) {
                             if (c0 + j0 >= cols) break;
-                            for (int s0 = 0; s0 < p.splits; s0 += 8) {
+                            for (int s0 = 0; s0 < n_ctas; s0 += 8) {
                                 float ld[8][8];
 #pragma unroll
-                                for (int si = 0; si < 8; ++si)
+                                for (int si = 0; si < 8; ++si) {
+                                    const int s = s0 + si;
+                                    const float* part = base + (size_t(s) * 2 + (s == 0 ? first_which : 0)) * (BN * BM);
 #pragma unroll
                                     for (int jj = 0; jj < 8; ++jj)
-                                        ld[si][jj] = (s0 + si < p.splits && c0 + j0 + jj < cols)
-                                                         ? __ldcg(partials + size_t(s0 + si) * (BN * BM) + (c0 + j0 + jj) * BM + row)
-                                                         : 0.f;
+                                        ld[si][jj] = (s < n_ctas && c0 + j0 + jj < cols) ? __ldcg(part + (c0 + j0 + jj) * BM) : 0.f;
+                                }
 #pragma unroll
                                 for (int si = 0; si < 8; ++si)
 #pragma unroll
@@ -211,13 +246,13 @@ __global__ void __launch_bounds__(TC_THREADS, TileCfg<BN>::SMEM <= 112 * 1024 ? 
                             }
                         }
                     }
-                    tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, waited, c0, cols, v, rstd_s, ssq_s,
+                    tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, true, c0, cols, v, rstd_s, ssq_s,
                                         BN == 16 && p.resid_x ? x_early : nullptr);
                 }
                 if (p.resid_x) tc_write_ssq<BN>(p, w.n0, w.t0, row, 0, cols, ssq_s);
-                if (p.splits > 1 && threadIdx.x == 64) p.counters[w.tile] = 0;       // ready for the next launch
+                if (!whole && threadIdx.x == 64) p.counters[w.tile] = 0;       // ready for the next launch
             }
-            if (p.splits == 1) {
+            if (whole) {
                 tc_fence_before();
                 if (lane == 0) mbar_arrive(&acc_empty[buf]);     // all of this warp's TMEM loads are done
             }
@@ -300,21 +335,22 @@ int ensure_status() {
     return 0;
 }
 
+constexpr int MAX_DEVICES = 64;
+
 template <int BN>
-int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, cudaStream_t stream) {
+int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, cudaStream_t stream, bool pdl = true) {
     using Cfg = TileCfg<BN>;
-    static bool configured = false;
-    if (!configured) {
+    // the shared-memory limit is an attribute of the function on each device; the first launch of a tile width
+    // on a device sets it
+    static bool configured[MAX_DEVICES] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return gb_fail("gb_gemm_tc: no usable current device");
+    if (!configured[dev]) {
         if (cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
             return gb_fail("gb_gemm_tc: cannot get %d bytes of shared memory", Cfg::SMEM);
-        configured = true;
+        configured[dev] = true;
     }
-    long long units = (long long)((p.N + BM - 1) / BM) * ((p.T + BN - 1) / BN) * p.splits;
-    int slots = (Cfg::SMEM <= 112 * 1024 ? 2 : 1) * p.sms;        // CTAs that can be resident at once
-    // every CTA gets the same number of units (or one less): rounds = ceil(units / slots), grid = ceil(units / rounds)
-    long long rounds = (units + slots - 1) / slots;
-    dim3 grid((unsigned)((units + rounds - 1) / rounds));
-    gb_launch(gemm_tc_kernel<BN>, grid, dim3(TC_THREADS), Cfg::SMEM, stream, mw, mx, p);
+    gb_launch_opt(gemm_tc_kernel<BN>, dim3(p.n_ctas), dim3(TC_THREADS), Cfg::SMEM, stream, pdl, mw, mx, p);
     GB_LAUNCH_OK("gb_gemm_tc");
     return 0;
 }
@@ -324,56 +360,89 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, c
 // Tokens per tile for T tokens.
 GB_API int gb_gemm_tc_tile(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256; }
 
+// Tuning aids (process-wide; the defaults are what every caller wants).
+static int g_tile_override = 0;       // > 0: tokens per tile for every product
+GB_API int gb_gemm_tc_set_tile(int bn) { g_tile_override = bn; return 0; }
+static int g_pair = 1;                // 0: never two SMs per tile
+GB_API int gb_gemm_tc_set_pair(int on) { g_pair = on; return 0; }
+static int g_mode = 0;                // 0: by the rule below, 1: whole tiles only, 2: equal shares of K blocks where tiles are not shared out per tile, 3: equal shares always
+GB_API int gb_gemm_tc_set_mode(int mode) { g_mode = mode; return 0; }
+
 // The same with the number of output features known: a few hundred tokens with few features would
 // give 256-token tiles for less than half of the SMs, so they take 128-token tiles.
-static int g_tile_override = 0;       // > 0: tokens per tile for every product (tuning aid)
-GB_API int gb_gemm_tc_set_tile(int bn) { g_tile_override = bn; return 0; }
-
 static int tile_for(int T, int N, int sms) {
     if (g_tile_override > 0) return g_tile_override;
     int bn = gb_gemm_tc_tile(T);
     const long long ft = (N + BM - 1) / BM;
     if (bn == 256 && 2 * ft * ((T + 255) / 256) <= sms) bn = 128;
-    // a few dozen tokens and fewer feature tiles than SMs: two half-size token tiles give twice the units
-    // without splitting K further (measured faster at 32 and 64 tokens; the second read of W hits L2)
+    // a few dozen tokens and fewer feature tiles than SMs: two half-size token tiles give twice the tiles
+    // without more CTAs on each (the second read of W hits L2; the last CTA of a tile reads all its partial
+    // tiles, and those grow with the tile's width: batch 64 of the 8B shape 5.36 instead of 5.9 ms a step)
     if (bn > 16 && bn <= 64 && ft < sms) bn /= 2;
     // a few hundred tokens: tiles of 64 tokens, two CTAs per SM, as long as all of them fit the device at once
-    // (a CTA with a wide tile streams its operands no faster, and merging the K splits of a wide tile takes
-    // the last CTA long; measured at 128 to 768 tokens)
+    // (a CTA with a wide tile streams its operands no faster; measured at 128 to 768 tokens)
     if (bn >= 128 && (T <= 128 || ft * ((T + 63) / 64) <= 2LL * sms)) bn = 64;
     return bn;
 }
 
-// How many ways the kernel would split K for these sizes on a device with `sms` SMs (1 = no scratch needed).
-static int g_pair = 1;                // 0: never two SMs per tile (tuning aid)
-GB_API int gb_gemm_tc_set_pair(int on) { g_pair = on; return 0; }
-static int g_split_override = 0;      // > 0: every product uses this many splits (tuning aid)
-GB_API int gb_gemm_tc_set_splits(int s) { g_split_override = s; return 0; }
-
-GB_API int gb_gemm_tc_splits(int T, int N, int K, int sms) {
-    int bn = tile_for(T, N, sms);
-    if (g_split_override > 0) {
-        int kb0 = (K + BK - 1) / BK;
-        return g_split_override > kb0 ? kb0 : g_split_override;
+// How a product of these sizes is cut (gemm_tc.cuh): tile width, CTAs, and whether CTAs share tiles.
+struct TcCut {
+    int bn, n_ctas, cut, per_tile, extra, kb;
+    long long tiles, scratch_floats;
+    void fill(TcParams& p) const {
+        p.n_ctas = n_ctas; p.tiles = int(tiles); p.cut = cut; p.per_tile = per_tile; p.extra = extra;
+        p.total_its = int(tiles * kb); p.its_each = p.total_its / n_ctas; p.its_rest = p.total_its % n_ctas;
     }
-    long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
-    int kb = (K + BK - 1) / BK;
-    int slots = bn <= 64 ? 2 * sms : sms;          // CTAs that can be resident at once
-    if (tiles >= sms || kb < 8) return 1;
-    int s = int(slots / tiles);
-    if (s > kb / 4) s = kb / 4;       // at least 4 K blocks per split,
-    if (kb >= 64 && s > kb / 8) s = kb / 8;      // and 8 where K is long enough (4096 x 4096 at 8 to 16 tokens: 9.3 instead of 9.9 us)
-    if (s > 16) s = 16;
-    return s < 1 ? 1 : s;
+};
+static TcCut cut_for(int T, int N, int K, int sms, bool may_share, int n_counters) {
+    TcCut c;
+    c.bn = tile_for(T, N, sms);
+    c.tiles = (long long)((N + BM - 1) / BM) * ((T + c.bn - 1) / c.bn);
+    c.kb = (K + BK - 1) / BK;
+    const long long slots = (long long)ctas_per_sm(c.bn) * (sms > 0 ? sms : 1);        // CTAs that are resident at once
+    c.cut = CUT_WHOLE;
+    c.per_tile = c.extra = 0;
+    c.scratch_floats = 0;
+    c.n_ctas = 1;
+    if (c.tiles == 0) return c;              // no tokens: nothing is launched
+    // whole tiles: every CTA the same number of tiles, or one less
+    const long long rounds = (c.tiles + slots - 1) / slots;
+    c.n_ctas = int((c.tiles + rounds - 1) / rounds);
+    // Few tiles: several CTAs per tile, each with a part of the tile's K blocks, at least 4 K blocks a CTA (8 where K
+    // is long: 4096 x 4096 at 8 to 16 tokens took 9.3 instead of 9.9 us) and no more than 16 CTAs on one tile (the
+    // last of them reads all their partial tiles).  Tiles of 256 tokens go to the kernel that pairs two SMs.
+    const bool pair = c.bn == 256 && g_pair;
+    if (!may_share || pair || c.tiles > n_counters || g_mode == 1) return c;
+    long long n = c.tiles * c.kb / (c.kb >= 64 ? 8 : 4);
+    n = n > slots ? slots : n < 1 ? 1 : n;
+    if (n > 16 * c.tiles) n = 16 * c.tiles;
+    if (n >= 2 * c.tiles && g_mode != 3) {
+        // what is left over when every tile has the same number of CTAs goes to the first tiles, one CTA each,
+        // unless that would leave the shares more than 6% apart
+        long long q = n / c.tiles, r = n % c.tiles;
+        if (100 * r > 6 * q * c.tiles) r = 0;
+        c.n_ctas = int(q * c.tiles + r);
+        c.cut = CUT_PER_TILE;
+        c.per_tile = int(q);
+        c.extra = int(r);
+        c.scratch_floats = 2LL * c.n_ctas * c.bn * BM;
+    } else if (g_mode >= 2 && n != c.tiles && c.tiles % n != 0) {
+        // Equal shares of all K blocks wherever they fall (a tuning aid: measured on the 8B shape, gate and up at
+        // batch 8 with 224 tiles on 296 CTAs, the two merges per CTA cost more than the idle SMs: 3.60 instead of
+        // 3.43 ms a step).
+        c.n_ctas = int(n);
+        c.cut = CUT_EVEN;
+        c.scratch_floats = 2LL * n * c.bn * BM;
+    }
+    return c;
 }
 
-// Floats of scratch a launch with these sizes needs (0 when K is not split).
+// CTAs that a product of these sizes runs on, on a device with `sms` SMs, when it may use scratch memory.
+GB_API int gb_gemm_tc_ctas(int T, int N, int K, int sms) { return cut_for(T, N, K, sms, true, 1 << 30).n_ctas; }
+
+// Floats of scratch a launch with these sizes needs (0 when no tile is shared between CTAs).
 GB_API long long gb_gemm_tc_scratch_floats(int T, int N, int K, int sms) {
-    int s = gb_gemm_tc_splits(T, N, K, sms);
-    if (s == 1) return 0;
-    int bn = tile_for(T, N, sms);
-    long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
-    return tiles * s * bn * BM;
+    return cut_for(T, N, K, sms, true, 1 << 30).scratch_floats;
 }
 
 // Whether the tensor-core kernel takes these operands (bf16, 16-byte aligned, pitches multiples of 8).
@@ -383,8 +452,10 @@ GB_API int gb_gemm_tc_supported(const void* X, long long ldx, const void* W, lon
 }
 
 // X: bf16 [T, K] pitch ldx; W: bf16 [N, K] pitch ldw; out: bf16 or f32 [T, N] pitch ldo; bias optional.
+// W must not be written by the kernel that runs before this one on the stream: the first tiles of W are
+// requested before that kernel has finished (the engine's W are constant weights).
 // scratch: gb_gemm_tc_scratch_floats(...) floats; counters: at least as many zeroed ints as tiles
-// (the kernel leaves them zero).  Both may be null when K is not split.
+// (the kernel leaves them zero).  Both may be null: every CTA then takes whole tiles.
 // swiglu_features > 0: W is [2*64*ceil(F/64), K], row 2f being gate row f and row 2f+1 up row f (zero
 // rows pad the last tile), F = swiglu_features, and
 // out[t,f] = silu(gate_f) * up_f has F columns (src/model/llama.rs:399-401 in the product's epilogue).
@@ -432,19 +503,19 @@ static int gemm_tc_impl(const void* X, long long ldx, const void* W, long long l
                K, ldx, ldw);
     if (T == 0) return 0;
     if (ensure_status()) return 1;
-    int bn = tile_for(T, N, sms);
+    const TcCut cut = cut_for(T, N, K, sms, scratch && counters, n_counters);
+    GB_REQUIRE(cut.tiles * cut.kb < (1LL << 31) - (1 << 20), "gb_gemm_tc: T=%d N=%d K=%d is more work than the kernel numbers", T, N, K);
+    const int bn = cut.bn;
     TcParams p;
     p.out = out; p.bias = bias; p.scratch = scratch; p.counters = counters; p.status = g_status_dev;
     p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype; p.T = T; p.N = N; p.K = K;
-    p.splits = (scratch && counters) ? gb_gemm_tc_splits(T, N, K, sms) : 1;
     p.swiglu = swiglu_features > 0; p.N_out = swiglu_features; p.sms = sms;
+    cut.fill(p);
     p.row_ssq = row_ssq; p.ssq_parts = ssq_parts; p.norm_size = norm_size; p.eps = eps;
     p.resid_x = resid_x; p.resid_xb = (__nv_bfloat16*)resid_xb; p.ssq_out = ssq_out; p.ld_x = ld_x;
-    long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
-    GB_REQUIRE(p.splits == 1 || tiles <= n_counters, "gb_gemm_tc: %lld tiles need as many counters, %d given", tiles, n_counters);
     CUtensorMap mw, mx;
     if (tensor_map_2d(W, N, K, ldw, BM, &mw)) return 1;
-    if (bn == 256 && g_pair && p.splits == 1) {
+    if (bn == 256 && g_pair && cut.cut == CUT_WHOLE) {
         // many tokens: two SMs per 256 x 256 tile, each loading 128 tokens of X per stage; bf16 results leave
         // through shared memory and TMA stores of [16 tokens x 128 features] (64 features after SwiGLU)
         if (tensor_map_2d(X, T, K, ldx, 128, &mx)) return 1;
@@ -464,7 +535,7 @@ static int gemm_tc_impl(const void* X, long long ldx, const void* W, long long l
 }
 
 // Non-zero when a bounded wait inside a tensor-core kernel gave up since the last clear
-// (1: a load stage never came free, 2: a load never arrived, 3: the accumulator never completed).
+// (1: a load stage never came free, 2: a load never arrived, 3/4: an accumulator never completed or never came free).
 // Read after synchronising the stream.
 GB_API int gb_tc_status() { return g_status_host ? *g_status_host : 0; }
 GB_API int gb_tc_status_clear() {
@@ -543,34 +614,38 @@ GB_API int gb_gemm_tc_noalloc(const void* X, long long ldx, const void* W, long 
     if (cudaGetDevice(&dev) != cudaSuccess) return gb_fail("gb_gemm_tc_noalloc: no current device");
     NoallocDevice* d = nullptr;
     if (noalloc_setup(dev, &d)) return 1;
-    const int bn = tile_for(T, N, d->sms);
-    const long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
-    const int splits = gb_gemm_tc_splits(T, N, K, d->sms);
-    if (splits > 1) {
-        const long long need = tiles * splits * bn * BM;
-        GB_REQUIRE(need <= GB_NOALLOC_SCRATCH_FLOATS && tiles <= GB_NOALLOC_COUNTERS,
-                   "gb_gemm_tc_noalloc: T=%d N=%d K=%d splits K %d ways over %lld tiles and needs %lld floats of scratch; the "
-                   "built-in scratch holds %d floats and %d tiles (use gb_gemm_tc with memory of your own)",
-                   T, N, K, splits, tiles, need, GB_NOALLOC_SCRATCH_FLOATS, GB_NOALLOC_COUNTERS);
+    // the same cut of the work as gb_gemm_tc makes; tiles that CTAs share need scratch memory and counters
+    const TcCut cut = cut_for(T, N, K, d->sms, true, 1 << 30);
+    GB_REQUIRE(cut.tiles * cut.kb < (1LL << 31) - (1 << 20), "gb_gemm_tc_noalloc: T=%d N=%d K=%d is more work than the kernel numbers", T, N, K);
+    const int bn = cut.bn;
+    if (cut.cut != CUT_WHOLE) {
+        GB_REQUIRE(cut.scratch_floats <= GB_NOALLOC_SCRATCH_FLOATS && cut.tiles <= GB_NOALLOC_COUNTERS,
+                   "gb_gemm_tc_noalloc: T=%d N=%d K=%d runs on %d CTAs that share %lld tiles and needs %lld floats of scratch; "
+                   "the built-in scratch holds %d floats and %d tiles (use gb_gemm_tc with memory of your own)",
+                   T, N, K, cut.n_ctas, cut.tiles, cut.scratch_floats, GB_NOALLOC_SCRATCH_FLOATS, GB_NOALLOC_COUNTERS);
         // the arrival counters must start at zero whatever an earlier call left behind
-        if (cudaMemsetAsync(d->counters, 0, sizeof(int) * size_t(tiles), stream) != cudaSuccess)
+        if (cudaMemsetAsync(d->counters, 0, sizeof(int) * size_t(cut.tiles), stream) != cudaSuccess)
             return gb_fail("gb_gemm_tc_noalloc: cannot clear the counters");
     }
     TcParams p;
     p.out = out; p.bias = bias; p.scratch = d->scratch; p.counters = d->counters; p.status = d->status;
     p.ldo = ldo; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype; p.T = T; p.N = N; p.K = K;
-    p.splits = splits; p.swiglu = 0; p.N_out = 0; p.sms = d->sms;
+    p.swiglu = 0; p.N_out = 0; p.sms = d->sms;
+    cut.fill(p);
     p.row_ssq = nullptr; p.ssq_parts = 0; p.norm_size = 0; p.eps = 0.f;
     p.resid_x = nullptr; p.resid_xb = nullptr; p.ssq_out = nullptr; p.ld_x = 0;
     CUtensorMap mw, mx;
     if (encode_map_2d(W, N, K, ldw, BM, &mw)) return 1;
     if (encode_map_2d(X, T, K, ldx, bn, &mx)) return 1;
+    // An ordinary launch, not a programmatic dependent one: the kernel asks for its first tiles of W before it
+    // waits for the kernel in front of it, which is right for constant weights but not for a caller whose W may
+    // be the output of the call before.
     switch (bn) {
-        case 16: return launch_tc<16>(mw, mx, p, stream);
-        case 32: return launch_tc<32>(mw, mx, p, stream);
-        case 64: return launch_tc<64>(mw, mx, p, stream);
-        case 128: return launch_tc<128>(mw, mx, p, stream);
-        default: return launch_tc<256>(mw, mx, p, stream);
+        case 16: return launch_tc<16>(mw, mx, p, stream, false);
+        case 32: return launch_tc<32>(mw, mx, p, stream, false);
+        case 64: return launch_tc<64>(mw, mx, p, stream, false);
+        case 128: return launch_tc<128>(mw, mx, p, stream, false);
+        default: return launch_tc<256>(mw, mx, p, stream, false);
     }
 }
 

@@ -23,17 +23,25 @@ template <int BN> struct TileCfg {
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators
 };
 
+// CTAs of the one-CTA kernel that share an SM (by shared memory; the kernel's launch bounds say the same).
+__host__ __device__ constexpr int ctas_per_sm(int bn) { return bn <= 64 ? 2 : 1; }
+
 struct TcParams {
     void* out;
     const void* bias;
-    float* scratch;       // [tiles][splits][BN][128] partial sums, used when splits > 1
+    float* scratch;       // [2 * CTAs][BN][128] partial sums of the tiles that several CTAs share
     int* counters;        // [tiles], zero between launches
     int* status;          // set non-zero when a bounded wait gave up
     long long ldo;
     int out_dtype, bias_dtype;
-    int T, N, K, splits;
+    int T, N, K;
     int swiglu, N_out;    // swiglu: W's rows alternate gate, up; out has N_out features
     int sms;
+    // how the work is cut (see Unit): CTAs, tiles, and the rule that gives each CTA its share
+    int n_ctas, tiles, cut;   // cut: CUT_WHOLE, CUT_EVEN or CUT_PER_TILE
+    int per_tile, extra;      // CUT_PER_TILE: every tile has per_tile CTAs, the first `extra` tiles one more
+    int total_its;            // tiles * K blocks (the entry point refuses sizes beyond 2^31)
+    int its_each, its_rest;   // total_its / n_ctas and total_its % n_ctas
     // deferred RMS norm of the input: X holds the un-normalised rows (the norm's weight is folded into W), and
     // the result is scaled per token by 1 / sqrt(sum_i row_ssq[i][t] / norm_size + eps)
     const float* row_ssq;
@@ -47,31 +55,102 @@ struct TcParams {
     long long ld_x;
 };
 
-// One unit of work: a tile of 128 features x BN tokens over one split of K.  Units are numbered
-// unit = tile * splits + split, and CTA c takes units c, c + grid, ...  Tiles are numbered so that the CTAs
-// running at one time share operands in L2: token tiles in groups of TILE_GROUP, inside a group feature tile
-// by feature tile with the group's token tiles innermost (many tokens: the group's activations stay in L2
-// while the weights stream; few tokens: one group, feature-major as the weights lie in memory).
+// The work of a product is the sequence of all (tile, K block) pairs, tile after tile: tiles * kb_total
+// iterations, cut into one contiguous share per CTA, with no more CTAs than are resident at once.  A CTA's
+// share is cut into units at tile borders.  A unit that covers all of its tile's K blocks is finished by its
+// CTA alone; a tile that several CTAs share is merged by all of them (gemm_tc.cu).  Three rules:
+//   CUT_WHOLE     whole tiles only, CTA c taking every CTAs-th tile from tile c on (no shared tiles, no scratch)
+//   CUT_EVEN      CTA c takes the iterations [c * total / CTAs, (c + 1) * total / CTAs): every CTA streams the
+//                 same number of operand bytes whatever the sizes are; a share may end inside one tile and
+//                 begin inside another
+//   CUT_PER_TILE  fewer tiles than CTAs: every tile gets CTAs / tiles CTAs of its own (the first CTAs % tiles
+//                 tiles one more), each an equal part of the tile's K blocks; no share crosses a tile border
+// Tiles are numbered so that the CTAs running at one time share operands in L2: token tiles in groups of
+// TILE_GROUP, inside a group feature tile by feature tile with the group's token tiles innermost (many
+// tokens: the group's activations stay in L2 while the weights stream; few tokens: one group, feature-major
+// as the weights lie in memory).
+enum { CUT_WHOLE = 0, CUT_EVEN = 1, CUT_PER_TILE = 2 };
 constexpr int TILE_GROUP = 16;
 struct Unit {
-    int tile, split, n0, t0, kb_begin, kb_end;
+    int tile, n0, t0, kb_begin, kb_end;
 };
-__device__ __forceinline__ Unit unit_of(int u, const TcParams& p, int BN, int token_tiles, int kb_total) {
-    Unit w;
-    w.tile = u / p.splits;
-    w.split = u - w.tile * p.splits;
+__device__ __forceinline__ void tile_origin(int tile, const TcParams& p, int BN, int token_tiles, int& n0, int& t0) {
     const int feature_tiles = (p.N + BM - 1) / BM;
     const int per_group = TILE_GROUP * feature_tiles;
-    const int group = w.tile / per_group, r = w.tile - group * per_group;
+    const int group = tile / per_group, r = tile - group * per_group;
     const int group_start = group * TILE_GROUP;
     const int group_size = min(TILE_GROUP, token_tiles - group_start);
     const int ft = r / group_size;
-    w.n0 = ft * BM;
-    w.t0 = (group_start + (r - ft * group_size)) * BN;
-    w.kb_begin = int((long long)w.split * kb_total / p.splits);
-    w.kb_end = int((long long)(w.split + 1) * kb_total / p.splits);
-    return w;
+    n0 = ft * BM;
+    t0 = (group_start + (r - ft * group_size)) * BN;
 }
+// CUT_PER_TILE: the tile of CTA c and the first CTA and number of CTAs of tile t.
+__device__ __forceinline__ int per_tile_first(int t, const TcParams& p) { return t * p.per_tile + min(t, p.extra); }
+__device__ __forceinline__ int per_tile_count(int t, const TcParams& p) { return p.per_tile + (t < p.extra ? 1 : 0); }
+__device__ __forceinline__ int per_tile_of(int c, const TcParams& p) {
+    const int wide = p.extra * (p.per_tile + 1);
+    return c < wide ? c / (p.per_tile + 1) : p.extra + (c - wide) / p.per_tile;
+}
+// First iteration of CTA c (c = n_ctas gives the end of all work).  32-bit arithmetic throughout: a 64-bit
+// division is a subroutine of a hundred instructions, inlined wherever it stands, and this code runs once per
+// CTA from a cold instruction cache.
+__device__ __forceinline__ int cta_begin(int c, const TcParams& p, int kb_total) {
+    if (p.cut == CUT_WHOLE) return 0;       // not used: see UnitWalk
+    if (p.cut == CUT_EVEN) return c * p.its_each + c * p.its_rest / p.n_ctas;      // = c * total / CTAs
+    if (c >= p.n_ctas) return p.total_its;
+    const int t = per_tile_of(c, p);
+    return t * kb_total + (c - per_tile_first(t, p)) * kb_total / per_tile_count(t, p);
+}
+// The CTA whose share holds iteration g under CUT_EVEN: an estimate in floating point, put right by comparing.
+__device__ __forceinline__ int cta_holding(int g, const TcParams& p, int kb_total) {
+    int c = int((float(g) + 0.5f) * float(p.n_ctas) / float(p.total_its));
+    c = min(max(c, 0), p.n_ctas - 1);
+    while (c + 1 < p.n_ctas && cta_begin(c + 1, p, kb_total) <= g) ++c;
+    while (c > 0 && cta_begin(c, p, kb_total) > g) --c;
+    return c;
+}
+// The first CTA and the number of CTAs of a shared tile (CUT_EVEN and CUT_PER_TILE).
+__device__ __forceinline__ void tile_ctas(int tile, const TcParams& p, int kb_total, int& first, int& count) {
+    if (p.cut == CUT_PER_TILE) {
+        first = per_tile_first(tile, p);
+        count = per_tile_count(tile, p);
+        return;
+    }
+    first = cta_holding(tile * kb_total, p, kb_total);
+    count = cta_holding(tile * kb_total + kb_total - 1, p, kb_total) - first + 1;
+}
+// The units of this CTA, in the order it works on them.  With whole tiles CTA c takes the tiles c, c + CTAs,
+// c + 2 CTAs, ...: the CTAs that run at one time then work on neighbouring tiles, whose operands they share in L2
+// (CTA c taking tiles 2c and 2c + 1 instead made gate and up at 128 tokens read W twice from memory: 85 instead
+// of 60 us).  Otherwise the units are the pieces of the CTA's share of the iterations.
+struct UnitWalk {
+    int g, g_end, tile, whole;
+    __device__ __forceinline__ UnitWalk(const TcParams& p, int begin, int end)
+        : g(begin), g_end(end), tile(blockIdx.x), whole(p.cut == CUT_WHOLE) {}
+    __device__ __forceinline__ bool next(Unit& u, const TcParams& p, int BN, int token_tiles, int kb_total) {
+        if (whole) {
+            if (tile >= p.tiles) return false;
+            u.tile = tile;
+            u.kb_begin = 0;
+            u.kb_end = kb_total;
+            tile += p.n_ctas;
+        } else {
+            if (g >= g_end) return false;
+            u.tile = g / kb_total;
+            u.kb_begin = g - u.tile * kb_total;
+            const int left = g_end - g;
+            u.kb_end = left < kb_total - u.kb_begin ? u.kb_begin + left : kb_total;
+            g += u.kb_end - u.kb_begin;
+        }
+        if (token_tiles == 1) {             // few tokens: tile t is feature tile t
+            u.n0 = u.tile * BM;
+            u.t0 = 0;
+        } else {
+            tile_origin(u.tile, p, BN, token_tiles, u.n0, u.t0);
+        }
+        return true;
+    }
+};
 
 // The scale of each token of a tile under a deferred norm (the splits of one tile all compute the same
 // numbers): the 128 epilogue threads share the loads, GROUPS threads per token each summing every GROUPS-th

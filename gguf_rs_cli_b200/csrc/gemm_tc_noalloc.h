@@ -7,9 +7,10 @@
 // and must know its footprint when it starts, or a latency-critical loop in which the
 // device-wide synchronisation of cudaMalloc/cudaFree would stall every other stream.
 //
-// The ordinary entry point (gb_gemm_tc) gets the scratch memory of its K split from the
-// caller, who usually allocates it; this one uses a fixed array that lives in the library
-// itself.  The caller still passes inputs and outputs.
+// The ordinary entry point (gb_gemm_tc) gets the scratch memory in which CTAs that share an
+// output tile leave their partial sums from the caller, who usually allocates it; this one
+// uses a fixed array that lives in the library itself.  The caller still passes inputs and
+// outputs.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -17,7 +18,7 @@
 extern "C" {
 #endif
 
-// Capacity of the built-in scratch: floats of partial tiles, and tiles whose K is split.
+// Capacity of the built-in scratch: floats of partial tiles, and tiles that CTAs may share.
 // Every GPU that loads the library holds GB_NOALLOC_SCRATCH_FLOATS * 4 bytes (8 MiB) plus the
 // counters until the process exits.
 #define GB_NOALLOC_SCRATCH_FLOATS (2 * 1024 * 1024)
@@ -26,13 +27,19 @@ extern "C" {
 // out[t,n] = sum_k X[t,k] * W[n,k] (+ bias[n]): X bf16 [T,K] with pitch ldx, W bf16 [N,K] with
 // pitch ldw, out bf16 (dtype 1) or f32 (dtype 0) [T,N] with pitch ldo, bias f32 or bf16 or null.
 // K and the pitches must be multiples of 8 and the pointers 16-byte aligned, as for gb_gemm_tc.
-// Returns 0, or non-zero with a message in gb_last_error(): sizes whose K split would need more
-// than the built-in scratch are refused (gb_gemm_tc with caller memory takes them).
+// Returns 0, or non-zero with a message in gb_last_error(): sizes whose partial tiles would need
+// more than the built-in scratch are refused (gb_gemm_tc with caller memory takes them).
 //
 // It calls no cudaMalloc, cudaFree, or any other allocating routine, on the device or the host.
 // The first call on each device looks up the address of the built-in scratch
 // (cudaGetSymbolAddress, with that device current); make that first call before any stream
-// capture begins on that device.
+// capture begins on that device.  The kernel exists in five widths (tiles of 16, 32, 64, 128
+// and 256 tokens, chosen from T and N), and the first launch of each width on each device
+// loads that kernel and raises its shared-memory limit (cudaFuncSetAttribute): a caller who
+// must not trigger even that later on, or who captures streams, warms up one call of every
+// width it will use (T = 16, 32, 64 and so on) first.
+// The launch is an ordinary one: it starts when everything before it on `stream` has finished,
+// so W and X may be outputs of earlier work on the stream, of this entry point included.
 // All calls share the one scratch array, and it keeps what the last call left: the counters
 // that must start at zero are cleared on `stream` before each launch, the partial tiles are
 // always written before they are read.  Two calls that overlap on the GPU (different streams,

@@ -136,10 +136,10 @@ _SIGNATURES = {
     "gb_sample": [_P, _L, _I, _I, _P, _P, _F, _I, _F, _F, _P, _P, _P, _P],
     "gb_gemm_tc": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _P, _P, _I, _I, _I, _P],
     "gb_gemm_tc_tile": [_I],
-    "gb_gemm_tc_set_splits": [_I],
+    "gb_gemm_tc_set_mode": [_I],
     "gb_gemm_tc_set_pair": [_I],
     "gb_gemm_tc_set_tile": [_I],
-    "gb_gemm_tc_splits": [_I, _I, _I, _I],
+    "gb_gemm_tc_ctas": [_I, _I, _I, _I],
     "gb_gemm_tc_scratch_floats": [_I, _I, _I, _I],
     "gb_gemm_tc_supported": [_P, _L, _P, _L, _I],
     "gb_attention_decode": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _F, _I, _P, _P, _I, _P],

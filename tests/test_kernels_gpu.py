@@ -124,7 +124,7 @@ def test_gemm_tensor_core(T, N, Kd, out_dtype):
     twin = torch.empty(T, N, dtype=F32, device=DEV)
     k.gemm_generic(x, w, b, twin)
     assert rel_err(twin, want) < 1e-5
-    # without the K split the result is the same up to the order of the 32-bit sums
+    # with whole tiles only (no scratch memory) the result is the same up to the order of the 32-bit sums
     nosplit = torch.empty(T, N, dtype=F32, device=DEV)
     k.gemm_tc(x, w, b, nosplit, split_k=False)
     assert rel_err(nosplit, want) < 1e-5
@@ -636,6 +636,7 @@ def test_gemm_tensor_core_two_sms_per_tile(T, N, Kd):
     want = P.linear(x.double().cpu(), w.double().cpu(), b.double().cpu())
     outs = []
     try:
+        native.call("gb_gemm_tc_set_mode", 1)              # whole tiles in the one-CTA kernel too: the same sums
         for pair in (1, 0):
             native.call("gb_gemm_tc_set_pair", pair)
             out = torch.full((T, N), float("nan"), dtype=F32, device=DEV)
@@ -648,6 +649,7 @@ def test_gemm_tensor_core_two_sms_per_tile(T, N, Kd):
             outs.append(out)
     finally:
         native.call("gb_gemm_tc_set_pair", 1)
+        native.call("gb_gemm_tc_set_mode", 0)
     assert torch.equal(outs[0], outs[1])
 
 
@@ -706,6 +708,71 @@ def test_gemm_tensor_core_deferred_norm_and_residual(T, N, Kd):
     assert torch.equal(rb.cpu(), r.cpu().to(BF))
     want_ssq = torch.stack([(r.cpu().double()[:, 128 * i:128 * (i + 1)] ** 2).sum(1) for i in range(tiles)])
     assert rel_err(ssq_out, want_ssq) < 1e-5
+
+
+@pytest.mark.parametrize("T,N,Kd,tile", [(5, 384, 4096, 16), (16, 4096, 4096, 16), (40, 1000, 2048, 32), (64, 520, 1024, 64),
+                                         (64, 4096, 4096, 64), (130, 300, 4096, 128), (300, 260, 2048, 256), (700, 264, 640, 64)])
+@pytest.mark.parametrize("mode", [2, 3])
+def test_gemm_tensor_core_tiles_shared_between_ctas(T, N, Kd, tile, mode):
+    """Tiles shared by CTAs in every way, at every tile width.  Mode 3: every CTA takes an equal share of all K
+    blocks (a share that ends inside a tile, one that lies inside a tile, whole tiles between two partial ones);
+    mode 2: where the sizes allow it, every tile has CTAs of its own instead.  Plain,
+    gated and residual epilogues against 64-bit products, twice in a row to the bit (the counters are left at
+    zero), and the same values as with whole tiles only up to the order of the 32-bit sums."""
+    from gguf_rs_cli_b200 import native
+    k = K()
+    g = torch.Generator().manual_seed(T + N + Kd)
+    x = torch.randn(T, Kd, generator=g).to(BF).to(DEV)
+    w = (torch.randn(N, Kd, generator=g) * 0.1).to(BF).to(DEV)
+    b = torch.randn(N, generator=g).to(DEV)
+    want = P.linear(x.double().cpu(), w.double().cpu(), b.double().cpu())
+    F_ = (N // 2 // 8) * 8
+    wg, wu = w[:F_], w[F_:2 * F_]
+    wgu = k.interleave_gate_up(wg, wu)
+    want_g = P.silu(P.linear(x.double().cpu(), wg.double().cpu())) * P.linear(x.double().cpu(), wu.double().cpu())
+    r0 = torch.randn(T, N, generator=g) * 2
+    want_r = r0.double() + want
+    parts = (Kd + 127) // 128
+    ssq = torch.rand(parts, T, generator=g).to(DEV) * 50
+    rstd = 1 / torch.sqrt(ssq.double().cpu().sum(0) / Kd + 1e-5)
+    try:
+        native.call("gb_gemm_tc_set_pair", 0)
+        native.call("gb_gemm_tc_set_tile", tile)
+        native.call("gb_gemm_tc_set_mode", mode)
+        assert native.library().gb_gemm_tc_scratch_floats(T, N, Kd, native.library().gb_sm_count()) > 0
+        outs = []
+        for _ in range(2):
+            out = torch.full((T, N), float("nan"), dtype=F32, device=DEV)
+            k.gemm_tc(x, w, b, out)
+            outb = torch.full((T, N), float("nan"), dtype=BF, device=DEV)
+            k.gemm_tc(x, w, b, outb)
+            gated = torch.full((T, F_), float("nan"), dtype=F32, device=DEV)
+            k.gemm_tc(x, wgu, None, gated, swiglu_features=F_)
+            normed = torch.full((T, N), float("nan"), dtype=F32, device=DEV)
+            k.gemm_tc(x, w, b, normed, row_ssq=ssq, ssq_parts=parts, norm_size=Kd, eps=1e-5)
+            r = r0.to(DEV).clone()
+            rb = torch.zeros(T, N, dtype=BF, device=DEV)
+            ssq_out = torch.full(((N + 127) // 128, T), float("nan"), device=DEV)
+            k.gemm_tc(x, w, b, None, resid_x=r, resid_xb=rb, ssq_out=ssq_out)
+            torch.cuda.synchronize()
+            k.check_tc_status()
+            outs.append((out, outb, gated, normed, r, rb, ssq_out))
+        out, outb, gated, normed, r, rb, ssq_out = outs[0]
+        assert rel_err(out, want) < 1e-5 and rel_err(outb, want) < 5e-3 and rel_err(gated, want_g) < 1e-5
+        assert rel_err(normed, (want - b.double().cpu()) * rstd[:, None] + b.double().cpu()) < 1e-5
+        assert rel_err(r, want_r) < 1e-5 and torch.equal(rb.cpu(), r.cpu().to(BF))
+        want_ssq = torch.stack([(r.cpu().double()[:, 128 * i:128 * (i + 1)] ** 2).sum(1) for i in range((N + 127) // 128)])
+        assert rel_err(ssq_out, want_ssq) < 1e-5
+        for a, c in zip(outs[0], outs[1]):
+            assert torch.equal(a, c)
+        native.call("gb_gemm_tc_set_mode", 1)
+        whole = torch.full((T, N), float("nan"), dtype=F32, device=DEV)
+        k.gemm_tc(x, w, b, whole)
+        assert rel_err(whole, want) < 1e-5 and rel_err(whole, out.double()) < 1e-5
+    finally:
+        native.call("gb_gemm_tc_set_pair", 1)
+        native.call("gb_gemm_tc_set_tile", 0)
+        native.call("gb_gemm_tc_set_mode", 0)
 
 
 def test_embed_shadow():
