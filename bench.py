@@ -3,7 +3,7 @@
 one B200.  Prints one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--layers L] [--batch B] [--no-points]
+                    [--layers L] [--batch B] [--no-points] [--prompt-steps 128,256] [--shape 8b|1b|13b]
 
 `value` is decoded tokens a second at batch 8 after 512-token prompts, timed on the
 device with CUDA events around K decode steps (each step: index arrays host to
@@ -33,6 +33,23 @@ SHAPE_8B = {
                      "original_max_position_embeddings": 8192},
     "rms_norm_eps": 1e-5, "max_position_embeddings": 8192, "tie_word_embeddings": False, "hidden_act": "silu",
 }
+# The two further workloads: unequal prompts through generate(), then 256 decode steps.
+SHAPE_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 16, "hidden_size": 2048,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192,
+    "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 8192, "tie_word_embeddings": True, "hidden_act": "silu",
+}
+SHAPE_13B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 40, "hidden_size": 5120,
+    "num_attention_heads": 40, "num_key_value_heads": 40, "head_dim": 128, "intermediate_size": 13824,
+    "vocab_size": 32000, "rope_theta": 10000.0, "rope_scaling": None,
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 4096, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+WORKLOADS = {"1b": (SHAPE_1B, "llama-3.2-1b-shape", 16, 64, 1024), "13b": (SHAPE_13B, "llama-2-13b-shape", 32, 128, 2048)}
+WORKLOAD_STEPS = 256
 CONTEXT = 8192
 PROMPT = 512
 PREFILL_TOKENS = 2048
@@ -97,10 +114,12 @@ class ClockSampler:
 
 
 def weight_bytes(cfg, layers):
+    """Bytes of weights a decode step reads: every layer, the final norm and the head (for a tied head the
+    embedding table, read once as the head); the embedding rows of the step's tokens are negligible."""
     E, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     per_layer = (nh * hd * E + 2 * nkv * hd * E + E * nh * hd + 3 * F * E + 2 * E) * 2
-    return layers * per_layer + (V * E + E) * 2          # + head and final norm; embedding rows are negligible
+    return layers * per_layer + (V * E + E) * 2
 
 
 def kv_bytes_per_token(cfg, layers):
@@ -191,13 +210,73 @@ def measure_e2e(llm, cfg, batch, steps, warmup):
     return tok_s, (backend.h2d_bytes - h0) // n_steps, (backend.d2h_bytes - d0) // n_steps
 
 
+def run_workload(name, layers_arg, pk):
+    """One of the further workloads, through the Python entry point: a batch of unequal prompts (lengths uniform
+    in the workload's range, seeded) in one step, then 256 decode steps with every sequence alive.  One JSON line:
+    decode tokens a second (the loop's own clock, synchronised around every step), the prompt step, and the
+    decode step's bytes (weights once, the cache of the live sequences at the middle step) over its time."""
+    import torch
+    from gguf_rs_cli_b200.api import from_random, generate
+    from gguf_rs_cli_b200.engine.generate import GenerationStats
+    cfg, model_name, n_prompts, lo, hi = WORKLOADS[name]
+    cfg = dict(cfg)
+    full_layers = cfg["num_hidden_layers"]
+    layers = full_layers if layers_arg is None else layers_arg
+    cfg["num_hidden_layers"] = layers
+    llm = from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(lo, hi + 1, (n_prompts,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    ctx = cfg["max_position_embeddings"]
+    sampler = ClockSampler()
+    sampler.start()
+    best = None
+    for rep in range(3):                                  # the first pass warms up (kernels, graphs of this batch size)
+        stats = GenerationStats()
+        t0 = sampler.mark()
+        out = generate(llm, prompts, max_tokens=WORKLOAD_STEPS, temperature=0.0, stop_token_ids=[], max_batch=64,
+                       ctx_len=ctx, stats=stats)
+        t1 = sampler.mark()
+        assert all(len(o) == WORKLOAD_STEPS for o in out)
+        if rep and (best is None or stats.decode_seconds < best[0].decode_seconds):
+            best = (stats, t0, t1)
+    sampler.stop()
+    stats, t0, t1 = best
+    ms = stats.decode_seconds * 1e3 / stats.decode_steps
+    mid_tokens = sum(lens) + n_prompts * (WORKLOAD_STEPS // 2)
+    step_bytes = weight_bytes(cfg, layers) + mid_tokens * kv_bytes_per_token(cfg, layers)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    flops = sum(prefill_flops(cfg, layers, n) for n in lens)
+    line = {
+        "metric": f"{model_name} decode tok/s @ batch {n_prompts} (prompts of {lo} to {hi} tokens, {WORKLOAD_STEPS} steps)",
+        "value": round(n_prompts * 1000.0 / ms, 2), "unit": "tokens/s", "n_gpus": 1, "steps": stats.decode_steps, "warmup": 1,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic token ids, random weights N(0,0.02)", "impl": "ours",
+        "config": {"model": model_name, "layers": layers, "layers_full": full_layers, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": n_prompts,
+                   "seq_len": ctx, "prompt_tokens": sum(lens), "parallelism": "single-gpu", "peaks": pk["source"],
+                   "timing": "through generate(), host ids in and out, synchronised around every step"},
+        "clocks": sampler.summary(t0, t1),
+        "prefill": {"value": round(stats.prompt_tokens / stats.prefill_seconds, 1), "tokens": stats.prompt_tokens,
+                    "ms": round(stats.prefill_seconds * 1e3, 3),
+                    "frac": round(flops / stats.prefill_seconds / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": step_bytes},
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=SHAPE_8B["num_hidden_layers"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (profiles)")
+    ap.add_argument("--shape", default="8b", choices=["8b", "1b", "13b"],
+                    help="8b: the headline line; 1b, 13b: the further workloads (unequal prompts, 256 decode steps)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1/64, prefill and e2e")
     ap.add_argument("--temperature", type=float, default=0.0, help="sampling of the device-timed decode steps (default greedy)")
@@ -215,6 +294,10 @@ def main():
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup = max(args.warmup, 3)
+    if args.shape != "8b":
+        return run_workload(args.shape, args.layers, peaks())
+    if args.layers is None:
+        args.layers = SHAPE_8B["num_hidden_layers"]
 
     import torch
     from gguf_rs_cli_b200 import native
@@ -263,9 +346,11 @@ def main():
                            "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
         points = {}
         for b in (1, 64):
-            p_tok_s, p_ms, _, _ = measure_decode(llm, b, max(8, args.steps // 2), warmup, cfg)
+            p_steps = max(8, args.steps // 2)
+            p_tok_s, p_ms, _, p_ctx = measure_decode(llm, b, p_steps, warmup, cfg)
             points[f"decode_b{b}"] = round(p_tok_s, 2)
             points[f"decode_b{b}_ms"] = round(p_ms, 4)
+            points[f"decode_b{b}_frac"] = round((wbytes + b * p_ctx * kvb) / (p_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         line["points"] = points
     if args.prompt_steps:
         # short prompt steps: bound by the weights they stream (once) rather than by the tensor rate

@@ -50,6 +50,35 @@ __device__ __forceinline__ bool epilogue_any(bool flag) {
 }
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// v[jj] = the sum over a shared tile's CTAs, in ascending order, of token c0 + jj of this thread's feature: S partial
+// tiles x C tokens of loads in flight at a time (every round of loads costs a trip to L2, and the kernel after
+// this one waits for it: few CTAs on a tile take more tokens per round).  base: the first CTA's first slot, at
+// this thread's feature.
+template <int BN, int S, int C>
+__device__ __forceinline__ void sum_partials(const float* base, int first_which, int n_ctas, int c0, int cols, float (&v)[16]) {
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) v[jj] = 0.f;
+#pragma unroll
+    for (int j0 = 0; j0 < 16; j0 += C) {
+        if (c0 + j0 >= cols) break;
+        for (int s0 = 0; s0 < n_ctas; s0 += S) {
+            float ld[S][C];
+#pragma unroll
+            for (int si = 0; si < S; ++si) {
+                const int s = s0 + si;
+                const float* part = base + (size_t(s) * 2 + (s == 0 ? first_which : 0)) * (BN * BM);
+#pragma unroll
+                for (int jj = 0; jj < C; ++jj)
+                    ld[si][jj] = (s < n_ctas && c0 + j0 + jj < cols) ? __ldcg(part + (c0 + j0 + jj) * BM) : 0.f;
+            }
+#pragma unroll
+            for (int si = 0; si < S; ++si)
+#pragma unroll
+                for (int jj = 0; jj < C; ++jj) v[j0 + jj] += ld[si][jj];
+        }
+    }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x, TcParams p) {
@@ -221,30 +250,9 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
                     if (whole) {
                         tmem_ld16(taddr + c0, v);
                     } else {
-                        // the CTAs' partial sums in ascending order; 8 tokens x 8 partial tiles of loads in flight
-                        // (every round of loads costs a trip to L2, and the kernel after this one waits for it)
-#pragma unroll
-                        for (int jj = 0; jj < 16; ++jj) v[jj] = 0.f;
                         const float* base = p.scratch + size_t(first_cta) * 2 * (BN * BM) + row;
-#pragma unroll
-                        for (int j0 = 0; j0 < 16; j0 += 8) {
-                            if (c0 + j0 >= cols) break;
-                            for (int s0 = 0; s0 < n_ctas; s0 += 8) {
-                                float ld[8][8];
-#pragma unroll
-                                for (int si = 0; si < 8; ++si) {
-                                    const int s = s0 + si;
-                                    const float* part = base + (size_t(s) * 2 + (s == 0 ? first_which : 0)) * (BN * BM);
-#pragma unroll
-                                    for (int jj = 0; jj < 8; ++jj)
-                                        ld[si][jj] = (s < n_ctas && c0 + j0 + jj < cols) ? __ldcg(part + (c0 + j0 + jj) * BM) : 0.f;
-                                }
-#pragma unroll
-                                for (int si = 0; si < 8; ++si)
-#pragma unroll
-                                    for (int jj = 0; jj < 8; ++jj) v[j0 + jj] += ld[si][jj];
-                            }
-                        }
+                        if (n_ctas <= 4) sum_partials<BN, 4, 16>(base, first_which, n_ctas, c0, cols, v);
+                        else sum_partials<BN, 8, 8>(base, first_which, n_ctas, c0, cols, v);
                     }
                     tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, true, c0, cols, v, rstd_s, ssq_s,
                                         BN == 16 && p.resid_x ? x_early : nullptr);
