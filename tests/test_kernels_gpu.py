@@ -105,7 +105,7 @@ TC_SHAPES = [(1, 256, 512), (8, 128, 64), (16, 1000, 4096), (33, 300, 200), (64,
              (129, 6144, 1024), (300, 520, 4096), (700, 257, 328)]
 
 
-@pytest.mark.parametrize("T,N,Kd", TC_SHAPES)
+@pytest.mark.parametrize("T,N,Kd", TC_SHAPES + [(3, 40, 72), (9, 1000, 328), (16, 6144, 4096), (2, 130, 6144)])
 @pytest.mark.parametrize("out_dtype", [F32, BF])
 def test_gemm_tensor_core(T, N, Kd, out_dtype):
     k = K()
