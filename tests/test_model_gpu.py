@@ -17,7 +17,7 @@ def entry(slot, tokens, want):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("name", NAMES + ["E"])
 def test_whole_request_alone(name, dtype):
     eng = new_engine(name, dtype)
     for n, seed in [(1, 1), (5, 2), (33, 3), (100, 4)]:
@@ -30,7 +30,7 @@ def test_whole_request_alone(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("name", NAMES + ["E"])
 def test_last_32_one_by_one(name, dtype):
     eng = new_engine(name, dtype)
     n, seed = 90, 7

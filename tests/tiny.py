@@ -44,7 +44,17 @@ TINY_D = {
     "hidden_act": "silu", "attention_bias": True, "eos_token_id": 7,
 }
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# Sizes that fit no fast kernel: a width and an intermediate size that are no multiples of 8 (the tensor-core
+# product needs 16-byte rows), heads of 20, an odd vocabulary.  Whatever kernel runs, the result must be right.
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 5, "num_key_value_heads": 5, "head_dim": 20,
+    "intermediate_size": 52, "vocab_size": 257, "rope_theta": 1000.0, "rope_scaling": None,
+    "rms_norm_eps": 1e-5, "max_position_embeddings": 256, "tie_word_embeddings": True,
+    "hidden_act": "silu", "attention_bias": False, "eos_token_id": 0,
+}
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def qk_std(cfg, score_std=1.5):
