@@ -153,8 +153,14 @@ def measure_decode(llm, batch, steps, warmup, cfg, sampling=None):
     n0 = native.launch_count()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(steps):
-        toks = backend.run(slots, [[t] for t in toks], keys, params)
+    # as the generation loop drives it: each step is launched, fed on the device, before the tokens of the step in
+    # front of it are read, so the device does not wait for the host between steps
+    pending = backend.begin(slots, [[t] for t in toks], keys, params)
+    for i in range(steps):
+        ahead = backend.begin_after(pending) if i + 1 < steps else None
+        toks = backend.finish(pending)
+        if i + 1 < steps:
+            pending = ahead if ahead is not None else backend.begin(slots, [[t] for t in toks], keys, params)
     end.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(end) / steps

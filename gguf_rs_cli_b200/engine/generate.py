@@ -7,6 +7,13 @@ the last logits; a stop token ends the sequence and is not emitted; then the cou
 limit; then the context limit (position >= context - 1); else the token is emitted
 and fed back.  The loop itself touches no device: it drives a backend (`open`,
 `close`, `run`, `admit`), so its decisions are tested on the host with a scripted one.
+
+A backend that can launch a step without waiting for it (`begin`, `begin_after`,
+`finish`) is driven one step ahead: while no sequence of the batch can end by a limit,
+the next step is launched, fed on the device with the tokens of the step in flight,
+before those tokens are read.  A stop token is then found one step late: the sequence's
+row of the step that ran ahead is dropped, and its slot, already given back, is used by
+nobody before that step has run, because everything runs in one stream.
 """
 from __future__ import annotations
 
@@ -26,6 +33,22 @@ class _Live:
     slot: Optional[int]
     feed: List[int]
     pos: int = 0
+
+
+class _StepByStep:
+    """A backend that only has `run`, as one that launches and finishes: every step is finished when it begins."""
+
+    def __init__(self, backend):
+        self.backend = backend
+
+    def begin(self, slots, feeds, keys, params):
+        return self.backend.run(slots, feeds, keys, params)
+
+    def begin_after(self, pending):
+        return None
+
+    def finish(self, pending):
+        return pending
 
 
 @dataclass
@@ -65,6 +88,7 @@ def generate_ids(backend, prompts: Sequence[Sequence[int]], max_tokens: int, par
     results: List[List[int]] = [[] for _ in prompts]
     keys = [stream_key(params.seed, i) for i in range(len(prompts))]
     now = clock or (lambda: 0.0)
+    steps = backend if hasattr(backend, "begin_after") else _StepByStep(backend)
     nxt = 0
     while nxt < len(prompts):
         window = prompts[nxt:nxt + max_batch] if max_batch else prompts[nxt:]
@@ -76,25 +100,36 @@ def generate_ids(backend, prompts: Sequence[Sequence[int]], max_tokens: int, par
             for i in range(nxt, nxt + n):
                 live.append(_Live(i, backend.open(), list(prompts[i])))
             nxt += n
-            first = True
             if stats:
                 stats.batches += 1
+            first = True
+            rows, counts = live, [len(s.feed) for s in live]
+            t0 = now()
+            pending = steps.begin([s.slot for s in rows], [s.feed for s in rows], [keys[s.request] for s in rows], params)
             while live:
-                t0 = now()
-                sampled = backend.run([s.slot for s in live], [s.feed for s in live], [keys[s.request] for s in live], params)
+                # The step after, before this one's tokens are read: only while its rows would be this step's rows,
+                # so none may have ended already and none may end by a limit now; a stop token shows one step late.
+                ahead = None
+                if all(s.slot is not None for s in rows) and not any(
+                        len(results[s.request]) >= max_tokens or s.pos + c >= ctx - 1 for s, c in zip(rows, counts)):
+                    ahead = steps.begin_after(pending)
+                sampled = steps.finish(pending)
                 dt = now() - t0
+                t0 = now()
                 if stats:
                     stats.step_batch_sizes.append(len(live))
                     if first:
-                        stats.prompt_tokens += sum(len(s.feed) for s in live)
+                        stats.prompt_tokens += sum(counts)
                         stats.prefill_seconds += dt
                     else:
                         stats.decode_steps += 1
                         stats.decode_seconds += dt
                 first = False
                 still = []
-                for k, (s, tok) in enumerate(zip(live, sampled)):
-                    s.pos += len(s.feed)
+                for s, c, tok in zip(rows, counts, sampled):
+                    if s.slot is None:                     # ended a step ago: this row ran ahead for nothing
+                        continue
+                    s.pos += c
                     tok = int(tok)
                     if tok in stops or len(results[s.request]) >= max_tokens or s.pos >= ctx - 1:
                         backend.close(s.slot)          # given back at once: the next batch may use it
@@ -108,6 +143,13 @@ def generate_ids(backend, prompts: Sequence[Sequence[int]], max_tokens: int, par
                     s.feed = [tok]
                     still.append(s)
                 live = still
+                if ahead is not None:
+                    pending, counts = ahead, [1] * len(rows)
+                    if not live:
+                        steps.finish(ahead)                # nobody is left to read it
+                elif live:
+                    rows, counts = live, [1] * len(live)
+                    pending = steps.begin([s.slot for s in rows], [s.feed for s in rows], [keys[s.request] for s in rows], params)
         finally:
             # a step, a callback or the cache may raise: whatever the batch still holds is given back
             for s in live:

@@ -170,6 +170,8 @@ def test_decode_steps_updated_in_place_cross_pages(name):
         for g, w in zip(got, want):
             assert g == (w[:w.index(stop)] if stop in w else w)        # the stop token itself is not given out
         assert eng.cache.slots.held_count == 0
+        # captured steps are launched before the tokens of the step in front of them are read; others are not
+        assert (backend.steps_ahead >= 20) if graphs else backend.steps_ahead == 0
 
 
 def test_decode_past_a_thousand_positions_splits_pages_and_changes_graphs():

@@ -137,6 +137,104 @@ def test_streaming_callback_and_keys():
     assert -(1 << 63) <= stream_key(123, 4) < (1 << 63)
 
 
+class ScriptedAhead(Scripted):
+    """The same sequences behind a backend that launches steps without waiting: a launched step's tokens exist
+    only when it is finished, a step launched after another feeds each sequence what that one sampled, at most two
+    steps are in flight, and no step is begun or launched ahead for a slot that is known to be given back."""
+
+    def __init__(self, *a, ahead_from=0, **kw):
+        super().__init__(*a, **kw)
+        self.in_flight = []
+        self.serial = 0
+        self.ahead_from = ahead_from          # begin_after answers None for the first steps (as uncaptured steps do)
+        self.seq = {}                         # slot -> [first prompt token, steps launched]
+
+    def open(self):
+        s = super().open()
+        self.seq[s] = None
+        return s
+
+    def _launch(self, slots, feeds, kind):
+        assert len(self.in_flight) < 2, "more than two steps in flight"
+        for s in slots:
+            assert s in self.state, "a step was launched for a slot that is not held"
+        self.serial += 1
+        out = []
+        for s, f in zip(slots, feeds):
+            if self.seq[s] is None:
+                self.seq[s] = [f[0], 0]
+            elif f is not None:
+                assert f == [self.seq[s][0] + self.seq[s][1]], "fed something else than the token sampled last"
+            self.seq[s][1] += 1
+            out.append(self.seq[s][0] + self.seq[s][1])
+        h = {"slots": list(slots), "out": out}
+        self.in_flight.append(h)
+        self.log.append((kind, list(slots)))
+        return h
+
+    def begin(self, slots, feeds, keys, params):
+        return self._launch(slots, feeds, "begin")
+
+    def begin_after(self, pending):
+        if self.serial < self.ahead_from:
+            return None
+        assert pending in self.in_flight, "launched after a step that was already finished"
+        return self._launch(pending["slots"], [None] * len(pending["slots"]), "ahead")
+
+    def finish(self, pending):
+        assert self.in_flight and self.in_flight[0] is pending, "steps are finished in the order of their launch"
+        self.in_flight.pop(0)
+        return pending["out"]
+
+
+def _ahead(**kw):
+    return ScriptedAhead(**kw)
+
+
+@pytest.mark.parametrize("ahead_from", [0, 3])
+def test_steps_launched_ahead_give_the_tokens_of_steps_run_one_by_one(ahead_from):
+    import random
+    rng = random.Random(5)
+    for trial in range(60):
+        n = rng.randint(1, 7)
+        prompts = [[rng.randint(1, 40) * 10] + [1] * rng.randint(0, 5) for _ in range(n)]
+        kw = dict(max_tokens=rng.randint(0, 9), stop_token_ids=[rng.randint(1, 40) * 10 + rng.randint(1, 9) for _ in range(3)],
+                  max_batch=rng.choice([None, 2, 3]), context_limit=rng.choice([None, 9, 12]))
+        slots = rng.randint(1, 4)
+        want_stats, got_stats = GenerationStats(), GenerationStats()
+        want = generate_ids(Scripted(n_slots=slots), prompts, stats=want_stats, **kw)
+        b = _ahead(n_slots=slots, ahead_from=ahead_from)
+        got = generate_ids(b, prompts, stats=got_stats, **kw)
+        assert got == want, (trial, prompts, kw)
+        assert not b.state and not b.in_flight and sorted(b.free) == list(range(slots))
+        assert got_stats.generated_tokens == want_stats.generated_tokens and got_stats.batches == want_stats.batches
+        assert got_stats.prompt_tokens == want_stats.prompt_tokens
+
+
+def test_a_stop_token_costs_one_row_of_the_step_that_ran_ahead():
+    b = _ahead(n_slots=2)
+    out = generate_ids(b, [[10], [20]], max_tokens=6, stop_token_ids=[13])
+    assert out == [[11, 12], [21, 22, 23, 24, 25, 26]]
+    kinds = [e for e in b.log if e[0] in ("begin", "ahead")]
+    # prompts, two steps ahead (the second carries the sequence that its predecessor ends), one step begun anew
+    # for the sequence that is left, then ahead again; the last step is not launched ahead: the count limit is known
+    assert kinds[:4] == [("begin", [0, 1]), ("ahead", [0, 1]), ("ahead", [0, 1]), ("ahead", [0, 1])]
+    assert kinds[4] == ("begin", [1]) and all(k == ("ahead", [1]) for k in kinds[5:])
+    i_close = b.log.index(("close", 0))
+    assert b.log[i_close - 1][0] == "ahead"       # the slot was given back while the step that ran ahead was in flight
+
+
+def test_a_failure_with_a_step_in_flight_gives_every_slot_back():
+    b = _ahead(n_slots=3)
+
+    def boom(i, tok):
+        if tok == 12:
+            raise RuntimeError("callback")
+    with pytest.raises(RuntimeError):
+        generate_ids(b, [[10], [20], [30]], max_tokens=5, on_token=boom)
+    assert not b.state and sorted(b.free) == [0, 1, 2]
+
+
 def test_decode_split_rule_is_fixed_within_a_graph_class():
     """A captured decode graph is keyed by the class of the longest sequence: within a class the number of page
     splits must not change, for any batch size, and it never asks for more CTAs than the rule allows."""
