@@ -4,9 +4,10 @@
 // keys and values serves the whole group with a handful of instructions per page:
 // S = Q K^T and O += P V through mma.sync m16n8k16 (bf16 in, f32 accumulate), softmax
 // in 32-bit registers.  A CTA is (token, KV head tile, split of the token's pages); its
-// 4 warps each take 16 of a page's 64 keys; pages stream through a 3-stage cp.async
-// ring.  The warps' results are merged in warp order, the splits' results by the CTA
-// that arrives last, in split order (scratch memory + a counter; nobody waits).
+// 4 warps each take 16 of a page's 64 keys (or its 2 warps 16 of half a page's 32, four
+// such CTAs on an SM); pages stream through a 3-stage cp.async ring.  The warps' results
+// are merged in warp order, the splits' results by the CTA that arrives last, in split
+// order (scratch memory + a counter; nobody waits).
 // Same arithmetic as src/model/llama.rs:374-394.  Other head sizes take the CUDA-core
 // decode kernel.
 #include <math.h>
@@ -15,8 +16,6 @@
 
 namespace {
 
-constexpr int DM_THREADS = 128;
-constexpr int DM_WARPS = 4;
 constexpr int DM_ROWS = 16;           // query heads per tile
 constexpr int DM_STAGES = 3;
 
@@ -110,16 +109,20 @@ __device__ __forceinline__ void dm_merge_splits(const DmParams& p, int t, int h0
     }
 }
 
-template <int HD>
-__global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmParams p) {
+// WARPS warps take 16 keys each of a unit of WARPS * 16 keys: a whole page with four warps, half a page with two.
+// The CTA of two warps needs half the shared memory, so four of them fit an SM where two of the other do: steps
+// with more CTAs than fit the device at once in the one shape and no more than fit in the other run in one round.
+template <int HD, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmParams p) {
     constexpr int CH = HD / 8, KS = HD / 16, OT = HD / 8, HALF = HD / 2;
-    constexpr int PAGE_ELEMS = GB_PAGE * HD;
+    constexpr int THREADS = WARPS * 32, UK = WARPS * 16, UPP = GB_PAGE / UK;      // keys per unit, units per page
+    constexpr int PAGE_ELEMS = GB_PAGE * HD, UNIT_ELEMS = UK * HD;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                  // [16][HD]
-    __nv_bfloat16* ks = qs + DM_ROWS * HD;                                            // [stages][64][HD]
-    __nv_bfloat16* vs = ks + DM_STAGES * PAGE_ELEMS;                                  // [stages][64][HD]
-    float* merge_o = reinterpret_cast<float*>(ks);                                    // reused after the loop: [4][16][HD]
-    __shared__ float m_s[DM_WARPS][DM_ROWS], l_s[DM_WARPS][DM_ROWS];
+    __nv_bfloat16* ks = qs + DM_ROWS * HD;                                            // [stages][UK][HD]
+    __nv_bfloat16* vs = ks + DM_STAGES * UNIT_ELEMS;                                  // [stages][UK][HD]
+    float* merge_o = reinterpret_cast<float*>(ks);                                    // reused after the loop: [WARPS][16][HD]
+    __shared__ float m_s[WARPS][DM_ROWS], l_s[WARPS][DM_ROWS];
     __shared__ int last_flag;
 
     // What the kernel in front writes is q (and k_new, v_new).  The index arrays were in place before the step
@@ -143,7 +146,7 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
     if (b < 0) {
         if (early) gb_grid_wait();                         // `out` may still be read by a kernel further back
         if (split == 0)
-            for (int i = tid; i < heads * HD; i += DM_THREADS)
+            for (int i = tid; i < heads * HD; i += THREADS)
                 p.out[size_t(t) * p.ldo + size_t(h0) * HD + i] = __float2bfloat16_rn(0.f);
         return;
     }
@@ -152,78 +155,92 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
     const int first_page = lo >> GB_PAGE_SHIFT, n_pages = (pos >> GB_PAGE_SHIFT) - first_page + 1;
     const int pg_begin = first_page + int((long long)split * n_pages / p.splits);
     const int pg_end = first_page + int((long long)(split + 1) * n_pages / p.splits);
+    // the split's units; those of its pages that lie wholly before the window or behind the token are left out
+    const int u_begin = max(pg_begin * UPP, lo / UK), u_end = min(pg_end * UPP, pos / UK + 1);
     const int* trow = p.table + size_t(b) * p.table_width;
     const bool own_kv = p.rotate && p.k_new != nullptr;
 
-    auto load_page = [&](int pg, int stage) {
+    auto load_unit = [&](int u, int stage) {
+        const int pg = u / UPP, row0 = (u % UPP) * UK;
         const int phys = trow[pg % p.ring_pages];
-        const size_t off = (size_t(phys) * p.nkv + g) * size_t(PAGE_ELEMS);
-        __nv_bfloat16* kd = ks + stage * PAGE_ELEMS;
-        __nv_bfloat16* vd = vs + stage * PAGE_ELEMS;
-        for (int i = tid; i < GB_PAGE * CH; i += DM_THREADS) {
+        const size_t off = (size_t(phys) * p.nkv + g) * size_t(PAGE_ELEMS) + size_t(row0) * HD;
+        __nv_bfloat16* kd = ks + stage * UNIT_ELEMS;
+        __nv_bfloat16* vd = vs + stage * UNIT_ELEMS;
+        for (int i = tid; i < UK * CH; i += THREADS) {
             int r = i / CH, c = i - r * CH;
-            const int key = pg * GB_PAGE + r;              // rows beyond the sequence are read as zeros, and so
+            const int key = u * UK + r;                    // rows beyond the sequence are read as zeros, and so
             bool ok = key < pos || (key == pos && !own_kv);   // is the token's own row when this kernel makes it
             dm_cp_async16(kd + dm_swz<HD>(r, c), p.kc + off + size_t(r) * HD + c * 8, ok);
             dm_cp_async16(vd + dm_swz<HD>(r, c), p.vc + off + size_t(r) * HD + c * 8, ok);
         }
     };
 
-    // the group's queries (rows beyond the group are zeros; with the first page's copies if they need no
-    // rotation, else through registers below) and the first pages
+    // the group's queries (rows beyond the group are zeros; with the first unit's copies if they need no
+    // rotation, else through registers below) and the first units
     if (!p.rotate) {
-        for (int i = tid; i < DM_ROWS * CH; i += DM_THREADS) {
+        for (int i = tid; i < DM_ROWS * CH; i += THREADS) {
             int r = i / CH, c = i - r * CH;
             dm_cp_async16(qs + dm_swz<HD>(r, c), p.q + size_t(t) * p.ldq + size_t(h0 + min(r, heads - 1)) * HD + c * 8, r < heads);
         }
     }
 #pragma unroll
     for (int s = 0; s < DM_STAGES - 1; ++s) {
-        if (pg_begin + s < pg_end) load_page(pg_begin + s, s);
+        if (u_begin + s < u_end) load_unit(u_begin + s, s);
         dm_commit();
     }
     if (early) gb_grid_wait();
-    float sn = 0.f, cs = 1.f;
-    int d0 = 0, d1 = 0;
-    float own0 = 0.f, own1 = 0.f;                     // this thread's two elements of the token's own key or value
+    // this thread's pairs of every row: pair pi is (pi, pi + half) or (2 pi, 2 pi + 1) inside the rotation,
+    // unchanged beyond it; a CTA of fewer threads than pairs gives each thread PPT of them
+    constexpr int PPT = HALF > THREADS ? HALF / THREADS : 1;
+    constexpr int LANES = HALF / PPT;                      // threads across a row's pairs
+    float sn[PPT], cs[PPT];
+    int d0[PPT], d1[PPT];
+    float own0[PPT], own1[PPT], ownv0[PPT], ownv1[PPT];     // the token's own key and value, this thread's elements
     const bool has_own = own_kv && pg_begin < pg_end && pg_end - 1 == (pos >> GB_PAGE_SHIFT);
+#pragma unroll
+    for (int e = 0; e < PPT; ++e) { sn[e] = 0.f; cs[e] = 1.f; d0[e] = d1[e] = 0; own0[e] = own1[e] = ownv0[e] = ownv1[e] = 0.f; }
     if (p.rotate) {
-        // pair `pi` of every row: (pi, pi + half) or (2 pi, 2 pi + 1) inside the rotation, unchanged beyond it
-        const int pi = tid % HALF, half = p.inv_freq ? p.rotary_dim / 2 : 0;
-        const float freq = pi < half ? p.inv_freq[pi] : 0.f;
-        d0 = pi < half ? (p.pairing ? 2 * pi : pi) : 2 * pi;
-        d1 = pi < half ? (p.pairing ? 2 * pi + 1 : pi + half) : 2 * pi + 1;
-        constexpr int RPT = DM_ROWS * HALF / DM_THREADS;         // rows per thread
-        float x0[RPT], x1[RPT];
+        const int half = p.inv_freq ? p.rotary_dim / 2 : 0;
 #pragma unroll
-        for (int j = 0; j < RPT; ++j) {
-            const int r = tid / HALF + j * (DM_THREADS / HALF);
-            x0[j] = x1[j] = 0.f;
-            if (r < heads) {
-                const __nv_bfloat16* src = p.q + size_t(t) * p.ldq + size_t(h0 + r) * HD;
-                x0[j] = __bfloat162float(src[d0]);
-                x1[j] = __bfloat162float(src[d1]);
-            }
+        for (int e = 0; e < PPT; ++e) {
+            const int pi = tid % LANES + e * LANES;
+            const float freq = pi < half ? p.inv_freq[pi] : 0.f;
+            d0[e] = pi < half ? (p.pairing ? 2 * pi : pi) : 2 * pi;
+            d1[e] = pi < half ? (p.pairing ? 2 * pi + 1 : pi + half) : 2 * pi + 1;
+            if (pi < half) sincosf(float(pos) * freq, &sn[e], &cs[e]);
         }
-        if (has_own) {
-            const size_t src = size_t(t) * p.ldq + size_t(g) * HD;
-            if (tid < HALF) {
-                own0 = __bfloat162float(p.k_new[src + d0]);
-                own1 = __bfloat162float(p.k_new[src + d1]);
-            } else if (tid < 2 * HALF) {
-                const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(p.v_new + src + 2 * (tid - HALF));
-                own0 = __low2float(x);
-                own1 = __high2float(x);
-            }
-        }
-        if (pi < half) sincosf(float(pos) * freq, &sn, &cs);
+        constexpr int RSTEP = THREADS / LANES;                   // rows a pass of all threads covers
+        constexpr int RPT = DM_ROWS / RSTEP;                     // rows per thread
 #pragma unroll
-        for (int j = 0; j < RPT; ++j) {
-            const int r = tid / HALF + j * (DM_THREADS / HALF);
-            float y0, y1;
-            gb_rotate(x0[j], x1[j], cs, sn, y0, y1);
-            qs[dm_swz<HD>(r, d0 >> 3) + (d0 & 7)] = __float2bfloat16_rn(y0);
-            qs[dm_swz<HD>(r, d1 >> 3) + (d1 & 7)] = __float2bfloat16_rn(y1);
+        for (int e = 0; e < PPT; ++e) {
+            float x0[RPT], x1[RPT];
+#pragma unroll
+            for (int j = 0; j < RPT; ++j) {
+                const int r = tid / LANES + j * RSTEP;
+                x0[j] = x1[j] = 0.f;
+                if (r < heads) {
+                    const __nv_bfloat16* src = p.q + size_t(t) * p.ldq + size_t(h0 + r) * HD;
+                    x0[j] = __bfloat162float(src[d0[e]]);
+                    x1[j] = __bfloat162float(src[d1[e]]);
+                }
+            }
+            if (has_own && tid < LANES) {
+                const size_t src = size_t(t) * p.ldq + size_t(g) * HD;
+                const int pi = tid + e * LANES;
+                own0[e] = __bfloat162float(p.k_new[src + d0[e]]);
+                own1[e] = __bfloat162float(p.k_new[src + d1[e]]);
+                const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(p.v_new + src + 2 * pi);
+                ownv0[e] = __low2float(x);
+                ownv1[e] = __high2float(x);
+            }
+#pragma unroll
+            for (int j = 0; j < RPT; ++j) {
+                const int r = tid / LANES + j * RSTEP;
+                float y0, y1;
+                gb_rotate(x0[j], x1[j], cs[e], sn[e], y0, y1);
+                qs[dm_swz<HD>(r, d0[e] >> 3) + (d0[e] & 7)] = __float2bfloat16_rn(y0);
+                qs[dm_swz<HD>(r, d1[e] >> 3) + (d1[e] & 7)] = __float2bfloat16_rn(y1);
+            }
         }
     }
 
@@ -232,34 +249,40 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
     for (int i = 0; i < OT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     unsigned qf[KS][4];
-    const int key_base = warp * 16;                          // this warp's 16 keys of every page
+    const int key_base = warp * 16;                          // this warp's 16 keys of every unit
 
-    for (int pg = pg_begin; pg < pg_end; ++pg) {
-        const int it = pg - pg_begin, stage = it % DM_STAGES;
-        if (pg + DM_STAGES - 1 < pg_end) load_page(pg + DM_STAGES - 1, (it + DM_STAGES - 1) % DM_STAGES);
+    for (int u = u_begin; u < u_end; ++u) {
+        const int it = u - u_begin, stage = it % DM_STAGES;
+        if (u + DM_STAGES - 1 < u_end) load_unit(u + DM_STAGES - 1, (it + DM_STAGES - 1) % DM_STAGES);
         dm_commit();
         dm_wait<DM_STAGES - 1>();
         __syncthreads();
-        if (has_own && pg == pg_end - 1) {
-            // the token's own key (rotated) and value: into the page in shared memory, and by the first head
+        if (has_own && u == pos / UK) {
+            // the token's own key (rotated) and value: into the unit in shared memory, and by the first head
             // tile of the KV head into the cache
-            const int r = pos & (GB_PAGE - 1);
+            const int r = pos & (UK - 1);
             const bool writes = (blockIdx.y % gtiles) == 0;
-            const size_t dst = (size_t(trow[pg % p.ring_pages]) * p.nkv + g) * size_t(PAGE_ELEMS) + size_t(r) * HD;
-            if (tid < HALF) {
-                float r0, r1;
-                gb_rotate(own0, own1, cs, sn, r0, r1);
-                const __nv_bfloat16 y0 = __float2bfloat16_rn(r0), y1 = __float2bfloat16_rn(r1);
-                __nv_bfloat16* kt_w = ks + stage * PAGE_ELEMS;
-                kt_w[dm_swz<HD>(r, d0 >> 3) + (d0 & 7)] = y0;
-                kt_w[dm_swz<HD>(r, d1 >> 3) + (d1 & 7)] = y1;
-                if (writes) { p.kc_w[dst + d0] = y0; p.kc_w[dst + d1] = y1; }
-            } else if (tid < 2 * HALF) {
-                const int e = 2 * (tid - HALF);
-                const __nv_bfloat162 x = __floats2bfloat162_rn(own0, own1);
-                __nv_bfloat16* vt_w = vs + stage * PAGE_ELEMS;
-                *reinterpret_cast<__nv_bfloat162*>(vt_w + dm_swz<HD>(r, e >> 3) + (e & 7)) = x;
-                if (writes) *reinterpret_cast<__nv_bfloat162*>(p.vc_w + dst + e) = x;
+            const size_t dst = (size_t(trow[(pos >> GB_PAGE_SHIFT) % p.ring_pages]) * p.nkv + g) * size_t(PAGE_ELEMS) +
+                               size_t(pos & (GB_PAGE - 1)) * HD;
+            if (tid < LANES) {
+#pragma unroll
+                for (int e = 0; e < PPT; ++e) {
+                    float r0, r1;
+                    gb_rotate(own0[e], own1[e], cs[e], sn[e], r0, r1);
+                    const __nv_bfloat16 y0 = __float2bfloat16_rn(r0), y1 = __float2bfloat16_rn(r1);
+                    __nv_bfloat16* kt_w = ks + stage * UNIT_ELEMS;
+                    kt_w[dm_swz<HD>(r, d0[e] >> 3) + (d0[e] & 7)] = y0;
+                    kt_w[dm_swz<HD>(r, d1[e] >> 3) + (d1[e] & 7)] = y1;
+                    const int ev = 2 * (tid + e * LANES);
+                    const __nv_bfloat162 x = __floats2bfloat162_rn(ownv0[e], ownv1[e]);
+                    __nv_bfloat16* vt_w = vs + stage * UNIT_ELEMS;
+                    *reinterpret_cast<__nv_bfloat162*>(vt_w + dm_swz<HD>(r, ev >> 3) + (ev & 7)) = x;
+                    if (writes) {
+                        p.kc_w[dst + d0[e]] = y0;
+                        p.kc_w[dst + d1[e]] = y1;
+                        *reinterpret_cast<__nv_bfloat162*>(p.vc_w + dst + ev) = x;
+                    }
+                }
             }
             __syncthreads();
         }
@@ -268,8 +291,8 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
             for (int k = 0; k < KS; ++k)
                 dm_ldmatrix_x4(qf[k][0], qf[k][1], qf[k][2], qf[k][3], qs + dm_swz<HD>(lane & 15, 2 * k + (lane >> 4)));
         }
-        const __nv_bfloat16* kt = ks + stage * PAGE_ELEMS;
-        const __nv_bfloat16* vt = vs + stage * PAGE_ELEMS;
+        const __nv_bfloat16* kt = ks + stage * UNIT_ELEMS;
+        const __nv_bfloat16* vt = vs + stage * UNIT_ELEMS;
         // ---- S[16 heads x 16 keys]
         float s[2][4];
 #pragma unroll
@@ -282,7 +305,7 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
             dm_mma(s[1], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b2, b3);
         }
         // ---- mask (every head sees the same keys) and online softmax; rows lane/4 and lane/4 + 8
-        const int key0 = pg * GB_PAGE + key_base + 2 * (lane & 3);
+        const int key0 = u * UK + key_base + 2 * (lane & 3);
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -324,7 +347,7 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
     dm_wait<0>();
     __syncthreads();
 
-    // ---- merge the four warps (each saw a quarter of the keys) in warp order
+    // ---- merge the warps (each saw its share of the keys) in warp order
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -345,14 +368,14 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
         }
     }
     __syncthreads();
-    for (int i = tid; i < heads * HD; i += DM_THREADS) {
+    for (int i = tid; i < heads * HD; i += THREADS) {
         const int r = i / HD, d = i - r * HD;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < DM_WARPS; ++w) M = fmaxf(M, m_s[w][r]);
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, m_s[w][r]);
         float L = 0.f, acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < DM_WARPS; ++w) {
+        for (int w = 0; w < WARPS; ++w) {
             float wgt = m_s[w][r] == -INFINITY ? 0.f : exp2f((m_s[w][r] - M) * p.scale_log2);
             L += l_s[w][r] * wgt;
             acc += merge_o[(size_t(w) * DM_ROWS + r) * HD + d] * wgt;
@@ -375,7 +398,7 @@ __global__ void __launch_bounds__(DM_THREADS) attention_decode_mma_kernel(DmPara
     __syncthreads();
     if (!last_flag) return;
     __threadfence();
-    dm_merge_splits<HD>(p, t, h0, heads, tid, DM_THREADS);
+    dm_merge_splits<HD>(p, t, h0, heads, tid, THREADS);
     if (tid == 0) p.counters[t * gridDim.y + blockIdx.y] = 0;
 }
 
@@ -651,15 +674,15 @@ template <int HD> int launch_pw(const DmParams& p, dim3 grid, cudaStream_t strea
     return 0;
 }
 
-template <int HD> int launch_dm(const DmParams& p, dim3 grid, cudaStream_t stream) {
-    constexpr int SMEM = (DM_ROWS + 2 * DM_STAGES * GB_PAGE) * HD * 2;
+template <int HD, int WARPS> int launch_dm(const DmParams& p, dim3 grid, cudaStream_t stream) {
+    constexpr int SMEM = (DM_ROWS + 2 * DM_STAGES * WARPS * 16) * HD * 2;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attention_decode_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(attention_decode_mma_kernel<HD, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return gb_fail("gb_attention_decode_mma: cannot get %d bytes of shared memory", SMEM);
         configured = true;
     }
-    gb_launch(attention_decode_mma_kernel<HD>, grid, dim3(DM_THREADS), SMEM, stream, p);
+    gb_launch(attention_decode_mma_kernel<HD, WARPS>, grid, dim3(WARPS * 32), SMEM, stream, p);
     GB_LAUNCH_OK("gb_attention_decode_mma");
     return 0;
 }
@@ -668,6 +691,8 @@ template <int HD> int launch_dm(const DmParams& p, dim3 grid, cudaStream_t strea
 
 static int g_pages_kernel = 1;        // 0: never the kernel whose warps take whole pages (tuning aid)
 GB_API int gb_attention_decode_set_pages_kernel(int on) { g_pages_kernel = on; return 0; }
+static int g_two_warps = 1;           // CTAs of two warps: 0 never, 1 by the rule, 2 wherever the head size allows (tuning aid)
+GB_API int gb_attention_decode_set_two_warps(int mode) { g_two_warps = mode; return 0; }
 
 GB_API int gb_attention_decode_mma_supported(int hd, int cache_dtype, int q_dtype) {
     return cache_dtype == GB_BF16 && q_dtype == GB_BF16 && (hd == 64 || hd == 128);
@@ -707,7 +732,12 @@ static int decode_mma(const void* q, long long ldq, void* out, long long ldo, in
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (g_pages_kernel && (long long)T * nkv * gtiles * splits <= sms)       // few CTAs: a CTA's latency is the step's
         return hd == 64 ? launch_pw<64>(p, grid, stream) : launch_pw<128>(p, grid, stream);
-    return hd == 64 ? launch_dm<64>(p, grid, stream) : launch_dm<128>(p, grid, stream);
+    // Heads of 128: two CTAs of four warps fit an SM, or four CTAs of two warps.  A step with more CTAs than fit
+    // in the first shape, and no more than fit in the second, runs in one round with the second.
+    const long long ctas = (long long)T * nkv * gtiles * splits;
+    if (hd == 128 && g_two_warps && (g_two_warps == 2 || (ctas > 2LL * sms && ctas <= 4LL * sms)))
+        return launch_dm<128, 2>(p, grid, stream);
+    return hd == 64 ? launch_dm<64, 4>(p, grid, stream) : launch_dm<128, 4>(p, grid, stream);
 }
 
 GB_API int gb_attention_decode_mma(const void* q, long long ldq, void* out, long long ldo, int T, int nh, int nkv, int hd,

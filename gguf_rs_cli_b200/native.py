@@ -148,6 +148,7 @@ _SIGNATURES = {
                                      _P, _P, _I, _P],
     "gb_attention_decode_mma_supported": [_I, _I, _I],
     "gb_attention_decode_set_pages_kernel": [_I],
+    "gb_attention_decode_set_two_warps": [_I],
     "gb_attention_decode_scratch_floats": [_I, _I, _I, _I],
     "gb_attention_decode_supported": [_I, _I, _I],
     "gb_attention_prefill": [_P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _P],

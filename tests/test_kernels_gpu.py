@@ -223,14 +223,28 @@ def test_rope_and_cache_write(dtype, nh, nkv, hd, rot, pairing):
 
 def fill_cache(kseqs, vseqs, nkv, hd, dtype, n_pages=64, seed=0):
     lens = [k.shape[0] for k in kseqs]
+    n_pages = max(n_pages, sum((n + 63) // 64 for n in lens) + 3)
     table = page_layout(lens, n_pages, seed)
     kc, vc = make_cache(n_pages, nkv, hd, dtype)
+    rows = table.tolist()
     for b, (ks, vs) in enumerate(zip(kseqs, vseqs)):
-        for p in range(ks.shape[0]):
-            pg = int(table[b, p // 64])
-            kc[pg, :, p % 64, :] = ks[p].to(dtype).to(DEV)
-            vc[pg, :, p % 64, :] = vs[p].to(dtype).to(DEV)
+        for first in range(0, ks.shape[0], 64):
+            pg, cnt = rows[b][first // 64], min(64, ks.shape[0] - first)
+            kc[pg, :, :cnt, :] = ks[first:first + cnt].transpose(0, 1).to(dtype).to(DEV)
+            vc[pg, :, :cnt, :] = vs[first:first + cnt].transpose(0, 1).to(dtype).to(DEV)
     return table, kc, vc
+
+
+def last_query_attention(q, k, v, window=None):
+    """P.attention's last row alone (a decode step's query), for long sequences: q [n, nh, hd], k, v [n, nkv, hd]."""
+    n, nh, hd = q.shape
+    ratio = nh // k.shape[1]
+    lo = max(0, n - window) if window else 0
+    out = torch.zeros(nh, hd)
+    for h in range(nh):
+        s = (k[lo:, h // ratio, :] @ q[-1, h, :]) / math.sqrt(hd)
+        out[h] = P.softmax(s[None, :])[0] @ v[lo:, h // ratio, :]
+    return out.reshape(1, nh * hd)
 
 
 def attention_case(nh, nkv, hd, lens, qlens, dtype, seed, window=None, boost=None):
@@ -246,7 +260,8 @@ def attention_case(nh, nkv, hd, lens, qlens, dtype, seed, window=None, boost=Non
     qs = [x.to(dtype).float() for x in qs]
     ks = [x.to(dtype).float() for x in ks]
     vs = [x.to(dtype).float() for x in vs]
-    want = torch.cat([P.attention(q, k, v, window=window)[n - ql:] for q, k, v, n, ql in zip(qs, ks, vs, lens, qlens)])
+    want = torch.cat([last_query_attention(q, k, v, window) if ql == 1 and n > 300 else P.attention(q, k, v, window=window)[n - ql:]
+                      for q, k, v, n, ql in zip(qs, ks, vs, lens, qlens)])
     q = torch.cat([q[n - ql:] for q, n, ql in zip(qs, lens, qlens)]).reshape(-1, nh * hd).to(dtype).to(DEV)
     seq_of = torch.tensor(sum(([b] * ql for b, ql in enumerate(qlens)), []), dtype=torch.int32, device=DEV)
     pos = torch.tensor(sum((list(range(n - ql, n)) for n, ql in zip(lens, qlens)), []), dtype=torch.int32, device=DEV)
@@ -397,14 +412,38 @@ def test_sampling_ring_and_padding():
 
 
 # ----------------------------------------------------------- decode attention
+class two_warps:
+    """mma == "two": the tensor-core decode kernel in its shape of two warps and half pages (heads of 128), which
+    the library takes by itself only for steps of several hundred CTAs."""
+
+    def __init__(self, mma, hd):
+        self.on = mma == "two"
+        if self.on and hd != 128:
+            pytest.skip("CTAs of two warps are for heads of 128")
+
+    def __enter__(self):
+        from gguf_rs_cli_b200 import native
+        if self.on:
+            native.call("gb_attention_decode_set_two_warps", 2)
+
+    def __exit__(self, *a):
+        from gguf_rs_cli_b200 import native
+        native.call("gb_attention_decode_set_two_warps", 1)
+
+
 @pytest.mark.parametrize("nh,nkv,hd", [(6, 3, 32), (4, 1, 48), (8, 8, 16), (8, 2, 128), (5, 5, 80), (16, 1, 64),
                                        (12, 2, 256), (3, 1, 112), (40, 2, 64), (32, 8, 128), (7, 7, 128)])
 @pytest.mark.parametrize("splits", [None, 1, 3, 7])
-@pytest.mark.parametrize("mma", [False, True])
+@pytest.mark.parametrize("mma", [False, True, "two"])
 def test_attention_decode(nh, nkv, hd, splits, mma):
-    k = K()
     if mma and hd not in (64, 128):
         pytest.skip("the tensor-core decode kernel takes head sizes 64 and 128")
+    with two_warps(mma, hd):
+        _attention_decode(nh, nkv, hd, splits, bool(mma))
+
+
+def _attention_decode(nh, nkv, hd, splits, mma):
+    k = K()
     lens = [200, 1, 65, 130, 64, 513]
     q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, [1] * len(lens), BF, seed=hd + nh)
     # two padding tokens in the middle of the batch
@@ -428,11 +467,16 @@ def test_attention_decode(nh, nkv, hd, splits, mma):
     assert torch.equal(again, out)                 # counters were left at zero; the merge order is fixed
 
 
-@pytest.mark.parametrize("window", [1, 64, 65, 100, 300])
-@pytest.mark.parametrize("mma", [False, True])
-def test_attention_decode_far_key_and_window(window, mma):
+@pytest.mark.parametrize("window", [1, 31, 64, 65, 100, 300])
+@pytest.mark.parametrize("mma,hd", [(False, 64), (True, 64), (True, 128), ("two", 128)])
+def test_attention_decode_far_key_and_window(window, mma, hd):
+    with two_warps(mma, hd):
+        _far_key_and_window(window, bool(mma), hd)
+
+
+def _far_key_and_window(window, mma, hd):
     k = K()
-    nh, nkv, hd = 8, 2, 64
+    nh, nkv = 8, 2
     lens = [700, 300, 50]
     scale = 1 / math.sqrt(hd)
     q, seq_of, pos, table, kc, vc, want = attention_case(nh, nkv, hd, lens, [1, 1, 1], BF, 5, boost=(0, 3, 2))
@@ -468,16 +512,22 @@ def test_attention_decode_few_long_sequences_in_many_splits(splits, hd):
 @pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 128), (40, 2, 64), (7, 7, 128), (16, 1, 64)])
 @pytest.mark.parametrize("pairing,rot", [(0, 1.0), (1, 1.0), (0, 0.5), (0, 0.0)])
 @pytest.mark.parametrize("own_kv", [True, False])
-def test_attention_decode_rotating(nh, nkv, hd, pairing, rot, own_kv):
+@pytest.mark.parametrize("mma", [True, "two"])
+def test_attention_decode_rotating(nh, nkv, hd, pairing, rot, own_kv, mma):
+    with two_warps(mma, hd):
+        _attention_decode_rotating(nh, nkv, hd, pairing, rot, own_kv)
+
+
+def _attention_decode_rotating(nh, nkv, hd, pairing, rot, own_kv):
     """The decode kernel that rotates q and k and writes the cache itself gives, bit for bit, the output and
     the cache of the rotation kernel followed by the plain decode kernel: whole and split pages, a window,
-    groups of more than 16 heads (two CTAs share the token's own key), padding tokens, a position that opens
-    a page (64) and one that ends it (191)."""
+    groups of more than 16 heads (two CTAs share the token's own key), padding tokens, positions that open
+    a page (64) or half a page (32, 96) and positions that end one (191, 31)."""
     k = K()
-    lens = [200, 1, 65, 130, 64, 513, 192]
+    lens = [200, 1, 65, 130, 64, 513, 192, 33, 32, 97]
     _, seq_of, pos, table, kc, vc, _ = attention_case(nh, nkv, hd, lens, [1] * len(lens), BF, seed=3 * hd + nh)
     T = len(lens) + 1
-    rows = [0, 1, 2, 4, 5, 6, 7]
+    rows = [i for i in range(T) if i != 3]
     sp = torch.full((T,), -1, dtype=torch.int32, device=DEV)
     pp = torch.zeros(T, dtype=torch.int32, device=DEV)
     sp[rows], pp[rows] = seq_of, pos
