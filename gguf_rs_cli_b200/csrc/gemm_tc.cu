@@ -246,16 +246,31 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
             }
             if (finish) {
                 for (int c0 = 0; c0 < cols; c0 += 16) {
-                    float v[16];
+                    float v[16], xv[16];
+                    bool have_x = false;
                     if (whole) {
                         tmem_ld16(taddr + c0, v);
                     } else {
+                        // the last CTA of a shared tile: its rows of the residual stream are asked for with the
+                        // partial sums, not after them (one trip to L2 instead of two for every 16 tokens; tiles of 16
+                        // tokens have them already, and with tiles of 32 it measured slower: 5.17 against 5.07 ms
+                        // a step at 64 tokens, where tiles of 64 gain 0.05 of 5.9 ms at 128 tokens)
+                        if (BN >= 64 && p.resid_x) {
+#pragma unroll
+                            for (int jj = 0; jj < 16; ++jj)
+                                xv[jj] = (n < p.N && c0 + jj < cols) ? __ldcg(p.resid_x + size_t(w.t0 + c0 + jj) * p.ld_x + n) : 0.f;
+                            have_x = true;
+                        }
                         const float* base = p.scratch + size_t(first_cta) * 2 * (BN * BM) + row;
                         if (n_ctas <= 4) sum_partials<BN, 4, 16>(base, first_which, n_ctas, c0, cols, v);
                         else sum_partials<BN, 8, 8>(base, first_which, n_ctas, c0, cols, v);
                     }
-                    tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, true, c0, cols, v, rstd_s, ssq_s,
-                                        BN == 16 && p.resid_x ? x_early : nullptr);
+                    if constexpr (BN == 16)
+                        tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, true, c0, cols, v, rstd_s, ssq_s,
+                                            p.resid_x ? x_early : nullptr);
+                    else
+                        tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, true, c0, cols, v, rstd_s, ssq_s,
+                                            have_x ? xv : nullptr);
                 }
                 if (p.resid_x) tc_write_ssq<BN>(p, w.n0, w.t0, row, 0, cols, ssq_s);
                 if (!whole && threadIdx.x == 64) p.counters[w.tile] = 0;       // ready for the next launch
