@@ -215,8 +215,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(AdParams p
         last_flag = (old == p.splits - 1);
     }
     __syncthreads();
-    if (!last_flag) return;
-    __threadfence();
+    if (!last_flag) return;                               // the others' records are read from L2 (__ldcg): no fence here
     for (int i = threadIdx.x; i < heads * hd; i += AD_THREADS) {
         int gi = i / hd, d = i - gi * hd;
         const float* rec = p.scratch + (size_t(t) * p.nh + h0 + gi) * p.splits * (hd + 2);

@@ -396,8 +396,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmPara
         last_flag = (old == p.splits - 1);
     }
     __syncthreads();
-    if (!last_flag) return;
-    __threadfence();
+    if (!last_flag) return;                               // the others' records are read from L2 (__ldcg): no fence here
     dm_merge_splits<HD>(p, t, h0, heads, tid, THREADS);
     if (tid == 0) p.counters[t * gridDim.y + blockIdx.y] = 0;
 }
@@ -655,8 +654,7 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
         last_flag = (old == p.splits - 1);
     }
     __syncthreads();
-    if (!last_flag) return;
-    __threadfence();
+    if (!last_flag) return;                               // the others' records are read from L2 (__ldcg): no fence here
     dm_merge_splits<HD>(p, t, h0, heads, tid, PW_THREADS);
     if (tid == 0) p.counters[t * gridDim.y + blockIdx.y] = 0;
 }

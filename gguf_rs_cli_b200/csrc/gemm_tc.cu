@@ -236,13 +236,16 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
                 }
                 tc_fence_before();
                 if (lane == 0) mbar_arrive(&acc_empty[buf]);     // the accumulator may be overwritten
+                // The partial sums are at L2 before the counter counts this CTA (stores that bypass L1, a fence by
+                // every thread that stored, a barrier, then the atomic).  The CTA that sees all others counted reads
+                // their sums from L2 (__ldcg), after a barrier behind the atomic: nothing of it can run ahead, and it
+                // needs no fence of its own.  The barrier in front of the next atomic also keeps last_flag from being
+                // written before every thread has read it.
                 __threadfence();
                 epilogue_sync();
                 if (threadIdx.x == 64) last_flag = atomicAdd(&p.counters[w.tile], 1) == n_ctas - 1;
                 epilogue_sync();
                 finish = last_flag != 0;
-                if (finish) __threadfence();
-                epilogue_sync();                         // last_flag may be written again for the next unit
             }
             if (finish) {
                 for (int c0 = 0; c0 < cols; c0 += 16) {
