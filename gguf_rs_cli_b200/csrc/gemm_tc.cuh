@@ -186,6 +186,23 @@ __device__ __forceinline__ void tc_token_scales(const TcParams& p, int t0, int c
     }
 }
 
+// The sums of v[0] .. v[15], each over the warp's 32 lanes, in 16 shuffles instead of 80: at every step a lane keeps
+// half of its values and hands the other half to the lane that keeps those.  Bit for bit gb_warp_sum's sums (the same
+// pairs are added in the same order).  Lane L ends with the sum of the value whose index has bits 3..0 = L's bits 4..1.
+__device__ __forceinline__ float tc_warp_sum16(const float (&v)[16], int lane) {
+    const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4, h2 = lane & 2;
+    float a[8], b[4], c[2];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = (h16 ? v[i + 8] : v[i]) + __shfl_xor_sync(0xffffffffu, h16 ? v[i] : v[i + 8], 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) b[i] = (h8 ? a[i + 4] : a[i]) + __shfl_xor_sync(0xffffffffu, h8 ? a[i] : a[i + 4], 8);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) c[i] = (h4 ? b[i + 2] : b[i]) + __shfl_xor_sync(0xffffffffu, h4 ? b[i] : b[i + 2], 4);
+    float d = (h2 ? c[1] : c[0]) + __shfl_xor_sync(0xffffffffu, h2 ? c[0] : c[1], 2);
+    d += __shfl_xor_sync(0xffffffffu, d, 1);
+    return d;
+}
+
 // The last steps for 16 columns (tokens c0 .. c0+15 of the tile, those below c_end being valid) of this
 // thread's feature row n = n0 + row: v[jj] holds the finished sum of column c0 + jj.  x_early: the 16 values of
 // the residual stream at these places if the caller has read them already, else null.
@@ -217,11 +234,9 @@ __device__ __forceinline__ void tc_finish_chunk(const TcParams& p, int n0, int t
             }
             v[jj] = sq;
         }
-#pragma unroll
-        for (int jj = 0; jj < 16; ++jj) {
-            const float sq = gb_warp_sum(v[jj]);
-            if (lane == 0 && c0 + jj < c_end) ssq_s[quarter][c0 + jj] = sq;
-        }
+        const float sq = tc_warp_sum16(v, lane);
+        const int jj = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+        if ((lane & 1) == 0 && c0 + jj < c_end) ssq_s[quarter][c0 + jj] = sq;
     } else if (!p.swiglu) {
         if (n < p.N && waited) {
 #pragma unroll
