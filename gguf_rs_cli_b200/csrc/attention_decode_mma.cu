@@ -121,7 +121,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmPara
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                  // [16][HD]
     __nv_bfloat16* ks = qs + DM_ROWS * HD;                                            // [stages][UK][HD]
     __nv_bfloat16* vs = ks + DM_STAGES * UNIT_ELEMS;                                  // [stages][UK][HD]
-    float* merge_o = reinterpret_cast<float*>(ks);                                    // reused after the loop: [WARPS][16][HD]
+    float* merge_o = reinterpret_cast<float*>(ks);                                    // reused after the loop: [WARPS][16][MS]
+    constexpr int MS = HD + 8;        // its rows lie 8 banks apart: a warp's 8-byte stores of 8 rows x 4 columns take two passes, not eight
     __shared__ float m_s[WARPS][DM_ROWS], l_s[WARPS][DM_ROWS];
     __shared__ int last_flag;
 
@@ -354,13 +355,11 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmPara
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     {
         const int ra = lane >> 2, rb = ra + 8, col = 2 * (lane & 3);
-        float* mo = merge_o + size_t(warp) * DM_ROWS * HD;
+        float* mo = merge_o + size_t(warp) * DM_ROWS * MS;
 #pragma unroll
         for (int i = 0; i < OT; ++i) {
-            mo[ra * HD + 8 * i + col] = o[i][0];
-            mo[ra * HD + 8 * i + col + 1] = o[i][1];
-            mo[rb * HD + 8 * i + col] = o[i][2];
-            mo[rb * HD + 8 * i + col + 1] = o[i][3];
+            if (ra < heads) *reinterpret_cast<float2*>(mo + ra * MS + 8 * i + col) = make_float2(o[i][0], o[i][1]);
+            if (rb < heads) *reinterpret_cast<float2*>(mo + rb * MS + 8 * i + col) = make_float2(o[i][2], o[i][3]);
         }
         if ((lane & 3) == 0) {
             m_s[warp][ra] = m0; l_s[warp][ra] = l0;
@@ -378,7 +377,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmPara
         for (int w = 0; w < WARPS; ++w) {
             float wgt = m_s[w][r] == -INFINITY ? 0.f : exp2f((m_s[w][r] - M) * p.scale_log2);
             L += l_s[w][r] * wgt;
-            acc += merge_o[(size_t(w) * DM_ROWS + r) * HD + d] * wgt;
+            acc += merge_o[(size_t(w) * DM_ROWS + r) * MS + d] * wgt;
         }
         if (p.splits == 1) {
             p.out[size_t(t) * p.ldo + size_t(h0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
@@ -418,7 +417,8 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                  // [16][HD]
     __nv_bfloat16* ks = qs + DM_ROWS * HD;                                            // [warps][32][HD]
     __nv_bfloat16* vs = ks + PW_WARPS * SLOT_ELEMS;                                   // [warps][32][HD]
-    float* merge_o = reinterpret_cast<float*>(ks);                                    // reused after the loop: [warps][16][HD]
+    float* merge_o = reinterpret_cast<float*>(ks);                                    // reused after the loop: [warps][16][MS]
+    constexpr int MS = HD + 8;        // as in the other kernel
     __shared__ float m_s[PW_WARPS][DM_ROWS], l_s[PW_WARPS][DM_ROWS];
     __shared__ float cs_s[HALF], sn_s[HALF];
     __shared__ int last_flag;
@@ -470,17 +470,20 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
     // every warp's first half page is asked for at once
     int u = warp;
     if (u < u_end) load_half(u);
+    // the rotation's cosines and sines, one pair index per thread (the position is known before the kernel in
+    // front has finished)
+    if (p.rotate && tid < HALF) {
+        const int half = p.inv_freq ? p.rotary_dim / 2 : 0;
+        float sn = 0.f, cs = 1.f;
+        if (tid < half) sincosf(float(pos) * p.inv_freq[tid], &sn, &cs);
+        cs_s[tid] = cs;
+        sn_s[tid] = sn;
+    }
     if (early) gb_grid_wait();
 
-    // the rotation's cosines and sines, one pair index per thread, and the queries
+    // the queries
     if (p.rotate) {
         const int half = p.inv_freq ? p.rotary_dim / 2 : 0;
-        if (tid < HALF) {
-            float sn = 0.f, cs = 1.f;
-            if (tid < half) sincosf(float(pos) * p.inv_freq[tid], &sn, &cs);
-            cs_s[tid] = cs;
-            sn_s[tid] = sn;
-        }
         __syncthreads();
         for (int idx = tid; idx < DM_ROWS * HALF; idx += PW_THREADS) {
             const int r = idx / HALF, pi = idx - r * HALF;
@@ -611,13 +614,11 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     {
         const int ra = lane >> 2, rb = ra + 8, col = 2 * (lane & 3);
-        float* mo = merge_o + size_t(warp) * DM_ROWS * HD;
+        float* mo = merge_o + size_t(warp) * DM_ROWS * MS;
 #pragma unroll
         for (int i = 0; i < OT; ++i) {
-            mo[ra * HD + 8 * i + col] = o[i][0];
-            mo[ra * HD + 8 * i + col + 1] = o[i][1];
-            mo[rb * HD + 8 * i + col] = o[i][2];
-            mo[rb * HD + 8 * i + col + 1] = o[i][3];
+            if (ra < heads) *reinterpret_cast<float2*>(mo + ra * MS + 8 * i + col) = make_float2(o[i][0], o[i][1]);
+            if (rb < heads) *reinterpret_cast<float2*>(mo + rb * MS + 8 * i + col) = make_float2(o[i][2], o[i][3]);
         }
         if ((lane & 3) == 0) {
             m_s[warp][ra] = m0; l_s[warp][ra] = l0;
@@ -635,7 +636,7 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
         for (int w = 0; w < PW_WARPS; ++w) {
             float wgt = m_s[w][r] == -INFINITY ? 0.f : exp2f((m_s[w][r] - M) * p.scale_log2);
             L += l_s[w][r] * wgt;
-            acc += merge_o[(size_t(w) * DM_ROWS + r) * HD + d] * wgt;
+            acc += merge_o[(size_t(w) * DM_ROWS + r) * MS + d] * wgt;
         }
         if (p.splits == 1) {
             p.out[size_t(t) * p.ldo + size_t(h0 + r) * HD + d] = __float2bfloat16_rn(acc / L);
