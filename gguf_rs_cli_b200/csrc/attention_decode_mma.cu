@@ -401,13 +401,16 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmPara
 }
 
 // The same attention for steps with so few (token, KV head) pairs that the device is mostly idle and a CTA's
-// time is the latency of its pages one after the other: twelve warps, each taking half pages of 32 keys (warp w:
-// half pages w, w + 12, ...) into a slot of shared memory of its own, so that six pages are on their way at
-// once, twelve warps work on them and nobody waits for a block-wide barrier per page.  One CTA per SM (twelve
-// slots of 32 keys and values); a sequence's pages may be split over several CTAs as in the other kernel.
+// time is the latency of its pages one after the other: twelve warps, each taking quarter pages of 16 keys (warp
+// w: quarters w, w + 12, ...) into two slots of shared memory of its own in turn, so that six pages are on their
+// way at once, a warp's next quarter arrives while it works on this one, and nobody waits for a block-wide
+// barrier per page.  One CTA per SM (24 slots of 16 keys and values); a sequence's pages may be split over
+// several CTAs as in the other kernel.
 constexpr int PW_WARPS = 12;
 constexpr int PW_THREADS = PW_WARPS * 32;
-constexpr int PW_KEYS = 32;                 // keys per slot
+constexpr int PW_KEYS = 16;                 // keys per slot
+constexpr int PW_SLOTS = 2;                 // slots per warp
+constexpr int PW_UPP = GB_PAGE / PW_KEYS;   // slots' worth of keys per page
 
 template <int HD>
 __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmParams p) {
@@ -415,8 +418,8 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
     constexpr int PAGE_ELEMS = GB_PAGE * HD, SLOT_ELEMS = PW_KEYS * HD;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                  // [16][HD]
-    __nv_bfloat16* ks = qs + DM_ROWS * HD;                                            // [warps][32][HD]
-    __nv_bfloat16* vs = ks + PW_WARPS * SLOT_ELEMS;                                   // [warps][32][HD]
+    __nv_bfloat16* ks = qs + DM_ROWS * HD;                                            // [warps][slots][16][HD]
+    __nv_bfloat16* vs = ks + PW_WARPS * PW_SLOTS * SLOT_ELEMS;                        // [warps][slots][16][HD]
     float* merge_o = reinterpret_cast<float*>(ks);                                    // reused after the loop: [warps][16][MS]
     constexpr int MS = HD + 8;        // as in the other kernel
     __shared__ float m_s[PW_WARPS][DM_ROWS], l_s[PW_WARPS][DM_ROWS];
@@ -450,26 +453,30 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
     const int pg_end = first_page + int((long long)(split + 1) * n_pages / p.splits);
     const int* trow = p.table + size_t(b) * p.table_width;
     const bool own_kv = p.rotate && p.k_new != nullptr;
-    __nv_bfloat16* kt = ks + warp * SLOT_ELEMS;
-    __nv_bfloat16* vt = vs + warp * SLOT_ELEMS;
-    const int u_end = 2 * (pg_end - pg_begin);               // half pages, counted from this split's first page
+    // quarter pages u of the sequence (16 keys each), those of this split's pages that hold a key the token sees
+    const int u_first = max(pg_begin * PW_UPP, lo / PW_KEYS), u_end = min(pg_end * PW_UPP, pos / PW_KEYS + 1);
 
-    auto load_half = [&](int u) {
-        const int pg = pg_begin + (u >> 1), row0 = (u & 1) * PW_KEYS;
-        const int phys = trow[pg % p.ring_pages];
-        const size_t off = (size_t(phys) * p.nkv + g) * size_t(PAGE_ELEMS) + size_t(row0) * HD;
-        for (int i = lane; i < PW_KEYS * CH; i += 32) {
-            int r = i / CH, c = i - r * CH;
-            const int key = pg * GB_PAGE + row0 + r;       // rows beyond the sequence are read as zeros, and so
-            bool ok = key < pos || (key == pos && !own_kv);   // is the token's own row when this kernel makes it
-            dm_cp_async16(kt + dm_swz<HD>(r, c), p.kc + off + size_t(r) * HD + c * 8, ok);
-            dm_cp_async16(vt + dm_swz<HD>(r, c), p.vc + off + size_t(r) * HD + c * 8, ok);
+    auto load_quarter = [&](int u, int slot) {
+        if (u < u_end) {
+            const int pg = u / PW_UPP, row0 = (u % PW_UPP) * PW_KEYS;
+            const int phys = trow[pg % p.ring_pages];
+            const size_t off = (size_t(phys) * p.nkv + g) * size_t(PAGE_ELEMS) + size_t(row0) * HD;
+            __nv_bfloat16* kt = ks + (warp * PW_SLOTS + slot) * SLOT_ELEMS;
+            __nv_bfloat16* vt = vs + (warp * PW_SLOTS + slot) * SLOT_ELEMS;
+            for (int i = lane; i < PW_KEYS * CH; i += 32) {
+                int r = i / CH, c = i - r * CH;
+                const int key = u * PW_KEYS + r;               // rows beyond the sequence are read as zeros, and so
+                bool ok = key < pos || (key == pos && !own_kv);   // is the token's own row when this kernel makes it
+                dm_cp_async16(kt + dm_swz<HD>(r, c), p.kc + off + size_t(r) * HD + c * 8, ok);
+                dm_cp_async16(vt + dm_swz<HD>(r, c), p.vc + off + size_t(r) * HD + c * 8, ok);
+            }
         }
-        dm_commit();
+        dm_commit();                                       // one group per call, also an empty one: the waits count groups
     };
-    // every warp's first half page is asked for at once
-    int u = warp;
-    if (u < u_end) load_half(u);
+    // every warp's first two quarters are asked for at once
+    int u = u_first + warp;
+    load_quarter(u, 0);
+    load_quarter(u + PW_WARPS, 1);
     // the rotation's cosines and sines, one pair index per thread (the position is known before the kernel in
     // front has finished)
     if (p.rotate && tid < HALF) {
@@ -519,18 +526,21 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
     for (int k = 0; k < KS; ++k)
         dm_ldmatrix_x4(qf[k][0], qf[k][1], qf[k][2], qf[k][3], qs + dm_swz<HD>(lane & 15, 2 * k + (lane >> 4)));
 
-    for (; u < u_end; u += PW_WARPS) {
-        const int pg = pg_begin + (u >> 1), row0 = (u & 1) * PW_KEYS;
-        dm_wait<0>();
+    for (int it = 0; u < u_end; u += PW_WARPS, ++it) {
+        const int slot = it & 1;
+        __nv_bfloat16* kt = ks + (warp * PW_SLOTS + slot) * SLOT_ELEMS;
+        __nv_bfloat16* vt = vs + (warp * PW_SLOTS + slot) * SLOT_ELEMS;
+        dm_wait<PW_SLOTS - 1>();                            // all groups but the newest: this quarter is there
         __syncwarp();
-        if (own_kv && pg * GB_PAGE + row0 <= pos && pos < pg * GB_PAGE + row0 + PW_KEYS) {
-            // the token's own key (rotated) and value: into the half page in shared memory, and by the first
+        if (own_kv && u == pos / PW_KEYS) {
+            // the token's own key (rotated) and value: into the quarter page in shared memory, and by the first
             // head tile of the KV head into the cache
             const int r = pos & (PW_KEYS - 1);
             const int half = p.inv_freq ? p.rotary_dim / 2 : 0;
             const bool writes = (blockIdx.y % gtiles) == 0;
             const size_t src = size_t(t) * p.ldq + size_t(g) * HD;
-            const size_t dst = (size_t(trow[pg % p.ring_pages]) * p.nkv + g) * size_t(PAGE_ELEMS) + size_t(row0 + r) * HD;
+            const size_t dst = (size_t(trow[(pos >> GB_PAGE_SHIFT) % p.ring_pages]) * p.nkv + g) * size_t(PAGE_ELEMS) +
+                               size_t(pos & (GB_PAGE - 1)) * HD;
             for (int pi = lane; pi < HALF; pi += 32) {
                 const int d0 = pi < half ? (p.pairing ? 2 * pi : pi) : 2 * pi;
                 const int d1 = pi < half ? (p.pairing ? 2 * pi + 1 : pi + half) : 2 * pi + 1;
@@ -550,10 +560,9 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
             }
             __syncwarp();
         }
-        // the slot's 32 keys in two groups of 16, each as the other kernel treats a warp's 16 keys of a page
-#pragma unroll 1
-        for (int grp = 0; grp < PW_KEYS / 16; ++grp) {
-            const int key_base = grp * 16;
+        // the slot's 16 keys, as the other kernel treats a warp's 16 keys of a page
+        {
+            constexpr int key_base = 0;
             float s[2][4];
 #pragma unroll
             for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -564,7 +573,7 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
                 dm_mma(s[0], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b0, b1);
                 dm_mma(s[1], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b2, b3);
             }
-            const int key0 = pg * GB_PAGE + row0 + key_base + 2 * (lane & 3);
+            const int key0 = u * PW_KEYS + key_base + 2 * (lane & 3);
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
@@ -602,7 +611,7 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
             }
         }
         __syncwarp();                                        // the slot may be loaded again
-        if (u + PW_WARPS < u_end) load_half(u + PW_WARPS);
+        load_quarter(u + PW_SLOTS * PW_WARPS, slot);
     }
     dm_wait<0>();
     __syncthreads();
@@ -661,7 +670,7 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
 }
 
 template <int HD> int launch_pw(const DmParams& p, dim3 grid, cudaStream_t stream) {
-    constexpr int SMEM = (DM_ROWS + 2 * PW_WARPS * PW_KEYS) * HD * 2;
+    constexpr int SMEM = (DM_ROWS + 2 * PW_WARPS * PW_SLOTS * PW_KEYS) * HD * 2;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_decode_pages_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
