@@ -189,7 +189,6 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmPara
         if (u_begin + s < u_end) load_unit(u_begin + s, s);
         dm_commit();
     }
-    if (early) gb_grid_wait();
     // this thread's pairs of every row: pair pi is (pi, pi + half) or (2 pi, 2 pi + 1) inside the rotation,
     // unchanged beyond it; a CTA of fewer threads than pairs gives each thread PPT of them
     constexpr int PPT = HALF > THREADS ? HALF / THREADS : 1;
@@ -210,6 +209,9 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmPara
             d1[e] = pi < half ? (p.pairing ? 2 * pi + 1 : pi + half) : 2 * pi + 1;
             if (pi < half) sincosf(float(pos) * freq, &sn[e], &cs[e]);
         }
+    }
+    if (early) gb_grid_wait();                               // the sines and cosines need only the position
+    if (p.rotate) {
         constexpr int RSTEP = THREADS / LANES;                   // rows a pass of all threads covers
         constexpr int RPT = DM_ROWS / RSTEP;                     // rows per thread
 #pragma unroll
