@@ -412,7 +412,7 @@ def test_sampling_ring_and_padding():
 
 
 # ----------------------------------------------------------- decode attention
-class two_warps:
+class TwoWarpShape:
     """mma == "two": the tensor-core decode kernel in its shape of two warps and half pages (heads of 128), which
     the library takes by itself only for steps of several hundred CTAs."""
 
@@ -438,7 +438,7 @@ class two_warps:
 def test_attention_decode(nh, nkv, hd, splits, mma):
     if mma and hd not in (64, 128):
         pytest.skip("the tensor-core decode kernel takes head sizes 64 and 128")
-    with two_warps(mma, hd):
+    with TwoWarpShape(mma, hd):
         _attention_decode(nh, nkv, hd, splits, bool(mma))
 
 
@@ -470,7 +470,7 @@ def _attention_decode(nh, nkv, hd, splits, mma):
 @pytest.mark.parametrize("window", [1, 31, 64, 65, 100, 300])
 @pytest.mark.parametrize("mma,hd", [(False, 64), (True, 64), (True, 128), ("two", 128)])
 def test_attention_decode_far_key_and_window(window, mma, hd):
-    with two_warps(mma, hd):
+    with TwoWarpShape(mma, hd):
         _far_key_and_window(window, bool(mma), hd)
 
 
@@ -514,7 +514,7 @@ def test_attention_decode_few_long_sequences_in_many_splits(splits, hd):
 @pytest.mark.parametrize("own_kv", [True, False])
 @pytest.mark.parametrize("mma", [True, "two"])
 def test_attention_decode_rotating(nh, nkv, hd, pairing, rot, own_kv, mma):
-    with two_warps(mma, hd):
+    with TwoWarpShape(mma, hd):
         _attention_decode_rotating(nh, nkv, hd, pairing, rot, own_kv)
 
 
