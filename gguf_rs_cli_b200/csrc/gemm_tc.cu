@@ -79,10 +79,17 @@ __device__ __forceinline__ void sum_partials(const float* base, int first_which,
     }
 }
 
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x, TcParams p) {
     using Cfg = TileCfg<BN>;
+    constexpr bool SLICES = BN >= 32;        // every CTA of a shared tile finishes a share of its tokens (else the last one all)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full_bar[Cfg::STAGES], empty_bar[Cfg::STAGES], acc_full[2], acc_empty[2];
@@ -221,6 +228,8 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
             tc_fence_after();
             const uint32_t taddr = tmem_d + (uint32_t(quarter * 32) << 16) + buf * BN;
             bool finish = true;                          // does this CTA write the tile's result?
+            bool sliced = false;                         // ... or a share of it, as every CTA of the tile does
+            int c_lo = 0, c_hi = cols;                   // the tokens of the tile that it finishes
             if (!whole) {
                 // this CTA's share of the tile: the partial sums go to scratch memory
                 // (a partial tile lies token by token, each token's 128 features side by side: a warp's stores and loads
@@ -243,12 +252,42 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
                 // written before every thread has read it.
                 __threadfence();
                 epilogue_sync();
-                if (threadIdx.x == 64) last_flag = atomicAdd(&p.counters[w.tile], 1) == n_ctas - 1;
-                epilogue_sync();
-                finish = last_flag != 0;
+                if (SLICES && p.cut == CUT_PER_TILE) {
+                    // Wide tiles: every CTA of the tile stays until all have counted themselves (a bounded wait) and
+                    // finishes its own share of the tile's tokens, where the last CTA alone would spend 3 to 4 us on
+                    // every 16 of them.  All CTAs of the kernel are resident when any of them waits (cut_for gives it
+                    // no more CTAs than fit the device; the kernel behind starts only when all of this one have).
+                    if (threadIdx.x == 64) {
+                        atomicAdd(&p.counters[w.tile], 1);
+                        int seen = 0;
+                        uint64_t start = 0;
+                        for (uint32_t i = 0; (seen = ld_acquire_gpu(&p.counters[w.tile])) < n_ctas; ++i) {
+                            __nanosleep(40);
+                            if ((i & 255) == 255) {          // gives up after about two seconds
+                                const uint64_t now = global_timer_ns();
+                                if (start == 0) start = now;
+                                else if (now - start > WAIT_NS) break;
+                            }
+                        }
+                        last_flag = seen >= n_ctas;
+                    }
+                    epilogue_sync();
+                    if (!last_flag) {                      // uniform: the flag is shared
+                        if (threadIdx.x == 64) atomicExch(p.status, 5);
+                        break;
+                    }
+                    c_lo = me * cols / n_ctas;
+                    c_hi = (me + 1) * cols / n_ctas;
+                    finish = c_lo < c_hi;
+                    sliced = true;
+                } else {
+                    if (threadIdx.x == 64) last_flag = atomicAdd(&p.counters[w.tile], 1) == n_ctas - 1;
+                    epilogue_sync();
+                    finish = last_flag != 0;
+                }
             }
             if (finish) {
-                for (int c0 = 0; c0 < cols; c0 += 16) {
+                for (int c0 = c_lo & ~15; c0 < c_hi; c0 += 16) {
                     float v[16], xv[16];
                     bool have_x = false;
                     if (whole) {
@@ -261,22 +300,28 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
                         if (BN >= 64 && p.resid_x) {
 #pragma unroll
                             for (int jj = 0; jj < 16; ++jj)
-                                xv[jj] = (n < p.N && c0 + jj < cols) ? __ldcg(p.resid_x + size_t(w.t0 + c0 + jj) * p.ld_x + n) : 0.f;
+                                xv[jj] = (n < p.N && c0 + jj >= c_lo && c0 + jj < c_hi)
+                                             ? __ldcg(p.resid_x + size_t(w.t0 + c0 + jj) * p.ld_x + n) : 0.f;
                             have_x = true;
                         }
                         const float* base = p.scratch + size_t(first_cta) * 2 * (BN * BM) + row;
-                        if (n_ctas <= 4) sum_partials<BN, 4, 16>(base, first_which, n_ctas, c0, cols, v);
-                        else sum_partials<BN, 8, 8>(base, first_which, n_ctas, c0, cols, v);
+                        if (n_ctas <= 4) sum_partials<BN, 4, 16>(base, first_which, n_ctas, c0, c_hi, v);
+                        else sum_partials<BN, 8, 8>(base, first_which, n_ctas, c0, c_hi, v);
                     }
                     if constexpr (BN == 16)
-                        tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, true, c0, cols, v, rstd_s, ssq_s,
-                                            p.resid_x ? x_early : nullptr);
+                        tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, true, c0, c_hi, v, rstd_s, ssq_s,
+                                            p.resid_x ? x_early : nullptr, c_lo);
                     else
-                        tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, true, c0, cols, v, rstd_s, ssq_s,
-                                            have_x ? xv : nullptr);
+                        tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, true, c0, c_hi, v, rstd_s, ssq_s,
+                                            have_x ? xv : nullptr, c_lo);
                 }
-                if (p.resid_x) tc_write_ssq<BN>(p, w.n0, w.t0, row, 0, cols, ssq_s);
-                if (!whole && threadIdx.x == 64) p.counters[w.tile] = 0;       // ready for the next launch
+                if (p.resid_x) tc_write_ssq<BN>(p, w.n0, w.t0, row, c_lo, c_hi, ssq_s);
+                if (!whole && !sliced && threadIdx.x == 64) p.counters[w.tile] = 0;       // ready for the next launch
+            }
+            if (sliced) {
+                // the last of the tile's CTAs to have read the others' sums puts the counter back for the next launch
+                epilogue_sync();
+                if (threadIdx.x == 64 && atomicAdd(&p.counters[w.tile], 1) == 2 * n_ctas - 1) p.counters[w.tile] = 0;
             }
             if (whole) {
                 tc_fence_before();
@@ -408,6 +453,10 @@ static int tile_for(int T, int N, int sms) {
     // a few hundred tokens: tiles of 64 tokens, two CTAs per SM, as long as all of them fit the device at once
     // (a CTA with a wide tile streams its operands no faster; measured at 128 to 768 tokens)
     if (bn >= 128 && (T <= 128 || ft * ((T + 63) / 64) <= 2LL * sms)) bn = 64;
+    // 65 to 96 tokens and fewer feature tiles than SMs: three tiles of 32 tokens instead of a full and a half-empty
+    // one of 64 (a 96-token step 5.26 instead of 5.60 ms; from 97 tokens on four tiles of 32 lose: 128 tokens 6.07
+    // instead of 5.59 ms)
+    if (bn == 64 && ft < sms && T > 64 && T <= 96) bn = 32;
     return bn;
 }
 

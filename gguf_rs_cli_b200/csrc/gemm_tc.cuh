@@ -203,13 +203,15 @@ __device__ __forceinline__ float tc_warp_sum16(const float (&v)[16], int lane) {
     return d;
 }
 
-// The last steps for 16 columns (tokens c0 .. c0+15 of the tile, those below c_end being valid) of this
-// thread's feature row n = n0 + row: v[jj] holds the finished sum of column c0 + jj.  x_early: the 16 values of
-// the residual stream at these places if the caller has read them already, else null.
+// The last steps for 16 columns (tokens c0 .. c0+15 of the tile, those from c_lo on and below c_end being the
+// caller's to finish) of this thread's feature row n = n0 + row: v[jj] holds the finished sum of column c0 + jj.
+// x_early: the 16 values of the residual stream at these places if the caller has read them already, else null.
 template <int BN>
 __device__ __forceinline__ void tc_finish_chunk(const TcParams& p, int n0, int t0, int n, int row, int lane, int quarter,
                                                 float bias, bool waited, int c0, int c_end, float (&v)[16],
-                                                const float* rstd_s, float (*ssq_s)[BN], const float* x_early = nullptr) {
+                                                const float* rstd_s, float (*ssq_s)[BN], const float* x_early = nullptr,
+                                                int c_lo = 0) {
+    auto mine = [&](int c) { return c >= c_lo && c < c_end; };
     if (p.row_ssq) {
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj) v[jj] *= rstd_s[min(c0 + jj, BN - 1)];
@@ -221,11 +223,11 @@ __device__ __forceinline__ void tc_finish_chunk(const TcParams& p, int n0, int t
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj)
             xv[jj] = x_early ? x_early[jj]
-                             : (n < p.N && c0 + jj < c_end) ? __ldcg(p.resid_x + size_t(t0 + c0 + jj) * p.ld_x + n) : 0.f;
+                             : (n < p.N && mine(c0 + jj)) ? __ldcg(p.resid_x + size_t(t0 + c0 + jj) * p.ld_x + n) : 0.f;
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj) {
             float sq = 0.f;
-            if (n < p.N && c0 + jj < c_end) {
+            if (n < p.N && mine(c0 + jj)) {
                 const size_t at = size_t(t0 + c0 + jj) * p.ld_x + n;
                 const float xn = xv[jj] + v[jj] + bias;
                 p.resid_x[at] = xn;
@@ -236,12 +238,12 @@ __device__ __forceinline__ void tc_finish_chunk(const TcParams& p, int n0, int t
         }
         const float sq = tc_warp_sum16(v, lane);
         const int jj = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
-        if ((lane & 1) == 0 && c0 + jj < c_end) ssq_s[quarter][c0 + jj] = sq;
+        if ((lane & 1) == 0 && mine(c0 + jj)) ssq_s[quarter][c0 + jj] = sq;
     } else if (!p.swiglu) {
         if (n < p.N && waited) {
 #pragma unroll
             for (int jj = 0; jj < 16; ++jj)
-                if (c0 + jj < c_end)
+                if (mine(c0 + jj))
                     gb_store(p.out, p.out_dtype, size_t(t0 + c0 + jj) * p.ldo + n, v[jj] + bias);
         }
     } else {
@@ -258,7 +260,7 @@ __device__ __forceinline__ void tc_finish_chunk(const TcParams& p, int n0, int t
             for (int jj = 0; jj < 8; ++jj) {
                 const float gte = odd ? other[jj] : v[jj], up = odd ? v[8 + jj] : other[jj];
                 const int c = c0 + (odd ? 8 : 0) + jj;
-                if (c < c_end)
+                if (mine(c))
                     gb_store(p.out, p.out_dtype, size_t(t0 + c) * p.ldo + f, gte / (1.f + expf(-gte)) * up);
             }
         }

@@ -357,7 +357,8 @@ def check_tc_status() -> None:
     if code:
         lib.gb_tc_status_clear()
         raise native.NativeError(f"a tensor-core product gave up waiting (code {code}: 1 a stage never came free, "
-                                 f"2 a load never arrived, 3/4 an accumulator never completed); its output is invalid")
+                                 f"2 a load never arrived, 3/4 an accumulator never completed, 5 a CTA that shares a tile never arrived); "
+                                 f"its output is invalid")
     code = lib.gb_attention_tc_status()
     if code:
         lib.gb_attention_tc_status_clear()

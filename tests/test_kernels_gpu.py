@@ -762,11 +762,13 @@ def test_gemm_tensor_core_deferred_norm_and_residual(T, N, Kd):
 
 @pytest.mark.parametrize("T,N,Kd,tile", [(5, 384, 4096, 16), (16, 4096, 4096, 16), (40, 1000, 2048, 32), (64, 520, 1024, 64),
                                          (64, 4096, 4096, 64), (130, 300, 4096, 128), (300, 260, 2048, 256), (700, 264, 640, 64)])
-@pytest.mark.parametrize("mode", [2, 3])
+@pytest.mark.parametrize("mode", [0, 2, 3])
 def test_gemm_tensor_core_tiles_shared_between_ctas(T, N, Kd, tile, mode):
     """Tiles shared by CTAs in every way, at every tile width.  Mode 3: every CTA takes an equal share of all K
     blocks (a share that ends inside a tile, one that lies inside a tile, whole tiles between two partial ones);
-    mode 2: where the sizes allow it, every tile has CTAs of its own instead.  Plain,
+    mode 2: where the sizes allow it, every tile has CTAs of its own instead (mode 0, the rule: only then are tiles
+    shared).  With CTAs of its own, a tile of 32 tokens or more is finished by all of them, each a share of its
+    tokens, after a bounded wait for one another; otherwise by the CTA that arrives last.  Plain,
     gated and residual epilogues against 64-bit products, twice in a row to the bit (the counters are left at
     zero), and the same values as with whole tiles only up to the order of the 32-bit sums."""
     from gguf_rs_cli_b200 import native
