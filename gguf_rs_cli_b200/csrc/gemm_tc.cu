@@ -446,17 +446,13 @@ static int tile_for(int T, int N, int sms) {
     int bn = gb_gemm_tc_tile(T);
     const long long ft = (N + BM - 1) / BM;
     if (bn == 256 && 2 * ft * ((T + 255) / 256) <= sms) bn = 128;
-    // a few dozen tokens and fewer feature tiles than SMs: two half-size token tiles give twice the tiles
-    // without more CTAs on each (the second read of W hits L2; the last CTA of a tile reads all its partial
-    // tiles, and those grow with the tile's width: batch 64 of the 8B shape 5.36 instead of 5.9 ms a step)
-    if (bn > 16 && bn <= 64 && ft < sms) bn /= 2;
+    // (A few dozen tokens used to take two half-size token tiles where there are fewer feature tiles than SMs,
+    // because the one CTA that finished a shared tile read all its partial tiles.  Since every CTA of a tile of
+    // 32 tokens or more finishes a share of it, whole-width tiles are faster: batch 24 to 64 of the 8B shape
+    // 3.87 / 3.94 / 4.60 / 4.71 instead of 4.07 / 4.10 / 4.79 / 4.84 ms a step.)
     // a few hundred tokens: tiles of 64 tokens, two CTAs per SM, as long as all of them fit the device at once
     // (a CTA with a wide tile streams its operands no faster; measured at 128 to 768 tokens)
     if (bn >= 128 && (T <= 128 || ft * ((T + 63) / 64) <= 2LL * sms)) bn = 64;
-    // 65 to 96 tokens and fewer feature tiles than SMs: three tiles of 32 tokens instead of a full and a half-empty
-    // one of 64 (a 96-token step 5.26 instead of 5.60 ms; from 97 tokens on four tiles of 32 lose: 128 tokens 6.07
-    // instead of 5.59 ms)
-    if (bn == 64 && ft < sms && T > 64 && T <= 96) bn = 32;
     return bn;
 }
 
