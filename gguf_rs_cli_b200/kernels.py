@@ -356,6 +356,8 @@ def check_tc_status() -> None:
     code = tc_status()
     if code:
         lib.gb_tc_status_clear()
+        for sc in _tc_scratch.values():              # a kernel that gave up may have left a tile's counter half counted
+            sc.counters.zero_()
         raise native.NativeError(f"a tensor-core product gave up waiting (code {code}: 1 a stage never came free, "
                                  f"2 a load never arrived, 3/4 an accumulator never completed, 5 a CTA that shares a tile never arrived); "
                                  f"its output is invalid")
