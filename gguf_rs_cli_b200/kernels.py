@@ -235,21 +235,29 @@ def decode_split_class(max_kv: int) -> int:
 
 
 def decode_splits(T: int, n_heads: int, n_kv_heads: int, max_kv: int, sms: int, mma: bool) -> int:
-    """Splits of each sequence's pages for a decode step.  The rule for many CTAs: 8 pages or more per split
-    (merging the splits costs more than it saves below that) and no more CTAs than fit the device at once
-    with two per SM (a second round costs more than the splits save).  Where even four pages per split leave
-    no more CTAs than SMs (long sequences, very few of them), the tensor-core kernel runs one CTA per SM whose
-    twelve warps take half pages each, and finer splits pay: from 16 pages on, 4 pages per split."""
+    """Splits of each sequence's pages for a decode step; a function of the step's class (decode_split_class)
+    and its CTAs, so that all steps of a captured graph split alike.
+
+    The tensor-core kernels split only while the step keeps to one CTA per SM, where the kernel of twelve warps
+    runs (measured against the kernels of many CTAs with more splits at 8 to 16 sequences of 1,000 to 8,000
+    positions: 17.5 instead of 21.1 us, 26.9 instead of 31.1, 14.8 instead of 20.5).  Few CTAs (a quarter of the
+    SMs or fewer) are bound by what one SM can read and spread out: splits of at least 4 pages, at most 8 of them.
+    More CTAs pay more for merging than they gain below about 12 pages per split.  Sequences of less than 16 pages
+    are never split.  The CUDA-core kernel splits into 8 pages or more per split while all CTAs fit the device at
+    once with two per SM."""
     group = n_heads // n_kv_heads
     tile = 16 if mma else (8 if group >= 8 else 4 if group > 2 else group)
     ctas = T * n_kv_heads * ((group + tile - 1) // tile)
     pages = (max_kv + 63) // 64
-    coarse = max(1, min(_split_class(pages // 8), 32, (2 * sms) // ctas))
-    if mma and pages >= 16:
-        fine = _split_class(min(pages // 4, sms // ctas))
-        if fine >= coarse:
-            return fine
-    return coarse
+    if not mma:
+        return max(1, min(_split_class(pages // 8), 32, (2 * sms) // ctas))
+    cls = decode_split_class(max_kv)                       # a quarter of the pages, rounded down to a class
+    if ctas > sms or cls < 4:
+        return 1
+    room = sms // ctas
+    if 4 * ctas <= sms:
+        return _split_class(min(room, 8, cls))
+    return _split_class(min(room, cls // 3))
 
 
 def attention_decode_mma_supported(q: torch.Tensor, kcache: torch.Tensor, head_dim: int) -> bool:

@@ -252,3 +252,6 @@ def test_decode_split_rule_is_fixed_within_a_graph_class():
                 ctas = T * kv * ((group + 15) // 16)
                 assert 1 <= s <= max(1, pages) and (s == 1 or s * ctas <= 2 * sms)
     assert kernels.decode_splits(1, 32, 8, 2048, sms, True) == 8 and kernels.decode_splits(8, 32, 8, 520, sms, True) == 1
+    # eight sequences split in two from about 1,500 positions on, sixteen never: one CTA per SM is kept
+    assert [kernels.decode_splits(8, 32, 8, n, sms, True) for n in (1024, 1600, 2048, 8000)] == [1, 2, 2, 2]
+    assert kernels.decode_splits(16, 32, 8, 4096, sms, True) == 1 and kernels.decode_splits(4, 32, 8, 4096, sms, True) == 4
