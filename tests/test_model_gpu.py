@@ -218,11 +218,14 @@ def test_step_errors_launch_nothing():
     eng.cache.check()
 
 
-def test_bfloat16_path_against_the_32_bit_path_at_the_benchmark_layer_sizes():
+@pytest.mark.parametrize("lens", [(700, 300, 64), tuple(20 + 2 * i for i in range(40))], ids=["3 long", "40 short"])
+def test_bfloat16_path_against_the_32_bit_path_at_the_benchmark_layer_sizes(lens):
     """Two layers of the Llama-3.1-8B layer shape (head size 128, 32 heads in 8 groups, widths 4096 / 14336;
     a smaller vocabulary) with random weights: prompts of unequal lengths in one step (the tensor-core
     attention and the two-SM product run here, which the tiny models do not reach), then single tokens; the
-    bfloat16 logits against the true 32-bit path's."""
+    bfloat16 logits against the true 32-bit path's.  With 40 sequences the decode steps take what a large batch
+    takes: tiles of 64 tokens that several CTAs share and finish a share each, and the attention kernel's CTAs of
+    two warps."""
     from gguf_rs_cli_b200.api import from_random
     from gguf_rs_cli_b200.engine.step import Engine, Entry
     cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 2, "hidden_size": 4096,
@@ -232,11 +235,11 @@ def test_bfloat16_path_against_the_32_bit_path_at_the_benchmark_layer_sizes():
                             "original_max_position_embeddings": 8192},
            "rms_norm_eps": 1e-5, "max_position_embeddings": 2048, "tie_word_embeddings": False, "hidden_act": "silu"}
     g = torch.Generator().manual_seed(1)
-    toks = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in (700, 300, 64)]
+    toks = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
     res = {}
     for dtype in ("float32", "bfloat16"):
         model = from_random(cfg, seed=0, dtype=dtype, device="cuda:0").model
-        eng = Engine(model, n_tokens=64 * 24, n_slots=4, max_len=2048)
+        eng = Engine(model, n_tokens=64 * max(24, 2 * len(lens)), n_slots=len(lens) + 1, max_len=2048)
         slots = [eng.open() for _ in toks]
         out = [eng.step([Entry(s, t[:-8], [len(t) - 9, 0, len(t) // 2]) for s, t in zip(slots, toks)])]
         for i in range(8, 0, -1):
