@@ -13,8 +13,21 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "stamps.cuh"
 
 namespace {
+
+// Time stamps (builds with -DGB_STAMPS), 16 slots a CTA: 0 entry, 1 the first pages are asked for, 2 the wait for the
+// kernel in front is over, 3 the queries are in shared memory, 4 this CTA's first warp has done its pages, 5 all
+// warps have, 6 the output (or the split's record) is written.
+#ifdef GB_STAMPS
+__device__ long long* g_stamps = nullptr;
+#define STAMP_IF(cond, k) if (cond) GB_STAMP_WRITE(g_stamps, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, k)
+#define STAMP_AFTER_IF(cond, k, val) if (cond) GB_STAMP_WRITE_AFTER(g_stamps, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, k, val)
+#else
+#define STAMP_IF(cond, k)
+#define STAMP_AFTER_IF(cond, k, val)
+#endif
 
 constexpr int DM_ROWS = 16;           // query heads per tile
 constexpr int DM_STAGES = 3;
@@ -131,6 +144,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmPara
     // the cache it reads was written in an earlier step: then the first pages are asked for before waiting for
     // that kernel.  Otherwise the rotation kernel in front wrote the token's row, or (a cache shared with another
     // run) a kernel further back did: wait first.
+    STAMP_IF(threadIdx.x == 0, 0);
     gb_grid_launch_dependents();
     const bool early = p.rotate && p.k_new != nullptr;
     if (!early) gb_grid_wait();
@@ -210,7 +224,9 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmPara
             if (pi < half) sincosf(float(pos) * freq, &sn[e], &cs[e]);
         }
     }
+    STAMP_IF(threadIdx.x == 0, 1);
     if (early) gb_grid_wait();                               // the sines and cosines need only the position
+    STAMP_IF(threadIdx.x == 0, 2);
     if (p.rotate) {
         constexpr int RSTEP = THREADS / LANES;                   // rows a pass of all threads covers
         constexpr int RPT = DM_ROWS / RSTEP;                     // rows per thread
@@ -289,6 +305,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmPara
             }
             __syncthreads();
         }
+        STAMP_IF(it == 0 && threadIdx.x == 0, 3);
         if (it == 0) {
 #pragma unroll
             for (int k = 0; k < KS; ++k)
@@ -347,8 +364,10 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmPara
         }
         __syncthreads();                                    // the stage may be loaded again
     }
+    STAMP_AFTER_IF(threadIdx.x == 0, 4, o[0][0]);
     dm_wait<0>();
     __syncthreads();
+    STAMP_IF(threadIdx.x == 0, 5);
 
     // ---- merge the warps (each saw its share of the keys) in warp order
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -389,6 +408,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_mma_kernel(DmPara
             if (d == 0) { rec[HD] = M == -INFINITY ? -INFINITY : M * p.scale_log2; rec[HD + 1] = L; }
         }
     }
+    STAMP_IF(threadIdx.x == 0, 6);
     if (p.splits == 1) return;
     __threadfence();
     __syncthreads();
@@ -428,6 +448,7 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
     __shared__ float cs_s[HALF], sn_s[HALF];
     __shared__ int last_flag;
 
+    STAMP_IF(threadIdx.x == 0, 0);
     gb_grid_launch_dependents();
     const bool early = p.rotate && p.k_new != nullptr;       // see the other kernel: pages before the wait
     if (!early) gb_grid_wait();
@@ -488,7 +509,9 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
         cs_s[tid] = cs;
         sn_s[tid] = sn;
     }
+    STAMP_IF(threadIdx.x == 0, 1);
     if (early) gb_grid_wait();
+    STAMP_IF(threadIdx.x == 0, 2);
 
     // the queries
     if (p.rotate) {
@@ -518,6 +541,7 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
         dm_wait<0>();
     }
     __syncthreads();                                         // the queries are in place
+    STAMP_IF(threadIdx.x == 0, 3);
 
     float o[OT][4];
 #pragma unroll
@@ -615,8 +639,10 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
         __syncwarp();                                        // the slot may be loaded again
         load_quarter(u + PW_SLOTS * PW_WARPS, slot);
     }
+    STAMP_AFTER_IF(threadIdx.x == 0, 4, o[0][0]);
     dm_wait<0>();
     __syncthreads();
+    STAMP_IF(threadIdx.x == 0, 5);
 
     // ---- merge the warps (each saw some of the pages) in warp order
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -657,6 +683,7 @@ __global__ void __launch_bounds__(PW_THREADS) attention_decode_pages_kernel(DmPa
             if (d == 0) { rec[HD] = M == -INFINITY ? -INFINITY : M * p.scale_log2; rec[HD + 1] = L; }
         }
     }
+    STAMP_IF(threadIdx.x == 0, 6);
     if (p.splits == 1) return;
     // ---- the splits of a (token, head tile) are merged by the CTA that finishes last, in split order
     __threadfence();
@@ -698,6 +725,18 @@ template <int HD, int WARPS> int launch_dm(const DmParams& p, dim3 grid, cudaStr
 }
 
 }  // namespace
+
+// Builds with -DGB_STAMPS: the CTAs of every decode attention kernel write their time stamps to buf (16 64-bit slots
+// a CTA, CTAs in the order of the grid; null: none do).
+GB_API int gb_attention_decode_set_stamps(long long* buf) {
+#ifdef GB_STAMPS
+    if (cudaMemcpyToSymbol(g_stamps, &buf, sizeof(buf)) != cudaSuccess) return gb_fail("gb_attention_decode_set_stamps: cannot set the buffer");
+    return 0;
+#else
+    (void)buf;
+    return gb_fail("gb_attention_decode_set_stamps: this library was built without -DGB_STAMPS");
+#endif
+}
 
 static int g_pages_kernel = 1;        // 0: never the kernel whose warps take whole pages (tuning aid)
 GB_API int gb_attention_decode_set_pages_kernel(int on) { g_pages_kernel = on; return 0; }

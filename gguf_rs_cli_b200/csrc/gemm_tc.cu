@@ -30,6 +30,7 @@
 #include <unordered_map>
 
 #include "gemm_tc.cuh"
+#include "stamps.cuh"
 
 using namespace sm100;
 
@@ -79,6 +80,20 @@ __device__ __forceinline__ void sum_partials(const float* base, int first_which,
     }
 }
 
+// Time stamps (builds with -DGB_STAMPS): slots of a CTA of the one product whose N and K were asked for.
+// 0 entry, 1 the wait for the kernel in front is over, 2 the first operands are there, 3 the last MMA is committed,
+// 4 the accumulator is seen complete, 5 partial sums stored and fenced, 6 counted (and the tile's other CTAs seen),
+// 7 the sharers' sums of the first 16 tokens are there, 8 the tile (or this CTA's share) is finished, 9 exit.
+#ifdef GB_STAMPS
+__device__ long long* g_stamps = nullptr;
+__device__ int g_stamps_n = 0, g_stamps_k = 0;
+#define STAMP_IF(cond, k) if (cond) GB_STAMP_WRITE((p.N == g_stamps_n && p.K == g_stamps_k) ? g_stamps : nullptr, blockIdx.x, k)
+#define STAMP_AFTER_IF(cond, k, val) if (cond) GB_STAMP_WRITE_AFTER((p.N == g_stamps_n && p.K == g_stamps_k) ? g_stamps : nullptr, blockIdx.x, k, val)
+#else
+#define STAMP_IF(cond, k)
+#define STAMP_AFTER_IF(cond, k, val)
+#endif
+
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
     int v;
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -100,6 +115,7 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
     __shared__ float ssq_s[4][BN];          // per epilogue warp and token: sum of squares of the new residual
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    STAMP_IF(threadIdx.x == 0, 0);
     const int kb_total = (p.K + BK - 1) / BK;
     const int token_tiles = (p.T + BN - 1) / BN;
     const int g_begin = cta_begin(blockIdx.x, p, kb_total), g_end = cta_begin(blockIdx.x + 1, p, kb_total);   // this CTA's share
@@ -172,6 +188,7 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
                 const uint32_t acc = tmem_d + buf * BN;
                 for (int kb = w.kb_begin; kb < w.kb_end; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase)) { atomicExch(p.status, 2); ok = false; break; }
+                    STAMP_IF(j == 0 && kb == w.kb_begin, 2);
                     tc_fence_after();
                     uint32_t a = smem_u32(ring + stage * Cfg::STAGE_BYTES);
                     uint32_t b = a + A_BYTES;
@@ -183,6 +200,7 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
                 }
                 mma_commit(&acc_full[buf]);             // this unit's accumulator is complete
+                STAMP_IF(true, 3);
             }
         }
     } else {
@@ -193,6 +211,7 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
         const int row = quarter * 32 + lane;        // feature within the tile = TMEM lane
         int j = 0;
         gb_grid_wait();                             // before anything is read or written that the kernel before touches
+        STAMP_IF(threadIdx.x == 64, 1);
         UnitWalk walk(p, g_begin, g_end);
         Unit w;
         for (; walk.next(w, p, BN, token_tiles, kb_total); ++j) {
@@ -226,6 +245,7 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
                 break;
             }
             tc_fence_after();
+            STAMP_IF(threadIdx.x == 64, 4);
             const uint32_t taddr = tmem_d + (uint32_t(quarter * 32) << 16) + buf * BN;
             bool finish = true;                          // does this CTA write the tile's result?
             bool sliced = false;                         // ... or a share of it, as every CTA of the tile does
@@ -252,6 +272,7 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
                 // written before every thread has read it.
                 __threadfence();
                 epilogue_sync();
+                STAMP_IF(threadIdx.x == 64, 5);
                 if (SLICES && p.cut == CUT_PER_TILE) {
                     // Wide tiles: every CTA of the tile stays until all have counted themselves (a bounded wait) and
                     // finishes its own share of the tile's tokens, where the last CTA alone would spend 3 to 4 us on
@@ -276,6 +297,7 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
                         if (threadIdx.x == 64) atomicExch(p.status, 5);
                         break;
                     }
+                    STAMP_IF(threadIdx.x == 64, 6);
                     c_lo = me * cols / n_ctas;
                     c_hi = (me + 1) * cols / n_ctas;
                     finish = c_lo < c_hi;
@@ -283,6 +305,7 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
                 } else {
                     if (threadIdx.x == 64) last_flag = atomicAdd(&p.counters[w.tile], 1) == n_ctas - 1;
                     epilogue_sync();
+                    STAMP_IF(threadIdx.x == 64, 6);
                     finish = last_flag != 0;
                 }
             }
@@ -307,6 +330,7 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
                         const float* base = p.scratch + size_t(first_cta) * 2 * (BN * BM) + row;
                         if (n_ctas <= 4) sum_partials<BN, 4, 16>(base, first_which, n_ctas, c0, c_hi, v);
                         else sum_partials<BN, 8, 8>(base, first_which, n_ctas, c0, c_hi, v);
+                        STAMP_AFTER_IF(threadIdx.x == 64 && c0 == (c_lo & ~15), 7, v[0] + v[7]);
                     }
                     if constexpr (BN == 16)
                         tc_finish_chunk<BN>(p, w.n0, w.t0, n, row, lane, quarter, bias, true, c0, c_hi, v, rstd_s, ssq_s,
@@ -316,6 +340,7 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
                                             have_x ? xv : nullptr, c_lo);
                 }
                 if (p.resid_x) tc_write_ssq<BN>(p, w.n0, w.t0, row, c_lo, c_hi, ssq_s);
+                STAMP_IF(threadIdx.x == 64, 8);
                 if (!whole && !sliced && threadIdx.x == 64) p.counters[w.tile] = 0;       // ready for the next launch
             }
             if (sliced) {
@@ -331,6 +356,7 @@ __global__ void __launch_bounds__(TC_THREADS, ctas_per_sm(BN)) gemm_tc_kernel(co
     }
     tc_fence_before();
     __syncthreads();
+    STAMP_IF(threadIdx.x == 0, 9);
     if (warp == 1) tmem_dealloc(tmem_d, Cfg::TMEM_COLS);
 }
 
@@ -608,6 +634,19 @@ static int gemm_tc_impl(const void* X, long long ldx, const void* W, long long l
 // Non-zero when a bounded wait inside a tensor-core kernel gave up since the last clear
 // (1: a load stage never came free, 2: a load never arrived, 3/4: an accumulator never completed or never came free).
 // Read after synchronising the stream.
+// Builds with -DGB_STAMPS: the CTAs of every product of N features over K write their time stamps to buf
+// (16 64-bit slots a CTA; null: none do).
+GB_API int gb_gemm_tc_set_stamps(long long* buf, int n, int k) {
+#ifdef GB_STAMPS
+    if (cudaMemcpyToSymbol(g_stamps_n, &n, sizeof(n)) != cudaSuccess || cudaMemcpyToSymbol(g_stamps_k, &k, sizeof(k)) != cudaSuccess ||
+        cudaMemcpyToSymbol(g_stamps, &buf, sizeof(buf)) != cudaSuccess)
+        return gb_fail("gb_gemm_tc_set_stamps: cannot set the buffer");
+    return 0;
+#else
+    (void)buf; (void)n; (void)k;
+    return gb_fail("gb_gemm_tc_set_stamps: this library was built without -DGB_STAMPS");
+#endif
+}
 GB_API int gb_tc_status() { return g_status_host ? *g_status_host : 0; }
 GB_API int gb_tc_status_clear() {
     if (g_status_host) *g_status_host = 0;

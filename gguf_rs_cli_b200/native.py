@@ -5,6 +5,10 @@ be built or loaded, or the device is not sm_100, the call fails loudly.
 The library is built in-tree (`csrc/_build/`) by nvcc at the first call that needs it
 and rebuilt when a source or flag changed; when the tree is not writable it is built
 in a per-user folder under the system's temporary directory.
+
+With GGUF_RS_CLI_B200_STAMPS=1 in the environment a second library is built beside it
+(`csrc/_build_stamps/`, -DGB_STAMPS) whose kernels write time stamps where they are asked
+to (csrc/stamps.cuh, bin/kernel_stamps); the ordinary library has none of that code.
 """
 from __future__ import annotations
 
@@ -25,6 +29,10 @@ CSRC = os.path.join(_HERE, "csrc")
 LIB_NAME = "libgguf_rs_cli_b200.so"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+STAMPS = os.environ.get("GGUF_RS_CLI_B200_STAMPS") == "1"
+if STAMPS:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DGB_STAMPS"]
+BUILD_DIR = "_build_stamps" if STAMPS else "_build"
 
 _lib = None
 _lock = threading.Lock()
@@ -57,7 +65,7 @@ def _stamp() -> str:
 
 
 def _build_dir() -> str:
-    d = os.path.join(CSRC, "_build")
+    d = os.path.join(CSRC, BUILD_DIR)
     try:
         os.makedirs(d, exist_ok=True)
         probe = os.path.join(d, f".w{os.getpid()}")
@@ -65,7 +73,7 @@ def _build_dir() -> str:
         os.remove(probe)
         return d
     except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"gguf_rs_cli_b200-{os.getuid()}", "_build")
+        d = os.path.join(tempfile.gettempdir(), f"gguf_rs_cli_b200-{os.getuid()}", BUILD_DIR)
         os.makedirs(d, exist_ok=True)
         return d
 
@@ -149,6 +157,8 @@ _SIGNATURES = {
     "gb_attention_decode_mma_supported": [_I, _I, _I],
     "gb_attention_decode_set_pages_kernel": [_I],
     "gb_attention_decode_set_two_warps": [_I],
+    "gb_attention_decode_set_stamps": [_P],
+    "gb_gemm_tc_set_stamps": [_P, _I, _I],
     "gb_attention_decode_scratch_floats": [_I, _I, _I, _I],
     "gb_attention_decode_supported": [_I, _I, _I],
     "gb_attention_prefill": [_P, _L, _P, _L, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _I, _F, _P],

@@ -65,3 +65,26 @@ def test_cli_generates_what_the_entry_point_generates(tmp_path):
     os.remove(os.path.join(folder, "model.safetensors"))
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 1 and "model.safetensors" in r.stderr
+
+
+@pytest.mark.gpu
+def test_kernel_stamps_program_reports_every_kernel_of_a_layer():
+    """bin/kernel_stamps builds the library's second variant (time stamps inside the kernels) and reports, for
+    the five kernels of a layer, where their CTAs pass the stamped places: every CTA enters, waits, and exits in
+    that order, and the products that share tiles show the places of the sharing."""
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "kernel_stamps"), "--tokens", "8", "--layers", "2"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = r.stdout
+    for name in ("q/k/v product", "o product", "gate+up product", "down product", "decode attention"):
+        assert f"--- {name}" in out
+    blocks = out.split("--- ")[1:]
+    assert "296 CTAs" in blocks[0] and "224 CTAs" in blocks[2] and "64 CTAs" in blocks[4]
+    assert "partial sums stored and fenced" in blocks[0] and "partial sums stored and fenced" not in blocks[2]
+    for b in blocks:
+        med = {}
+        for line in b.splitlines():
+            if " median " in line and line.startswith("  ") and "per CTA" not in line:
+                place = line[2:36].strip()
+                med[place] = float(line.split("median")[1].split()[0])
+        assert med["entry"] <= med["wait for the kernel in front over"] <= med["exit" if "exit" in med else "output written"]

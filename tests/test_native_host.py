@@ -15,3 +15,13 @@ def test_product_cut_never_asks_for_more_than_the_scratch_holds_and_takes_no_tok
     # a decode step of the 8B shape: the narrow products share their tiles, gate and up and the head do not
     assert lib.gb_gemm_tc_scratch_floats(8, 4096, 4096, sms) > 0 and lib.gb_gemm_tc_scratch_floats(8, 4096, 14336, sms) > 0
     assert lib.gb_gemm_tc_scratch_floats(8, 28672, 4096, sms) == 0 and lib.gb_gemm_tc_scratch_floats(8, 128256, 4096, sms) == 0
+
+
+def test_the_ordinary_library_has_no_time_stamps():
+    """Time stamps inside kernels belong to a second build (-DGB_STAMPS, bin/kernel_stamps); the library that
+    serves refuses to be given a buffer for them."""
+    import pytest
+    assert not native.STAMPS
+    for entry, args in (("gb_gemm_tc_set_stamps", (0, 0, 0)), ("gb_attention_decode_set_stamps", (0,))):
+        with pytest.raises(native.NativeError, match="without -DGB_STAMPS"):
+            native.call(entry, *args)
