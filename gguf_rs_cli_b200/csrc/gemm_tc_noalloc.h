@@ -44,6 +44,11 @@ extern "C" {
 // that must start at zero are cleared on `stream` before each launch, the partial tiles are
 // always written before they are read.  Two calls that overlap on the GPU (different streams,
 // or different host threads) race on it; run them one after the other.
+// Where CTAs share tiles of 32 tokens or more, each of them waits (for two seconds at most, then
+// the status below is set) until the tile's other CTAs have stored their sums; the kernel never
+// has more CTAs than the device holds at once, so they all run as soon as whatever occupied the
+// SMs before has left.  Work on other streams that keeps SMs busy for seconds can make that wait
+// run out.
 int gb_gemm_tc_noalloc(const void* X, long long ldx, const void* W, long long ldw, const void* bias, int bias_dtype,
                        void* out, int out_dtype, long long ldo, int T, int N, int K, cudaStream_t stream);
 
